@@ -1,0 +1,363 @@
+#!/usr/bin/env python
+"""Benchmark of the scan path: fwd+bwd elements/s and fraction of the HBM roofline.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one forward + one backward pass of the scan over the workload
+(B, D, T) = (16, 2048, 8192), bf16 storage / fp32 accumulation, long-memory gates
+a = 1 - 10^U(-4,-1), tokens and upstream gradient ~ N(0, 1), generated on the device from a
+seed (synthetic data).  Every tensor is 512 MiB, four times the L2, so no flush is needed
+between iterations.
+
+For N > 1 launch under torchrun (one rank per GPU).  Rows are independent, so each rank scans
+its own (16, 2048, 8192) shard of a global batch of 16*N with no data-path collective (weak
+scaling); `--scaling strong` instead splits the fixed 32768 rows over the ranks.
+
+Rank 0 prints ONE JSON line.  `value` is device-timed whole-job throughput with inputs resident
+in HBM; `e2e` is the same metric through the host-buffer entry of the C ABI (pinned host
+inputs -> device -> pinned host outputs inside the timed region); `roofline` describes the
+dominant kernel (backward); `cpu_baseline` is the CPU port timed on this box's host cores.
+
+`--impl reference` times the CPU implementation of the path (the pinned C port of the
+reference loop, OpenMP over rows, all host threads) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+WORKLOAD = {"name": "scan fwd+bwd (B,D,T)=(16,2048,8192) bf16 storage / fp32 accumulate",
+            "B": 16, "D": 2048, "T": 8192, "storage": "bf16"}
+METRIC = "scan fwd+bwd elements/s"
+UNIT = "elements/s"
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+CPU_SAMPLE_ROWS = 4096
+
+
+def measured_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+# ------------------------------------------------------------------------- clocks sampler ---
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+               0x4: "sw_power_cap", 0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, index: int, period_s: float = 0.005):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                    "samples": 0}
+        return {"sm_mhz": int(statistics.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def physical_gpu_index(local_index: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_index])
+        except Exception:
+            return local_index
+    return local_index
+
+
+# ------------------------------------------------------------------------- CPU baseline -----
+def cpu_port_throughput(rows: int, T: int, repeats: int, warmup: int = 1):
+    """fwd+bwd elements/s of the C port (OpenMP over rows) on `rows` x T of the workload."""
+    import numpy as np
+    from oracle import c_oracle as oc
+    from tests.helpers import make_inputs
+
+    a, x, G = make_inputs(rows, T, 1003, "long", "bf16")
+    times = []
+    for i in range(warmup + repeats):
+        t0 = time.perf_counter()
+        h = oc.plain_forward(a, x)
+        oc.plain_backward(a, h, G)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+    return rows * T / min(times), rows * T / statistics.mean(times), oc.num_threads(), times
+
+
+def torch_loop_throughput(rows: int, T: int):
+    """The reference's own CPU form (T dispatch-bound torch steps + autograd) on a small sample."""
+    import torch
+    from oracle import torch_loop as tl
+    from tests.helpers import make_inputs
+
+    a, x, G = (torch.from_numpy(v).view(1, rows, T) for v in make_inputs(rows, T, 1003, "long", "bf16"))
+    t0 = time.perf_counter()
+    tl.plain_fwd_bwd(a, x, G)
+    return rows * T / (time.perf_counter() - t0)
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    T = WORKLOAD["T"]
+    rows = CPU_SAMPLE_ROWS
+    best, mean, threads, times = cpu_port_throughput(rows, T, repeats=max(1, args.steps),
+                                                     warmup=max(1, args.warmup))
+    sample = (f"{rows} of {WORKLOAD['B'] * WORKLOAD['D']} rows x T={T} (rows are independent; "
+              f"fp32 arithmetic on bf16-rounded inputs), {len(times)} timed passes")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": mean, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": len(times), "warmup": max(1, args.warmup),
+        "ms_per_step": 1e3 * statistics.mean(times), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD["name"], "sample": sample},
+        "cpu_baseline": {"value": mean, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": sample, "best": best, "host_cpus": os.cpu_count()},
+        "e2e": {"value": mean, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------- GPU arm ----------
+def make_device_inputs(rows, T, seed, device):
+    import torch
+    gen = torch.Generator(device=device).manual_seed(seed)
+    u = torch.rand(rows, T, device=device, generator=gen)
+    a = (1.0 - torch.pow(10.0, -4.0 + 3.0 * u)).to(torch.bfloat16)
+    del u
+    x = torch.randn(rows, T, device=device, generator=gen).to(torch.bfloat16)
+    G = torch.randn(rows, T, device=device, generator=gen).to(torch.bfloat16)
+    return a, x, G
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from fm_b200 import capi, fm_scan_backward_ex, fm_scan_forward
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback of the product path)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    capi.lib()  # fail loudly if the CUDA library is missing
+
+    B, D, T = WORKLOAD["B"], WORKLOAD["D"], WORKLOAD["T"]
+    total_rows = B * D
+    if args.scaling == "strong":
+        rows = total_rows // world
+        global_rows = rows * world
+    else:
+        rows = total_rows
+        global_rows = rows * world
+    a, x, G = make_device_inputs(rows, T, 1003 + rank, device)
+    a3, x3, G3 = (t.view(-1, D, T) for t in (a, x, G))
+    h = torch.empty_like(a3)
+    ga = torch.empty_like(a3)
+    gx = torch.empty_like(a3)
+    n_local = rows * T
+
+    def step():
+        fm_scan_forward(a3, x3, None, h)
+        fm_scan_backward_ex(a3, G3, None, gx, h, ga, None, None)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+
+    K = args.steps
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(physical_gpu_index(local_rank)) as clocks:
+        barrier()
+        start.record()
+        for k in range(K):
+            ev[k][0].record()
+            fm_scan_forward(a3, x3, None, h)
+            ev[k][1].record()
+            fm_scan_backward_ex(a3, G3, None, gx, h, ga, None, None)
+            ev[k][2].record()
+        end.record()
+        barrier()
+    total_ms = start.elapsed_time(end)
+    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+    bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+
+    # end to end through host buffers
+    e2e = run_e2e(args, a3, x3, G3, device, barrier)
+
+    if world > 1:
+        t = torch.tensor([total_ms, fwd_ms, bwd_ms, e2e["ms"]], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, fwd_ms, bwd_ms, e2e_ms = (float(v) for v in t.tolist())
+    else:
+        e2e_ms = e2e["ms"]
+
+    if rank == 0:
+        s = 2  # bytes per stored element
+        ms_per_step = total_ms / K
+        value = global_rows * T / (ms_per_step * 1e-3)
+        peak, peak_kind = measured_peak()
+        bwd_gbs = 5 * s * n_local / (bwd_ms * 1e-3) / 1e9
+        fwd_gbs = 3 * s * n_local / (fwd_ms * 1e-3) / 1e9
+        both_gbs = 8 * s * n_local / ((fwd_ms + bwd_ms) * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K,
+            "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD["name"], "rows_per_gpu": rows, "T": T,
+                       "storage": "bf16", "accumulate": "f32",
+                       "gates": "a = 1 - 10^U(-4,-1) rounded to bf16; x, G ~ N(0,1)",
+                       "l2": "inputs larger than L2 (each tensor %d MiB per GPU), no flush" %
+                             (n_local * s >> 20),
+                       "sharding": "rows over ranks, no collective"},
+            "gpu_launches": 2 * K,
+            "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
+            "fwd_elements_per_s": global_rows * T / (fwd_ms * 1e-3),
+            "roofline": {"bound": "hbm", "kernel": "plain_backward_kernel", "achieved": bwd_gbs,
+                         "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": bwd_gbs / peak,
+                         "frac_of_nominal_8TBs": bwd_gbs / NOMINAL_HBM_GBS, "traffic": None,
+                         "algorithmic_bytes_per_launch": 5 * s * n_local},
+            "roofline_forward": {"kernel": "plain_forward_kernel", "achieved": fwd_gbs,
+                                 "frac": fwd_gbs / peak, "frac_of_nominal_8TBs": fwd_gbs / NOMINAL_HBM_GBS,
+                                 "algorithmic_bytes_per_launch": 3 * s * n_local},
+            "roofline_fwd_bwd": {"achieved": both_gbs, "frac": both_gbs / peak,
+                                 "frac_of_nominal_8TBs": both_gbs / NOMINAL_HBM_GBS},
+            "clocks": clocks.summary(),
+            "e2e": {"value": global_rows * T / (e2e_ms * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
+                    "ms_per_step": e2e_ms, "steps": e2e["steps"], "path": e2e["path"]},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            best, mean, threads, times = cpu_port_throughput(CPU_SAMPLE_ROWS, T, repeats=5)
+            line["cpu_baseline"] = {
+                "value": mean, "unit": UNIT, "cores": threads, "kind": "port",
+                "sample": f"{CPU_SAMPLE_ROWS} of {total_rows} rows x T={T}, 5 timed fwd+bwd passes of "
+                          "the C port (OpenMP over rows)",
+                "best": best, "host_cpus": os.cpu_count(),
+                "torch_loop_elements_per_s": torch_loop_throughput(64, T),
+                "torch_loop_sample": f"64 rows x T={T}, one fwd+autograd-bwd pass of the time-step loop"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_e2e(args, a3, x3, G3, device, barrier):
+    """Same step with pinned HOST inputs and outputs; copies inside the timed region."""
+    import torch
+
+    from fm_b200 import fm_scan_backward_ex, fm_scan_forward
+
+    steps = max(1, min(args.e2e_steps, args.steps))
+    host_in = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in (a3, x3, G3)]
+    for hb, t in zip(host_in, (a3, x3, G3)):
+        hb.copy_(t)
+    host_out = [torch.empty(a3.shape, dtype=a3.dtype, pin_memory=True) for _ in range(3)]
+    dev_in = [torch.empty_like(a3) for _ in range(3)]
+    dev_out = [torch.empty_like(a3) for _ in range(3)]
+    torch.cuda.synchronize()
+
+    def step():
+        for d, hb in zip(dev_in, host_in):
+            d.copy_(hb, non_blocking=True)
+        fm_scan_forward(dev_in[0], dev_in[1], None, dev_out[0])
+        fm_scan_backward_ex(dev_in[0], dev_in[2], None, dev_out[2], dev_out[0], dev_out[1], None, None)
+        for hb, d in zip(host_out, dev_out):
+            hb.copy_(d, non_blocking=True)
+
+    step()
+    barrier()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        step()
+    end.record()
+    barrier()
+    nbytes = a3.numel() * a3.element_size()
+    return {"ms": start.elapsed_time(end) / steps, "h2d": 3 * nbytes, "d2h": 3 * nbytes,
+            "steps": steps, "path": "pinned host -> H2D -> fm_scan_forward/backward -> D2H -> pinned host"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
+    ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

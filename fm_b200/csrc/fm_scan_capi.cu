@@ -1,0 +1,234 @@
+// C ABI of the B200 scan (see include/fm_scan_b200.h): argument checks, choice of the aligned
+// or the masked instantiation, kernel launches.  No allocation, no synchronisation, no torch.
+#include "fm_scan_b200.h"
+
+#include <cstdlib>
+
+#include "scan_kernels.cuh"
+
+#define FMS_EXPORT extern "C" __attribute__((visibility("default")))
+
+namespace {
+
+thread_local int g_last_cuda_error = 0;
+
+inline int record(cudaError_t e) {
+    if (e == cudaSuccess) return FMS_OK;
+    g_last_cuda_error = static_cast<int>(e);
+    if (e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver ||
+        e == cudaErrorNoKernelImageForDevice || e == cudaErrorInvalidDeviceFunction)
+        return FMS_ERR_NO_DEVICE;
+    return FMS_ERR_LAUNCH;
+}
+
+inline int check_launch() { return record(cudaGetLastError()); }
+
+inline bool aligned_to(const void *p, size_t a) {
+    return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0;
+}
+
+inline size_t elem_size(int dtype) { return dtype == FMS_F32 ? 4 : 2; }
+
+// rows * T must be addressable with int64 byte offsets.
+inline bool sizes_ok(int64_t rows, int64_t T) {
+    if (rows < 0 || T < 0) return false;
+    if (rows == 0 || T == 0) return true;
+    return rows <= (INT64_MAX / 8) / T;
+}
+
+// Tiles per group (loads in flight per warp = U x tensors x 512 B).  Tunable for experiments
+// through the environment; the defaults are the measured best on B200.
+int tune_unroll(const char *name, int dflt) {
+    const char *s = std::getenv(name);
+    if (!s) return dflt;
+    const int v = std::atoi(s);
+    return (v == 1 || v == 2 || v == 4) ? v : dflt;
+}
+
+struct Problem {
+    int64_t rows, T;
+    bool aligned;  // every row of every tensor starts on a 16-byte boundary
+    unsigned grid;
+};
+
+template <typename... Ptrs>
+int make_problem(Problem &pb, int64_t rows, int64_t T, int dtype, Ptrs... big) {
+    if (dtype != FMS_F32 && dtype != FMS_F16 && dtype != FMS_BF16) return FMS_ERR_BAD_DTYPE;
+    if (!sizes_ok(rows, T)) return FMS_ERR_BAD_SHAPE;
+    pb.rows = rows;
+    pb.T = T;
+    const int64_t ctas = (rows + fms::kWarpsPerCta - 1) / fms::kWarpsPerCta;
+    if (ctas > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;
+    pb.grid = static_cast<unsigned>(ctas);
+    if (rows == 0 || T == 0) {
+        pb.aligned = true;
+        return FMS_OK;
+    }
+    const size_t es = elem_size(dtype);
+    const void *ptrs[] = {big...};
+    bool all16 = (static_cast<uint64_t>(T) * es) % 16 == 0;
+    for (const void *p : ptrs) {
+        if (!p) return FMS_ERR_NULL_POINTER;
+        if (!aligned_to(p, es)) return FMS_ERR_MISALIGNED;
+        all16 = all16 && aligned_to(p, 16);
+    }
+    pb.aligned = all16;
+    return FMS_OK;
+}
+
+__global__ void copy_or_zero_kernel(const float *__restrict__ src, float *__restrict__ dst, int64_t n,
+                                    float fill) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = src ? src[i] : fill;
+}
+
+int copy_or_zero(const float *src, float *dst, int64_t n, float fill, cudaStream_t st) {
+    if (!dst || n == 0) return FMS_OK;
+    const int64_t blocks = (n + 255) / 256;
+    copy_or_zero_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(src, dst, n, fill);
+    return check_launch();
+}
+
+template <typename S, bool WRITE>
+int launch_forward(const Problem &pb, const void *gates, const void *tokens, const float *h0,
+                   void *states, float *h_last, float *P, cudaStream_t st) {
+    static const int unroll = tune_unroll("FMS_TUNE_FWD_U", sizeof(S) == 4 ? 4 : 4);
+    const dim3 grid(pb.grid), block(fms::kWarpsPerCta * 32);
+#define FMS_LAUNCH_FWD(G, UU)                                                                      \
+    fms::plain_forward_kernel<S, G, UU, WRITE><<<grid, block, 0, st>>>(                            \
+        static_cast<const S *>(gates), static_cast<const S *>(tokens), h0, static_cast<S *>(states), \
+        h_last, P, pb.rows, pb.T)
+    if (pb.aligned) {
+        if (unroll == 4) FMS_LAUNCH_FWD(false, 4);
+        else if (unroll == 2) FMS_LAUNCH_FWD(false, 2);
+        else FMS_LAUNCH_FWD(false, 1);
+    } else {
+        FMS_LAUNCH_FWD(true, 2);
+    }
+#undef FMS_LAUNCH_FWD
+    return check_launch();
+}
+
+template <typename S, bool WRITE>
+int launch_backward(const Problem &pb, const void *gates, const void *states, const void *grad_states,
+                    const float *h0, const float *carry_in, void *grad_gates, void *grad_tokens,
+                    float *grad_h0, float *P, cudaStream_t st) {
+    static const int unroll = tune_unroll("FMS_TUNE_BWD_U", 2);
+    const dim3 grid(pb.grid), block(fms::kWarpsPerCta * 32);
+#define FMS_LAUNCH_BWD(G, UU)                                                                      \
+    fms::plain_backward_kernel<S, G, UU, WRITE><<<grid, block, 0, st>>>(                           \
+        static_cast<const S *>(gates), static_cast<const S *>(states),                             \
+        static_cast<const S *>(grad_states), h0, carry_in, static_cast<S *>(grad_gates),           \
+        static_cast<S *>(grad_tokens), grad_h0, P, pb.rows, pb.T)
+    if (pb.aligned) {
+        if (unroll == 4) FMS_LAUNCH_BWD(false, 4);
+        else if (unroll == 2) FMS_LAUNCH_BWD(false, 2);
+        else FMS_LAUNCH_BWD(false, 1);
+    } else {
+        FMS_LAUNCH_BWD(true, 1);
+    }
+#undef FMS_LAUNCH_BWD
+    return check_launch();
+}
+
+#define FMS_DISPATCH_DTYPE(dtype, CALL)                                  \
+    switch (dtype) {                                                     \
+        case FMS_F32: { using S = float; return CALL; }                  \
+        case FMS_F16: { using S = __half; return CALL; }                 \
+        case FMS_BF16: { using S = __nv_bfloat16; return CALL; }         \
+        default: return FMS_ERR_BAD_DTYPE;                               \
+    }
+
+}  // namespace
+
+FMS_EXPORT int fms_version(void) { return 100; }
+
+FMS_EXPORT const char *fms_status_string(int status) {
+    switch (status) {
+        case FMS_OK: return "ok";
+        case FMS_ERR_BAD_SHAPE: return "bad shape: negative size or size overflow";
+        case FMS_ERR_BAD_DTYPE: return "unsupported dtype: expecting float32, float16 or bfloat16";
+        case FMS_ERR_NULL_POINTER: return "a required pointer is NULL";
+        case FMS_ERR_MISALIGNED: return "a pointer is not aligned to its element size";
+        case FMS_ERR_LAUNCH: return "CUDA launch or copy failed (see fms_last_cuda_error)";
+        case FMS_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+        case FMS_ERR_TOO_LARGE: return "problem exceeds a fixed capacity of this entry point";
+        case FMS_ERR_NO_DEVICE: return "no usable CUDA device (this library holds sm_100a code only)";
+        default: return "unknown status";
+    }
+}
+
+FMS_EXPORT int fms_last_cuda_error(void) { return g_last_cuda_error; }
+
+FMS_EXPORT int fms_plain_forward(const void *gates, const void *tokens, const float *h0, void *states,
+                                 float *h_last, int64_t rows, int64_t T, int dtype,
+                                 fms_stream_t stream) {
+    Problem pb;
+    if (int rc = make_problem(pb, rows, T, dtype, gates, tokens, static_cast<const void *>(states)))
+        return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (rows == 0) return FMS_OK;
+    if (T == 0) return copy_or_zero(h0, h_last, rows, 0.f, st);
+    FMS_DISPATCH_DTYPE(dtype, (launch_forward<S, true>(pb, gates, tokens, h0, states, h_last, nullptr, st)));
+}
+
+FMS_EXPORT int fms_plain_reduce(const void *gates, const void *tokens, float *P, float *S_out,
+                                int64_t rows, int64_t T, int dtype, fms_stream_t stream) {
+    Problem pb;
+    if (int rc = make_problem(pb, rows, T, dtype, gates, tokens)) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (rows == 0) return FMS_OK;
+    if (!P || !S_out) return FMS_ERR_NULL_POINTER;
+    if (T == 0) {
+        if (int rc = copy_or_zero(nullptr, P, rows, 1.f, st)) return rc;
+        return copy_or_zero(nullptr, S_out, rows, 0.f, st);
+    }
+    FMS_DISPATCH_DTYPE(dtype, (launch_forward<S, false>(pb, gates, tokens, nullptr, nullptr, S_out, P, st)));
+}
+
+FMS_EXPORT int fms_plain_backward(const void *gates, const void *states, const void *grad_states,
+                                  const float *h0, const float *carry_in, void *grad_gates,
+                                  void *grad_tokens, float *grad_h0, int64_t rows, int64_t T,
+                                  int dtype, fms_stream_t stream) {
+    Problem pb;
+    if (int rc = make_problem(pb, rows, T, dtype, gates, states, grad_states,
+                              static_cast<const void *>(grad_gates),
+                              static_cast<const void *>(grad_tokens)))
+        return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (rows == 0) return FMS_OK;
+    if (T == 0) return copy_or_zero(carry_in, grad_h0, rows, 0.f, st);
+    FMS_DISPATCH_DTYPE(dtype, (launch_backward<S, true>(pb, gates, states, grad_states, h0, carry_in,
+                                                        grad_gates, grad_tokens, grad_h0, nullptr, st)));
+}
+
+FMS_EXPORT int fms_plain_reduce_reverse(const void *gates, const void *grad_states, float *P,
+                                        float *S_rev, int64_t rows, int64_t T, int dtype,
+                                        fms_stream_t stream) {
+    Problem pb;
+    if (int rc = make_problem(pb, rows, T, dtype, gates, grad_states)) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (rows == 0) return FMS_OK;
+    if (!S_rev) return FMS_ERR_NULL_POINTER;
+    if (T == 0) {
+        if (int rc = copy_or_zero(nullptr, P, rows, 1.f, st)) return rc;
+        return copy_or_zero(nullptr, S_rev, rows, 0.f, st);
+    }
+    FMS_DISPATCH_DTYPE(dtype, (launch_backward<S, false>(pb, gates, nullptr, grad_states, nullptr, nullptr,
+                                                         nullptr, nullptr, S_rev, P, st)));
+}
+
+FMS_EXPORT int fms_combine_carries(const float *P, const float *S, const float *carry0,
+                                   float *carry_out, float *total, int64_t nchunks, int64_t rows,
+                                   int reverse, fms_stream_t stream) {
+    if (nchunks < 0 || rows < 0) return FMS_ERR_BAD_SHAPE;
+    if (rows == 0) return FMS_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (nchunks == 0) return copy_or_zero(carry0, total, rows, 0.f, st);
+    if (!P || !S || !carry_out) return FMS_ERR_NULL_POINTER;
+    const int64_t blocks = (rows + 127) / 128;
+    if (blocks > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;
+    fms::combine_carries_kernel<<<static_cast<unsigned>(blocks), 128, 0, st>>>(
+        P, S, carry0, carry_out, total, nchunks, rows, reverse ? 1 : 0);
+    return check_launch();
+}

@@ -1,0 +1,465 @@
+// Device code of the B200 scan: PLAIN-mode forward, backward and carry-only (reduce) kernels.
+//
+// Work decomposition
+//   One warp owns one row and walks it along time in groups of U tiles.  A tile is 32 lanes x
+//   one 16-byte vector (E = 4 fp32 or 8 fp16/bf16 elements per lane), i.e. 512 contiguous bytes
+//   per tensor per warp instruction, so every global access is a fully coalesced 128-bit
+//   access.  The loads of group g+1 are issued into registers before group g is computed, which
+//   keeps U x (number of input tensors) x 512 B in flight per warp across the serial carry.
+//
+//   Inside a tile: each lane scans its E elements sequentially to an aggregate pair
+//   (A, H) = (prod a, state from a zero start); the 32 pairs are combined with a 5-step
+//   warp-shuffle scan under the associative operator
+//        (A2, H2) o (A1, H1) = (A2*A1, A2*H1 + H2)          ("1" earlier in time than "2");
+//   the lane's carry-in follows from the exclusive prefix and the running row carry, and the
+//   lane re-runs its E elements sequentially from that carry-in to produce the outputs.  Only
+//   multiply-add pairs are used, so gates that are exactly 0 or 1 need no special case.
+//
+//   Backward uses the substitution c_t = a_t * delta_t (delta_t = G_t + c_{t+1}), which turns the
+//   "reverse scan with the gate shifted by one" (fm/scan/fm_scan.cuh:86-88,103-108) into a
+//   reverse scan with UNSHIFTED gates and tokens a_t*G_t: every vector load stays aligned, and
+//   the only halo is the single state h_{t-1} before a tile (one scalar load by lane 0).
+//
+// Rows whose start is not 16-byte aligned (odd T with 2-byte elements, sliced views) use the
+// GENERIC instantiation: tiles are laid on the 16-byte grid of the gates row, vectors that
+// straddle a row end or belong to a tensor with a different phase are read/written element by
+// element under a mask, and masked positions carry the identity (a = 1, x = 0).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fms {
+
+constexpr int kWarpsPerCta = 4;
+constexpr unsigned kFullMask = 0xffffffffu;
+
+// ---------------------------------------------------------------- storage <-> fp32 ----------
+// Mirrors the role of cast_to_float / cast_from_float (fm/scan/fm_scan.cuh:14-40): all
+// arithmetic is fp32, storage is fp32 / fp16 / bf16 with round-to-nearest-even on the way out.
+template <typename S>
+struct Store;
+
+template <>
+struct Store<float> {
+    static constexpr int E = 4;
+    static constexpr uint32_t kOne = 0x3f800000u;
+    static __device__ __forceinline__ void unpack(const uint4 &v, float (&f)[4]) {
+        f[0] = __uint_as_float(v.x);
+        f[1] = __uint_as_float(v.y);
+        f[2] = __uint_as_float(v.z);
+        f[3] = __uint_as_float(v.w);
+    }
+    static __device__ __forceinline__ uint4 pack(const float (&f)[4]) {
+        return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]),
+                          __float_as_uint(f[3]));
+    }
+    static __device__ __forceinline__ float to_float(float s) { return s; }
+};
+
+template <>
+struct Store<__nv_bfloat16> {
+    static constexpr int E = 8;
+    static constexpr uint32_t kOne = 0x3f803f80u;
+    static __device__ __forceinline__ void unpack(const uint4 &v, float (&f)[8]) {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            f[2 * k] = __uint_as_float(w[k] << 16);
+            f[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+        }
+    }
+    static __device__ __forceinline__ uint4 pack(const float (&f)[8]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            __nv_bfloat162 p = __floats2bfloat162_rn(f[2 * k], f[2 * k + 1]);
+            w[k] = *reinterpret_cast<uint32_t *>(&p);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    static __device__ __forceinline__ float to_float(__nv_bfloat16 s) { return __bfloat162float(s); }
+};
+
+template <>
+struct Store<__half> {
+    static constexpr int E = 8;
+    static constexpr uint32_t kOne = 0x3c003c00u;
+    static __device__ __forceinline__ void unpack(const uint4 &v, float (&f)[8]) {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float2 p = __half22float2(*reinterpret_cast<const __half2 *>(&w[k]));
+            f[2 * k] = p.x;
+            f[2 * k + 1] = p.y;
+        }
+    }
+    static __device__ __forceinline__ uint4 pack(const float (&f)[8]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            __half2 p = __floats2half2_rn(f[2 * k], f[2 * k + 1]);
+            w[k] = *reinterpret_cast<uint32_t *>(&p);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    static __device__ __forceinline__ float to_float(__half s) { return __half2float(s); }
+};
+
+// ---------------------------------------------------------------- global memory access ------
+// Streaming 128-bit accesses: every byte is touched once per kernel, so loads bypass L1
+// allocation and stores are marked evict-first.
+__device__ __forceinline__ uint4 ldg_stream(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void stg_stream(void *p, const uint4 &v) {
+    asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+                 "r"(v.w)
+                 : "memory");
+}
+
+// One lane's vector of a row: positions [v, v+E).  `fill` is the 32-bit pattern returned for
+// positions outside [0, T) (packed ones for gates, zero otherwise).  In the aligned
+// instantiation a vector is either wholly inside the row or wholly outside it.
+template <typename S, bool GENERIC>
+__device__ __forceinline__ uint4 load_vec(const S *__restrict__ row, int64_t v, int64_t T,
+                                          bool same_phase, uint32_t fill) {
+    constexpr int E = Store<S>::E;
+    if constexpr (!GENERIC) {
+        if (v < T) return ldg_stream(row + v);
+        return make_uint4(fill, fill, fill, fill);
+    } else {
+        if (same_phase && v >= 0 && v + E <= T) return ldg_stream(row + v);
+        union {
+            uint4 q;
+            S s[E];
+        } u;
+        u.q = make_uint4(fill, fill, fill, fill);
+#pragma unroll
+        for (int i = 0; i < E; ++i) {
+            const int64_t t = v + i;
+            if (t >= 0 && t < T) u.s[i] = row[t];
+        }
+        return u.q;
+    }
+}
+
+template <typename S, bool GENERIC>
+__device__ __forceinline__ void store_vec(S *__restrict__ row, int64_t v, int64_t T,
+                                          bool same_phase, const uint4 &q) {
+    constexpr int E = Store<S>::E;
+    if constexpr (!GENERIC) {
+        if (v < T) stg_stream(row + v, q);
+    } else {
+        if (same_phase && v >= 0 && v + E <= T) {
+            stg_stream(row + v, q);
+            return;
+        }
+        union {
+            uint4 q;
+            S s[E];
+        } u;
+        u.q = q;
+#pragma unroll
+        for (int i = 0; i < E; ++i) {
+            const int64_t t = v + i;
+            if (t >= 0 && t < T) row[t] = u.s[i];
+        }
+    }
+}
+
+// Row geometry shared by all kernels: where the first (virtual) vector of the row starts and
+// how many groups of U tiles cover it.
+template <typename S, bool GENERIC>
+__device__ __forceinline__ int64_t row_phase(const S *row) {
+    if constexpr (GENERIC)
+        return -static_cast<int64_t>((reinterpret_cast<uintptr_t>(row) & 15u) / sizeof(S));
+    else
+        return 0;
+}
+
+__device__ __forceinline__ bool same_phase16(const void *p, const void *q) {
+    return ((reinterpret_cast<uintptr_t>(p) ^ reinterpret_cast<uintptr_t>(q)) & 15u) == 0;
+}
+
+// ---------------------------------------------------------------- forward / reduce ----------
+// WRITE = true : states (and optionally h_last) are produced            -> fms_plain_forward
+// WRITE = false: only the carries P = prod a and S = h_last are produced -> fms_plain_reduce
+template <typename S, bool GENERIC, int U, bool WRITE>
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+plain_forward_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
+                     const float *__restrict__ h0, S *__restrict__ states,
+                     float *__restrict__ h_last, float *__restrict__ P_out, int64_t R, int64_t T) {
+    constexpr int E = Store<S>::E;
+    constexpr int TILE = 32 * E;
+    const int lane = threadIdx.x & 31;
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
+    if (row >= R) return;
+
+    const S *ar = gates + row * T;
+    const S *xr = tokens + row * T;
+    S *hr = WRITE ? states + row * T : nullptr;
+    const int64_t vbase = row_phase<S, GENERIC>(ar);
+    const bool ph_x = !GENERIC || same_phase16(ar, xr);
+    const bool ph_h = !GENERIC || !WRITE || same_phase16(ar, hr);
+    const int64_t ngroups = (T - vbase + TILE * U - 1) / (TILE * U);
+
+    float carry = h0 ? h0[row] : 0.f;  // state entering the current tile
+    float prod = 1.f;                  // product of all gates so far (reduce only)
+
+    int64_t v = vbase + lane * E;  // this lane's vector in tile 0 of the current group
+    uint4 ra[U], rx[U];
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+        ra[j] = load_vec<S, GENERIC>(ar, v + j * TILE, T, true, Store<S>::kOne);
+        rx[j] = load_vec<S, GENERIC>(xr, v + j * TILE, T, ph_x, 0u);
+    }
+
+    for (int64_t g = 0; g < ngroups; ++g) {
+        // Prefetch the next group (vectors past the row end return the identity without a
+        // memory access).
+        uint4 na[U], nx[U];
+        const int64_t vn = v + TILE * U;
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            na[j] = load_vec<S, GENERIC>(ar, vn + j * TILE, T, true, Store<S>::kOne);
+            nx[j] = load_vec<S, GENERIC>(xr, vn + j * TILE, T, ph_x, 0u);
+        }
+
+        float fa[U][E], fx[U][E], A[U], H[U];
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            Store<S>::unpack(ra[j], fa[j]);
+            Store<S>::unpack(rx[j], fx[j]);
+            A[j] = fa[j][0];
+            H[j] = fx[j][0];
+#pragma unroll
+            for (int i = 1; i < E; ++i) {
+                H[j] = fmaf(fa[j][i], H[j], fx[j][i]);
+                A[j] *= fa[j][i];
+            }
+        }
+        // Inclusive warp scan of the U independent tiles (interleaved for ILP).
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+#pragma unroll
+            for (int j = 0; j < U; ++j) {
+                const float pA = __shfl_up_sync(kFullMask, A[j], d);
+                const float pH = __shfl_up_sync(kFullMask, H[j], d);
+                if (lane >= d) {
+                    H[j] = fmaf(A[j], pH, H[j]);
+                    A[j] *= pA;
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            float eA = __shfl_up_sync(kFullMask, A[j], 1);
+            float eH = __shfl_up_sync(kFullMask, H[j], 1);
+            if (lane == 0) {
+                eA = 1.f;
+                eH = 0.f;
+            }
+            const float tA = __shfl_sync(kFullMask, A[j], 31);
+            const float tH = __shfl_sync(kFullMask, H[j], 31);
+            if constexpr (WRITE) {
+                float s = fmaf(eA, carry, eH);  // state entering this lane's elements
+                float out[E];
+#pragma unroll
+                for (int i = 0; i < E; ++i) {
+                    s = fmaf(fa[j][i], s, fx[j][i]);
+                    out[i] = s;
+                }
+                store_vec<S, GENERIC>(hr, v + j * TILE, T, ph_h, Store<S>::pack(out));
+            } else {
+                prod *= tA;
+            }
+            carry = fmaf(tA, carry, tH);
+        }
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            ra[j] = na[j];
+            rx[j] = nx[j];
+        }
+        v = vn;
+    }
+    if (lane == 0) {
+        if (h_last) h_last[row] = carry;
+        if (!WRITE && P_out) P_out[row] = prod;
+    }
+}
+
+// ---------------------------------------------------------------- backward / reverse reduce -
+// c_t = a_t * (G_t + c_{t+1}) scanned from the row end; delta_t = G_t + c_{t+1};
+// grad_tokens_t = delta_t; grad_gates_t = delta_t * h_{t-1}; grad_h0 = c_0.
+// WRITE = false produces only S_rev = c_0 (from carry_in = 0) and P = prod a.
+template <typename S, bool GENERIC, int U, bool WRITE>
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+plain_backward_kernel(const S *__restrict__ gates, const S *__restrict__ states,
+                      const S *__restrict__ grad_states, const float *__restrict__ h0,
+                      const float *__restrict__ carry_in, S *__restrict__ grad_gates,
+                      S *__restrict__ grad_tokens, float *__restrict__ grad_h0,
+                      float *__restrict__ P_out, int64_t R, int64_t T) {
+    constexpr int E = Store<S>::E;
+    constexpr int TILE = 32 * E;
+    const int lane = threadIdx.x & 31;
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
+    if (row >= R) return;
+
+    const S *ar = gates + row * T;
+    const S *gr = grad_states + row * T;
+    const S *hr = WRITE ? states + row * T : nullptr;
+    S *gar = WRITE ? grad_gates + row * T : nullptr;
+    S *gxr = WRITE ? grad_tokens + row * T : nullptr;
+    const int64_t vbase = row_phase<S, GENERIC>(ar);
+    const bool ph_g = !GENERIC || same_phase16(ar, gr);
+    const bool ph_h = !GENERIC || !WRITE || same_phase16(ar, hr);
+    const bool ph_ga = !GENERIC || !WRITE || same_phase16(ar, gar);
+    const bool ph_gx = !GENERIC || !WRITE || same_phase16(ar, gxr);
+    const int64_t ngroups = (T - vbase + TILE * U - 1) / (TILE * U);
+
+    const float h_init = (WRITE && h0) ? h0[row] : 0.f;
+    float carry = carry_in ? carry_in[row] : 0.f;  // c at the first position after the tile
+    float prod = 1.f;
+
+    // State just before a tile (h_{t-1} of the tile's first element); needed by lane 0 only.
+    auto load_halo = [&](int64_t vt) -> float {
+        if (!WRITE || lane != 0) return 0.f;
+        const int64_t t = vt - 1;
+        return (t >= 0 && t < T) ? Store<S>::to_float(hr[t]) : h_init;
+    };
+
+    int64_t v = vbase + (ngroups - 1) * (TILE * U) + lane * E;  // last group first
+    uint4 ra[U], rg[U], rh[U];
+    float halo[U];
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+        ra[j] = load_vec<S, GENERIC>(ar, v + j * TILE, T, true, Store<S>::kOne);
+        rg[j] = load_vec<S, GENERIC>(gr, v + j * TILE, T, ph_g, 0u);
+        if constexpr (WRITE) {
+            rh[j] = load_vec<S, GENERIC>(hr, v + j * TILE, T, ph_h, 0u);
+            halo[j] = load_halo(v + j * TILE);
+        }
+    }
+
+    for (int64_t g = ngroups - 1; g >= 0; --g) {
+        uint4 na[U], ng[U], nh[U];
+        float nhalo[U];
+        const int64_t vn = v - TILE * U;
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            // vn + j*TILE + E <= vbase means the whole vector lies before the row: identity.
+            const int64_t vv = (g > 0) ? vn + j * TILE : T;  // T = "outside" for every path
+            na[j] = load_vec<S, GENERIC>(ar, vv, T, true, Store<S>::kOne);
+            ng[j] = load_vec<S, GENERIC>(gr, vv, T, ph_g, 0u);
+            if constexpr (WRITE) {
+                nh[j] = load_vec<S, GENERIC>(hr, vv, T, ph_h, 0u);
+                nhalo[j] = (g > 0) ? load_halo(vv) : 0.f;
+            }
+        }
+
+        float fa[U][E], fg[U][E], A[U], C[U];
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            Store<S>::unpack(ra[j], fa[j]);
+            Store<S>::unpack(rg[j], fg[j]);
+            A[j] = fa[j][E - 1];
+            C[j] = fa[j][E - 1] * fg[j][E - 1];
+#pragma unroll
+            for (int i = E - 2; i >= 0; --i) {
+                C[j] = fa[j][i] * (fg[j][i] + C[j]);
+                A[j] *= fa[j][i];
+            }
+        }
+        // Inclusive warp scan towards lane 0 (later positions combine into earlier ones).
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+#pragma unroll
+            for (int j = 0; j < U; ++j) {
+                const float pA = __shfl_down_sync(kFullMask, A[j], d);
+                const float pC = __shfl_down_sync(kFullMask, C[j], d);
+                if (lane + d < 32) {
+                    C[j] = fmaf(A[j], pC, C[j]);
+                    A[j] *= pA;
+                }
+            }
+        }
+#pragma unroll
+        for (int j = U - 1; j >= 0; --j) {
+            float eA = __shfl_down_sync(kFullMask, A[j], 1);
+            float eC = __shfl_down_sync(kFullMask, C[j], 1);
+            if (lane == 31) {
+                eA = 1.f;
+                eC = 0.f;
+            }
+            const float tA = __shfl_sync(kFullMask, A[j], 0);
+            const float tC = __shfl_sync(kFullMask, C[j], 0);
+            if constexpr (WRITE) {
+                float fh[E];
+                Store<S>::unpack(rh[j], fh);
+                // h_{t-1} of this lane's first element: last state of the lane below, or the halo.
+                float hprev0 = __shfl_up_sync(kFullMask, fh[E - 1], 1);
+                if (lane == 0) hprev0 = halo[j];
+                float c = fmaf(eA, carry, eC);  // c just after this lane's elements
+                float dx[E], da[E];
+#pragma unroll
+                for (int i = E - 1; i >= 0; --i) {
+                    const float delta = fg[j][i] + c;
+                    c = fa[j][i] * delta;
+                    float hp = (i > 0) ? fh[i > 0 ? i - 1 : 0] : hprev0;
+                    if constexpr (GENERIC) {
+                        if (v + j * TILE + i == 0) hp = h_init;  // row start inside a vector
+                    }
+                    dx[i] = delta;
+                    da[i] = delta * hp;
+                }
+                store_vec<S, GENERIC>(gxr, v + j * TILE, T, ph_gx, Store<S>::pack(dx));
+                store_vec<S, GENERIC>(gar, v + j * TILE, T, ph_ga, Store<S>::pack(da));
+            } else {
+                prod *= tA;
+            }
+            carry = fmaf(tA, carry, tC);
+        }
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            ra[j] = na[j];
+            rg[j] = ng[j];
+            if constexpr (WRITE) {
+                rh[j] = nh[j];
+                halo[j] = nhalo[j];
+            }
+        }
+        v = vn;
+    }
+    if (lane == 0) {
+        if (grad_h0) grad_h0[row] = carry;
+        if (!WRITE && P_out) P_out[row] = prod;
+    }
+}
+
+// ---------------------------------------------------------------- carry combination ---------
+// One thread per row folds the per-block carries serially in scan order (nchunks is the number
+// of ranks or time blocks: small).
+__global__ void combine_carries_kernel(const float *__restrict__ P, const float *__restrict__ S,
+                                       const float *__restrict__ carry0,
+                                       float *__restrict__ carry_out, float *__restrict__ total,
+                                       int64_t nchunks, int64_t R, int reverse) {
+    const int64_t r = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (r >= R) return;
+    float c = carry0 ? carry0[r] : 0.f;
+    for (int64_t i = 0; i < nchunks; ++i) {
+        const int64_t k = reverse ? nchunks - 1 - i : i;
+        carry_out[k * R + r] = c;
+        c = fmaf(P[k * R + r], c, S[k * R + r]);
+    }
+    if (total) total[r] = c;
+}
+
+}  // namespace fms

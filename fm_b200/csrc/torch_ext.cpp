@@ -1,0 +1,145 @@
+// Thin torch C++ extension over the C ABI (include/fm_scan_b200.h).
+//
+// It exports the two functions the reference binds into Python (fm/scan/fm_scan.py:8-16,34-35)
+// with the same names, argument order and conventions:
+//   at::Tensor fm_scan_forward (gates, tokens, initial_state, out)         fm/scan/fm_scan.cuh:344-358
+//   void       fm_scan_backward(gates, outGrad, firstPropGrad, tokenGradOut,
+//                               cached_output, input_tokens, gateGradOut)  fm/scan/fm_scan.cuh:361-381
+// Every tensor, outputs included, is allocated by the caller; failures surface as c10::Error
+// (RuntimeError in Python) exactly like the reference's TORCH_CHECKs.  Unlike the reference it
+// installs a device guard, launches on the current stream of the tensors' device, and checks
+// the launch.
+//
+// Layout: all big tensors are (B, D, T) -- one independent scan per (b, d) row.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "fm_scan_b200.h"
+
+namespace {
+
+int dtype_tag(const at::Tensor &t) {
+    switch (t.scalar_type()) {
+        case at::ScalarType::Float: return FMS_F32;
+        case at::ScalarType::Half: return FMS_F16;
+        case at::ScalarType::BFloat16: return FMS_BF16;
+        default:
+            TORCH_CHECK(false, "Unsupported tensor dtype: expecting bfloat16, float16 or float32");
+    }
+}
+
+void check_status(int rc, const char *what) {
+    TORCH_CHECK(rc == FMS_OK, what, " failed: ", fms_status_string(rc), " (status ", rc,
+                ", cuda error ", fms_last_cuda_error(), ")");
+}
+
+void check_big(const at::Tensor &t, const at::Tensor &like, const char *name) {
+    TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+    TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+    TORCH_CHECK(t.scalar_type() == like.scalar_type(), name, " must have the dtype of gates");
+    TORCH_CHECK(t.device() == like.device(), name, " must be on the device of gates");
+    TORCH_CHECK(t.sizes() == like.sizes(), name, " must have the shape of gates");
+}
+
+// Per-row fp32 carry vector from an optional tensor of `rows` elements (any float dtype).
+// Returns an fp32 contiguous tensor (possibly the argument itself) or an undefined tensor.
+at::Tensor carry_f32(const c10::optional<at::Tensor> &t, int64_t rows, const at::Tensor &like,
+                     const char *name) {
+    if (!t.has_value() || !t->defined() || t->numel() == 0) return at::Tensor();
+    TORCH_CHECK(t->is_cuda() && t->device() == like.device(), name, " must be on the device of gates");
+    TORCH_CHECK(t->numel() == rows, name, " must have one element per row (", rows, "), got ",
+                t->numel());
+    return t->to(at::kFloat).contiguous();
+}
+
+const float *fptr(const at::Tensor &t) { return t.defined() ? t.data_ptr<float>() : nullptr; }
+
+
+int64_t rows_of_shape(const at::Tensor &t) {
+    int64_t r = 1;
+    for (int64_t i = 0; i + 1 < t.dim(); ++i) r *= t.size(i);
+    return r;
+}
+
+}  // namespace
+
+// Forward.  gates, tokens, out: (..., T) of one dtype; initial_state: (...), None or empty (= zeros,
+// which is what fm/scan/fm_scan.py:48 passes by default).  Returns `out`.
+at::Tensor fm_scan_forward(const at::Tensor &gates, const at::Tensor &tokens,
+                           const c10::optional<at::Tensor> &initial_state, const at::Tensor &out) {
+    TORCH_CHECK(gates.is_cuda(), "gates must be a CUDA tensor");
+    TORCH_CHECK(gates.is_contiguous(), "gates must be contiguous");
+    check_big(tokens, gates, "tokens");
+    check_big(out, gates, "out");
+    const int dtype = dtype_tag(gates);
+    const int64_t rows = rows_of_shape(gates), T = gates.size(-1);
+    const c10::cuda::CUDAGuard guard(gates.device());
+    at::Tensor h0 = carry_f32(initial_state, rows, gates, "initial_state");
+    auto stream = at::cuda::getCurrentCUDAStream().stream();
+    check_status(fms_plain_forward(gates.data_ptr(), tokens.data_ptr(), fptr(h0), out.data_ptr(),
+                                   nullptr, rows, T, dtype, stream),
+                 "fm_scan_forward");
+    return out;
+}
+
+// Backward with every carry exposed.
+//   carry_in           (...) or empty: a_T*delta_T entering from beyond the block (the reference's
+//                      firstPropGrad, fm/scan/fm_scan.cuh:120-122)
+//   initial_state      (...) or empty: the forward h0, i.e. h_{-1} for grad_gates at t = 0
+//   grad_initial_state (...) fp32 or empty: receives dL/dh0
+void fm_scan_backward_ex(const at::Tensor &gates, const at::Tensor &outGrad,
+                         const c10::optional<at::Tensor> &carry_in, const at::Tensor &tokenGradOut,
+                         const at::Tensor &cached_output, const at::Tensor &gateGradOut,
+                         const c10::optional<at::Tensor> &initial_state,
+                         const c10::optional<at::Tensor> &grad_initial_state_opt) {
+    TORCH_CHECK(gates.is_cuda(), "gates must be a CUDA tensor");
+    TORCH_CHECK(gates.is_contiguous(), "gates must be contiguous");
+    check_big(outGrad, gates, "outGrad");
+    check_big(cached_output, gates, "cached_output");
+    check_big(tokenGradOut, gates, "tokenGradOut");
+    check_big(gateGradOut, gates, "gateGradOut");
+    const int dtype = dtype_tag(gates);
+    const int64_t rows = rows_of_shape(gates), T = gates.size(-1);
+    const c10::cuda::CUDAGuard guard(gates.device());
+    at::Tensor cin = carry_f32(carry_in, rows, gates, "firstPropGrad");
+    at::Tensor h0 = carry_f32(initial_state, rows, gates, "initial_state");
+    float *gh0 = nullptr;
+    const at::Tensor grad_initial_state =
+        grad_initial_state_opt.has_value() ? *grad_initial_state_opt : at::Tensor();
+    if (grad_initial_state.defined() && grad_initial_state.numel() > 0) {
+        TORCH_CHECK(grad_initial_state.is_cuda() && grad_initial_state.is_contiguous() &&
+                        grad_initial_state.scalar_type() == at::kFloat &&
+                        grad_initial_state.numel() == rows,
+                    "grad_initial_state must be a contiguous fp32 CUDA tensor with one element per row");
+        gh0 = grad_initial_state.data_ptr<float>();
+    }
+    auto stream = at::cuda::getCurrentCUDAStream().stream();
+    check_status(fms_plain_backward(gates.data_ptr(), cached_output.data_ptr(), outGrad.data_ptr(),
+                                    fptr(h0), fptr(cin), gateGradOut.data_ptr(),
+                                    tokenGradOut.data_ptr(), gh0, rows, T, dtype, stream),
+                 "fm_scan_backward");
+}
+
+// Backward with the reference's seven arguments.  firstPropGrad seeds the reverse scan
+// (fm/scan/fm_scan.cuh:120-122); the reference passes zeros (fm/scan/fm_scan.py:65).
+// input_tokens is accepted for signature compatibility and not read: with the token weight
+// dropped, grad_gates_t = delta_t * h_{t-1} needs no tokens.  h_{-1} is taken as zero, which is
+// what the reference's call amounts to (its h_{-1} is firstPropGrad = zeros,
+// fm/scan/fm_scan.cuh:195-196).
+void fm_scan_backward(const at::Tensor &gates, const at::Tensor &outGrad,
+                      const c10::optional<at::Tensor> &firstPropGrad, const at::Tensor &tokenGradOut,
+                      const at::Tensor &cached_output, const c10::optional<at::Tensor> &input_tokens,
+                      const at::Tensor &gateGradOut) {
+    (void)input_tokens;
+    fm_scan_backward_ex(gates, outGrad, firstPropGrad, tokenGradOut, cached_output, gateGradOut,
+                        c10::nullopt, c10::nullopt);
+}
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.doc() = "fm_scan for B200: torch shim over the C ABI libfm_scan_b200.so";
+    m.def("fm_scan_forward", &fm_scan_forward, "scan forward (writes and returns out)");
+    m.def("fm_scan_backward", &fm_scan_backward, "scan backward, reference signature");
+    m.def("fm_scan_backward_ex", &fm_scan_backward_ex, "scan backward with h0 / carry_in / grad_h0");
+    m.def("abi_version", []() { return fms_version(); });
+}

@@ -1,0 +1,99 @@
+"""Python op API of the scan, mirroring fm/scan/fm_scan.py of the reference.
+
+``fm_scan(gates, tokens, initial_state=None)`` keeps the reference's call surface
+(fm/scan/fm_scan.py:84-99) on the plain recurrence and layout
+
+    gates a, tokens x, states h : (B, D, T)        h[b,d,t] = a[b,d,t] * h[b,d,t-1] + x[b,d,t]
+
+``FM_Scan`` is the autograd function (fm/scan/fm_scan.py:37-81): forward allocates the output
+and saves ``(gates, states)``; backward runs one fused reverse kernel that writes ``grad_gates``
+and ``grad_tokens`` directly in the inputs' shape (no full-size temporaries, no reductions) and
+returns ``(d_gates, d_tokens, d_initial_state)``.  Unlike the reference, a non-zero
+``initial_state`` is honoured in backward and receives its gradient.
+
+The compiled extension is loaded lazily on first use; if it is missing the call raises --
+nothing here computes on the CPU.
+"""
+from __future__ import annotations
+
+import importlib
+
+import torch
+
+_ext = None
+
+
+def _load_ext():
+    global _ext
+    if _ext is None:
+        try:
+            _ext = importlib.import_module("fm_b200._fm_scan_ext")
+        except ImportError as e:
+            raise RuntimeError(
+                "fm_b200._fm_scan_ext is not built or cannot be loaded "
+                "(run `python -m fm_b200.build`); there is no fallback implementation") from e
+    return _ext
+
+
+def fm_scan_forward(gates, tokens, initial_state, out):
+    """C++ entry point, reference signature (fm/scan/fm_scan.cuh:344-345): writes and returns ``out``."""
+    return _load_ext().fm_scan_forward(gates, tokens, initial_state, out)
+
+
+def fm_scan_backward(gates, outGrad, firstPropGrad, tokenGradOut, cached_output, input_tokens, gateGradOut):
+    """C++ entry point, reference signature (fm/scan/fm_scan.cuh:361-366)."""
+    return _load_ext().fm_scan_backward(gates, outGrad, firstPropGrad, tokenGradOut, cached_output,
+                                        input_tokens, gateGradOut)
+
+
+def fm_scan_backward_ex(gates, outGrad, carry_in, tokenGradOut, cached_output, gateGradOut,
+                        initial_state=None, grad_initial_state=None):
+    """Backward with the forward initial state and its gradient (fp32, one value per row)."""
+    return _load_ext().fm_scan_backward_ex(gates, outGrad, carry_in, tokenGradOut, cached_output,
+                                           gateGradOut, initial_state, grad_initial_state)
+
+
+class FM_Scan(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gates, tokens, initial_state=None):
+        assert gates.dim() >= 1 and gates.shape == tokens.shape, \
+            f"gates {tuple(gates.shape)} and tokens {tuple(tokens.shape)} must have the same shape"
+        assert gates.is_contiguous()
+        assert tokens.is_contiguous()
+        if initial_state is not None:
+            assert initial_state.shape == gates.shape[:-1]
+            assert initial_state.is_contiguous()
+        output = torch.empty_like(gates)
+        states = fm_scan_forward(gates, tokens, initial_state, output)
+        ctx.save_for_backward(gates, states, initial_state)
+        ctx.h0_needs_grad = initial_state is not None and ctx.needs_input_grad[2]
+        return states
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        gates, states, initial_state = ctx.saved_tensors
+        grad_output = grad_output.contiguous()
+        d_gates = torch.empty_like(gates)
+        d_tokens = torch.empty_like(gates)
+        d_h0 = None
+        if ctx.h0_needs_grad:
+            d_h0 = torch.empty(initial_state.shape, device=gates.device, dtype=torch.float32)
+        fm_scan_backward_ex(gates, grad_output, None, d_tokens, states, d_gates, initial_state, d_h0)
+        if d_h0 is not None:
+            d_h0 = d_h0.to(initial_state.dtype)
+        return d_gates, d_tokens, d_h0
+
+
+def fm_scan(gates, tokens, initial_state=None):
+    """Solve the first-order recurrence ``h_t = a_t * h_{t-1} + x_t`` along the last axis.
+
+    Arguments:
+        gates (torch.Tensor): a, shape (B, D, T), contiguous CUDA tensor, fp32 / fp16 / bf16.
+            Any T >= 1 (the reference required a power of two in [32, 131072]).
+        tokens (torch.Tensor): x, same shape, dtype and device.
+        initial_state (torch.Tensor, optional): h_{-1}, shape (B, D); zeros when omitted.
+
+    Returns:
+        torch.Tensor: states h, shape (B, D, T), dtype of ``gates``.  Arithmetic is fp32.
+    """
+    return FM_Scan.apply(gates, tokens, initial_state)

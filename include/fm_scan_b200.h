@@ -1,0 +1,132 @@
+/*
+ * fm_scan_b200 -- C ABI of the B200 (sm_100a) first-order linear-recurrence scan.
+ *
+ * This is the drop-in boundary for the scan path of lexionbear/fm.  The reference binds
+ * two C++ functions into Python (fm/scan/fm_scan.py:8-16,34-35):
+ *
+ *   at::Tensor fm_scan_forward (gates, tokens, initial_state, out)          fm/scan/fm_scan.cuh:344-358
+ *   void       fm_scan_backward(gates, outGrad, firstPropGrad, tokenGradOut,
+ *                               cached_output, input_tokens, gateGradOut)   fm/scan/fm_scan.cuh:361-381
+ *
+ * The functions below are what those two would call instead of the reference's
+ * fmscan_launch<> (fm/scan/fm_scan.cuh:248-331): raw device pointers, sizes, a dtype tag
+ * and a stream.  No torch types appear here.
+ *
+ * Conventions (all entry points unless stated otherwise)
+ *  - return value: 0 (FMS_OK) or an fms_status code; nothing throws;
+ *  - nothing allocates or frees device memory, nothing synchronises the device or the
+ *    stream; kernels are enqueued on `stream` of the CURRENT device (the caller selects
+ *    the device; the reference never did, fm/scan/fm_scan.cuh:271-272);
+ *  - tensors are contiguous, row-major, last axis = time; any T >= 0 and any number of
+ *    rows (the reference accepted 13 powers of two only, fm/scan/fm_scan.cuh:275-329);
+ *    offsets are 64-bit (the reference's were 32-bit, fm/scan/fm_scan.cuh:76-82);
+ *  - `dtype` is the STORAGE type of the big tensors; arithmetic is fp32 throughout
+ *    (fm/scan/fm_scan.cuh:14-40); per-row carries (h0, h_last, carry_in, grad_h0, P, S)
+ *    are always fp32;
+ *  - pointers must be aligned to their element size.  Rows that are 16-byte aligned in
+ *    every tensor (T*sizeof(element) % 16 == 0 and 16-byte aligned bases) take the fully
+ *    vectorised path; everything else takes the masked path with identical results.
+ *
+ * PLAIN mode:   h[r,t] = a[r,t] * h[r,t-1] + x[r,t]                    rows r < R
+ * FM mode   :   h[b,m,d,t] = g[b,m,t] * h[b,m,d,t-1] + (1 - g[b,m,t]) * x[b,d,t]
+ *               (the reference's operator, fm/scan/fm_pytorch.py:19-42)
+ */
+#ifndef FM_SCAN_B200_H_
+#define FM_SCAN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Opaque stream handle: pass a cudaStream_t (NULL = the legacy default stream). */
+typedef void *fms_stream_t;
+
+typedef enum fms_dtype {
+    FMS_F32 = 0,  /* float          (reference: <float, float>,               fm_scan.cuh:338-339) */
+    FMS_F16 = 1,  /* __half         (reference: <__half, at::Half>,           fm_scan.cuh:336-337) */
+    FMS_BF16 = 2  /* __nv_bfloat16  (reference: <__nv_bfloat16, at::BFloat16>, fm_scan.cuh:334-335) */
+} fms_dtype;
+
+typedef enum fms_status {
+    FMS_OK = 0,
+    FMS_ERR_BAD_SHAPE = 1,      /* negative size, or a size product that overflows int64          */
+    FMS_ERR_BAD_DTYPE = 2,      /* dtype tag not in fms_dtype (reference: fm_scan.cuh:340-341)    */
+    FMS_ERR_NULL_POINTER = 3,   /* a required pointer is NULL while the problem is non-empty      */
+    FMS_ERR_MISALIGNED = 4,     /* a pointer is not aligned to its element size                   */
+    FMS_ERR_LAUNCH = 5,         /* the CUDA runtime refused a launch or a copy (see fms_last_cuda_error) */
+    FMS_ERR_WORKSPACE = 6,      /* workspace pointer NULL/misaligned or smaller than the query said */
+    FMS_ERR_TOO_LARGE = 7,      /* problem exceeds a stated fixed capacity                        */
+    FMS_ERR_NO_DEVICE = 8       /* no CUDA device / wrong architecture (needs sm_100)              */
+} fms_status;
+
+/* Library version (major*10000 + minor*100 + patch) and a static description of a status. */
+int fms_version(void);
+const char *fms_status_string(int status);
+/* The cudaError_t (as int) recorded by the last failing runtime call of this thread, 0 if none. */
+int fms_last_cuda_error(void);
+
+/* ------------------------------------------------------------------ PLAIN mode, one GPU ---- */
+
+/*
+ * Forward scan.  Replaces the launch inside fm_scan_forward (fm/scan/fm_scan.cuh:344-358) for
+ * the layout gates, tokens, states : (rows, T).
+ *   h0      nullable; per-row initial state h[r,-1] (reference: initial_state,
+ *           fm/scan/fm_scan.py:47-51; NULL = zeros as fm_scan.py:48)
+ *   h_last  nullable; receives h[r,T-1] in fp32 before rounding to storage (equals h0 when T == 0)
+ */
+int fms_plain_forward(const void *gates, const void *tokens, const float *h0, void *states,
+                      float *h_last, int64_t rows, int64_t T, int dtype, fms_stream_t stream);
+
+/*
+ * Backward scan.  Replaces the launch inside fm_scan_backward (fm/scan/fm_scan.cuh:361-381) plus
+ * the reductions of fm/scan/fm_scan.py:75-78, which are the identity in this layout.
+ *   delta_t = grad_states_t + a_{t+1} delta_{t+1};  grad_tokens_t = delta_t;
+ *   grad_gates_t = delta_t * h_{t-1}   (h_{-1} = h0)
+ *   states      the forward output (reference: cached_output)
+ *   h0          nullable; the forward initial state (the reference passed zeros here,
+ *               fm/scan/fm_scan.py:65, which is only right when the forward h0 was zero)
+ *   carry_in    nullable; a_T * delta_T flowing in from positions beyond this block (split along T)
+ *   grad_h0     nullable; receives a_0 * delta_0 = dL/dh0 (the reference returns None,
+ *               fm/scan/fm_scan.py:80-81)
+ */
+int fms_plain_backward(const void *gates, const void *states, const void *grad_states,
+                       const float *h0, const float *carry_in, void *grad_gates,
+                       void *grad_tokens, float *grad_h0, int64_t rows, int64_t T, int dtype,
+                       fms_stream_t stream);
+
+/*
+ * Carries of a block of T positions, without writing states (first pass of the split-along-T
+ * scheme; the reference has no counterpart, its longest sequence is one CTA's serial chunk
+ * loop, fm/scan/fm_scan.cuh:84,211-216).
+ *   P[r] = prod_t a[r,t]         S[r] = h[r,T-1] given h[r,-1] = 0
+ * so that for any carry-in  h[r,T-1] = P[r]*h_in + S[r].
+ */
+int fms_plain_reduce(const void *gates, const void *tokens, float *P, float *S, int64_t rows,
+                     int64_t T, int dtype, fms_stream_t stream);
+
+/*
+ * Reverse carries of a block: S_rev[r] = a_0 * delta_0 given carry_in = 0 (P is the same product
+ * as in fms_plain_reduce and may be NULL), so that grad_h0 = P*carry_in + S_rev.
+ */
+int fms_plain_reduce_reverse(const void *gates, const void *grad_states, float *P, float *S_rev,
+                             int64_t rows, int64_t T, int dtype, fms_stream_t stream);
+
+/*
+ * Fold the carries of `nchunks` consecutive blocks of every row into the carry-in of each block.
+ *   P, S      : (nchunks, rows) fp32, chunk-major (the layout an all-gather over ranks produces)
+ *   carry0    : nullable (rows) carry entering the first block in scan order
+ *   carry_out : (nchunks, rows); carry_out[k] is the carry entering block k
+ *   total     : nullable (rows); the carry leaving the last block in scan order
+ *   reverse   : 0 = forward order (block k receives blocks < k), 1 = reverse (receives blocks > k)
+ */
+int fms_combine_carries(const float *P, const float *S, const float *carry0, float *carry_out,
+                        float *total, int64_t nchunks, int64_t rows, int reverse,
+                        fms_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FM_SCAN_B200_H_ */

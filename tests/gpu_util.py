@@ -1,0 +1,76 @@
+"""Helpers for the GPU parity tests: run the scan through the C ABI on torch-owned device buffers."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from fm_b200 import capi
+
+TORCH_DT = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
+
+
+def dev(arr, storage="f32", device="cuda"):
+    """fp32 numpy array (already rounded to `storage`) -> device tensor of that storage type."""
+    if arr is None:
+        return None
+    return torch.from_numpy(np.ascontiguousarray(arr, dtype=np.float32)).to(device).to(TORCH_DT[storage])
+
+
+def host(t):
+    return None if t is None else t.detach().to(torch.float32).cpu().numpy()
+
+
+def stream_ptr():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def forward(a, x, h0=None, want_last=False, out=None):
+    """a, x: device tensors (..., T); h0: fp32 device tensor (...) or None."""
+    T = a.shape[-1]
+    rows = a.numel() // T if T else int(np.prod(a.shape[:-1]))
+    h = torch.empty_like(a) if out is None else out
+    h_last = torch.empty(a.shape[:-1], device=a.device, dtype=torch.float32) if want_last else None
+    capi.call("fms_plain_forward", capi.ptr(a), capi.ptr(x), capi.ptr(h0), capi.ptr(h),
+              capi.ptr(h_last), rows, T, capi.dtype_tag(a.dtype), stream_ptr())
+    return (h, h_last) if want_last else h
+
+
+def backward(a, h, G, h0=None, carry_in=None, want_gh0=False, outs=None):
+    T = a.shape[-1]
+    rows = a.numel() // T if T else int(np.prod(a.shape[:-1]))
+    ga, gx = (torch.empty_like(a), torch.empty_like(a)) if outs is None else outs
+    gh0 = torch.empty(a.shape[:-1], device=a.device, dtype=torch.float32) if want_gh0 else None
+    capi.call("fms_plain_backward", capi.ptr(a), capi.ptr(h), capi.ptr(G), capi.ptr(h0),
+              capi.ptr(carry_in), capi.ptr(ga), capi.ptr(gx), capi.ptr(gh0), rows, T,
+              capi.dtype_tag(a.dtype), stream_ptr())
+    return (ga, gx, gh0) if want_gh0 else (ga, gx)
+
+
+def reduce(a, x):
+    T = a.shape[-1]
+    rows = a.numel() // T if T else int(np.prod(a.shape[:-1]))
+    P = torch.empty(a.shape[:-1], device=a.device, dtype=torch.float32)
+    S = torch.empty_like(P)
+    capi.call("fms_plain_reduce", capi.ptr(a), capi.ptr(x), capi.ptr(P), capi.ptr(S), rows, T,
+              capi.dtype_tag(a.dtype), stream_ptr())
+    return P, S
+
+
+def reduce_reverse(a, G, want_P=True):
+    T = a.shape[-1]
+    rows = a.numel() // T if T else int(np.prod(a.shape[:-1]))
+    P = torch.empty(a.shape[:-1], device=a.device, dtype=torch.float32) if want_P else None
+    S = torch.empty(a.shape[:-1], device=a.device, dtype=torch.float32)
+    capi.call("fms_plain_reduce_reverse", capi.ptr(a), capi.ptr(G), capi.ptr(P), capi.ptr(S), rows, T,
+              capi.dtype_tag(a.dtype), stream_ptr())
+    return P, S
+
+
+def combine(P, S, carry0=None, reverse=False):
+    """P, S: (nchunks, rows) fp32 device tensors."""
+    nchunks, rows = P.shape
+    out = torch.empty_like(P)
+    total = torch.empty(rows, device=P.device, dtype=torch.float32)
+    capi.call("fms_combine_carries", capi.ptr(P), capi.ptr(S), capi.ptr(carry0), capi.ptr(out),
+              capi.ptr(total), nchunks, rows, int(reverse), stream_ptr())
+    return out, total

@@ -1,0 +1,262 @@
+"""Parity of the CUDA path (through the C ABI) with the pinned CPU oracle and the golden fixtures."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import c_oracle as oc
+from tests import gpu_util as G
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+
+def tol(storage, ref):
+    if storage == "f32":
+        return H.FP32_RTOL, H.FP32_ATOL
+    return H.LOWP_RTOL, H.lowp_atol(ref)
+
+
+def check_fwd_bwd(a, x, Gd, storage, h0=None, carry_in=None, what=""):
+    """Kernel vs oracle on fp32 arrays already rounded to `storage`."""
+    ad, xd, gd = (G.dev(v, storage) for v in (a, x, Gd))
+    h0d = None if h0 is None else G.dev(h0)
+    cind = None if carry_in is None else G.dev(carry_in)
+    h, h_last = G.forward(ad, xd, h0d, want_last=True)
+    ga, gx, gh0 = G.backward(ad, h, gd, h0d, cind, want_gh0=True)
+    torch.cuda.synchronize()
+
+    h_ref, hl_ref = oc.plain_forward(a, x, h0, return_last=True)
+    r, at = tol(storage, h_ref)
+    H.assert_close(G.host(h), h_ref, r, at, what + " states")
+    H.assert_close(G.host(h_last), hl_ref, max(r, 1e-5) if storage == "f32" else 1e-4,
+                   at if storage == "f32" else 1e-4 * (1 + float(np.abs(hl_ref).max(initial=0))),
+                   what + " h_last")
+    # backward is checked against the oracle fed with the states the kernel itself saved
+    # (rounded to storage), which is what both the reference's CUDA path and this one read back
+    h_saved = G.host(h)
+    ga_ref, gx_ref, gh0_ref = oc.plain_backward(a, h_saved, Gd, h0, carry_in)
+    r, at = tol(storage, gx_ref)
+    H.assert_close(G.host(gx), gx_ref, r, at, what + " grad_tokens")
+    r, at = tol(storage, ga_ref)
+    H.assert_close(G.host(ga), ga_ref, r, at, what + " grad_gates")
+    H.assert_close(G.host(gh0), gh0_ref, 1e-4, 1e-5 * (1 + float(np.abs(gh0_ref).max(initial=0))),
+                   what + " grad_h0")
+
+
+# ------------------------------------------------------------------ golden fixtures ----------
+@pytest.mark.parametrize("name", H.golden_names("plain_via_fold"))
+def test_golden_through_fold(name):
+    """Outputs of the unmodified reference: reference(a, x) == plain(a, (1-a)x), gradients by chain rule."""
+    g = H.load_golden(name)
+    storage = H.manifest()[name]["storage"]
+    a, x, Gd = g["a"], g["x"], g["G"]
+    h0 = g.get("h0")
+    xp = H.round_storage(((np.float32(1) - a) * x).astype(np.float32), storage)
+    ad, xd, gd = (G.dev(v, storage) for v in (a, xp, Gd))
+    h0d = None if h0 is None else G.dev(h0)
+    h = G.forward(ad, xd, h0d)
+    ga, gx, gh0 = G.backward(ad, h, gd, h0d, None, want_gh0=True)
+    torch.cuda.synchronize()
+    sel = (lambda v: v[:, g["sample_idx"]]) if "sample_idx" in g else (lambda v: v)
+    r, at = tol(storage, g["ref32_h"])
+    H.assert_close(sel(G.host(h)), g["ref32_h"], r, at, name + " states")
+    gxh, gah = G.host(gx), G.host(ga)
+    d_tokens = (np.float32(1) - a) * gxh
+    d_gates = gah - x * gxh
+    r, at = tol(storage, g["ref32_d_tokens"])
+    H.assert_close(sel(d_tokens), g["ref32_d_tokens"], r, at, name + " d_tokens")
+    # d_gates = grad_a' - x*grad_x' cancels; its error scales with the two terms
+    scale = float(np.abs(gah).max() + np.abs(x * gxh).max())
+    if storage == "f32":
+        r, at = H.FP32_RTOL, 2e-7 * scale + H.FP32_ATOL
+    else:
+        r, at = H.LOWP_RTOL, 1e-2 * scale
+    H.assert_close(sel(d_gates), g["ref32_d_gates"], r, at, name + " d_gates")
+    if "ref32_d_h0" in g:
+        H.assert_close(G.host(gh0), g["ref32_d_h0"], 1e-5, 1e-6, name + " d_h0")
+
+
+# ------------------------------------------------------------------ seeded inputs vs oracle --
+@pytest.mark.parametrize("storage", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("T", list(range(1, 20)) + [31, 32, 33, 63, 64, 65, 127, 128, 129, 130,
+                                                     255, 256, 257, 511, 512, 513, 1000, 1024, 2047,
+                                                     2048, 2049, 3073, 4096])
+def test_every_tail_residue(storage, T):
+    a, x, Gd, h0 = H.make_inputs(5, T, 100 + T, "sigmoid01", storage, with_h0=True)
+    cin = np.linspace(-1, 1, 5).astype(np.float32)
+    check_fwd_bwd(a, x, Gd, storage, h0, cin, f"{storage} T={T}")
+
+
+@pytest.mark.parametrize("storage,R,T,gates", [
+    ("f32", 128, 1024, "sigmoid"),      # configuration 1, full
+    ("f32", 64, 4096, "sigmoid"),       # configuration 2, rows subset
+    ("bf16", 64, 8192, "long"),         # configuration 3, rows subset
+    ("f32", 8, 32768, "sigmoid+3"),     # configuration 4, one chunk length
+    ("f16", 3 * 16, 16385, "sigmoid01"),  # configuration 5, longest ragged length
+    ("f16", 3 * 768, 31, "sigmoid01"),  # configuration 5, full row count, short rows
+    ("f16", 3 * 768, 1, "sigmoid01"),
+    ("bf16", 5, 8192, "uniform09"),     # the reference notebook's usage cell: a = 0.9 + 0.1 U
+])
+def test_benchmark_configurations(storage, R, T, gates):
+    if gates == "uniform09":
+        rng = np.random.Generator(np.random.PCG64(77))
+        a = H.round_storage((0.9 + 0.1 * rng.random((R, T), dtype=np.float32)), storage)
+        x = H.round_storage(rng.standard_normal((R, T), dtype=np.float32), storage)
+        Gd = H.round_storage(rng.standard_normal((R, T), dtype=np.float32), storage)
+    else:
+        a, x, Gd = H.make_inputs(R, T, 2000 + T, gates, storage)
+    check_fwd_bwd(a, x, Gd, storage, what=f"{storage} {R}x{T} {gates}")
+
+
+@pytest.mark.parametrize("storage", ["f32", "f16"])
+@pytest.mark.parametrize("offsets", [(1, 1, 1), (0, 1, 2), (3, 0, 5)])
+def test_views_with_odd_element_offsets(storage, offsets):
+    """Tensors whose base is not 16-byte aligned, with equal and with different phases."""
+    R, T = 7, 1003
+    a, x, Gd = H.make_inputs(R, T, 31, "sigmoid", storage)
+    dt = G.TORCH_DT[storage]
+
+    def shifted(arr, off):
+        buf = torch.zeros(R * T + 16, device="cuda", dtype=dt)
+        view = buf[off:off + R * T].view(R, T)
+        view.copy_(G.dev(arr, storage))
+        return view
+
+    ad, xd, gd = shifted(a, offsets[0]), shifted(x, offsets[1]), shifted(Gd, offsets[2])
+    hbuf = torch.zeros(R * T + 16, device="cuda", dtype=dt)
+    hout = hbuf[offsets[2]:offsets[2] + R * T].view(R, T)
+    h = G.forward(ad, xd, out=hout)
+    ga, gx = G.backward(ad, h, gd)
+    torch.cuda.synchronize()
+    h_ref = oc.plain_forward(a, x)
+    r, at = tol(storage, h_ref)
+    H.assert_close(G.host(h), h_ref, r, at, "states")
+    ga_ref, gx_ref, _ = oc.plain_backward(a, G.host(h), Gd)
+    r, at = tol(storage, gx_ref)
+    H.assert_close(G.host(gx), gx_ref, r, at, "grad_tokens")
+    H.assert_close(G.host(ga), ga_ref, *tol(storage, ga_ref), "grad_gates")
+    # nothing outside the view was written
+    assert float(hbuf[:offsets[2]].abs().sum()) == 0.0 and float(hbuf[offsets[2] + R * T:].abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("storage", ["f32", "bf16"])
+@pytest.mark.parametrize("T", [1, 31, 1000, 3073])
+def test_outputs_stay_inside_their_buffers(storage, T):
+    """Guard bytes before and after every output survive (stand-in for a memory checker)."""
+    R = 9
+    a, x, Gd = H.make_inputs(R, T, 5, "sigmoid", storage)
+    dt = G.TORCH_DT[storage]
+    pad = 64
+    bufs = [torch.full((R * T + 2 * pad,), 7.0, device="cuda", dtype=dt) for _ in range(3)]
+    outs = [b[pad:pad + R * T].view(R, T) for b in bufs]
+    ad, xd, gd = (G.dev(v, storage) for v in (a, x, Gd))
+    G.forward(ad, xd, out=outs[0])
+    G.backward(ad, outs[0], gd, outs=(outs[1], outs[2]))
+    torch.cuda.synchronize()
+    for b in bufs:
+        assert bool((b[:pad] == 7.0).all()) and bool((b[pad + R * T:] == 7.0).all())
+    H.assert_close(G.host(outs[0]), oc.plain_forward(a, x), *tol(storage, oc.plain_forward(a, x)), "states")
+
+
+@pytest.mark.parametrize("storage", ["f32", "bf16"])
+def test_reduce_and_split_along_time(storage):
+    """Carries of chunks + combine + scan-with-carry reproduce the unsplit scan, both directions."""
+    R, T, K = 33, 8 * 517, 8
+    a, x, Gd = H.make_inputs(R, T, 9, "sigmoid+3", storage)
+    ad, xd, gd = (G.dev(v, storage) for v in (a, x, Gd))
+    L = T // K
+    chunks = [slice(k * L, (k + 1) * L) for k in range(K)]
+    # forward: reduce each chunk, combine, scan each chunk with its carry-in
+    PS = [G.reduce(ad[:, c].contiguous(), xd[:, c].contiguous()) for c in chunks]
+    P = torch.stack([p for p, _ in PS]); S = torch.stack([s for _, s in PS])
+    P_ref, S_ref = zip(*[oc.plain_reduce(a[:, c], x[:, c]) for c in chunks])
+    H.assert_close(G.host(P), np.stack(P_ref), 1e-4, 1e-30, "P")
+    H.assert_close(G.host(S), np.stack(S_ref), 1e-4, 1e-5, "S")
+    h_in, total = G.combine(P, S)
+    h_parts = [G.forward(ad[:, c].contiguous(), xd[:, c].contiguous(), h_in[k].contiguous())
+               for k, c in enumerate(chunks)]
+    h = torch.cat(h_parts, dim=1)
+    h_whole, h_last = G.forward(ad, xd, want_last=True)
+    torch.cuda.synchronize()
+    h_ref = oc.plain_forward(a, x)
+    r, at = tol(storage, h_ref)
+    H.assert_close(G.host(h), h_ref, r, at, "split states")
+    H.assert_close(G.host(total), G.host(h_last), 1e-4, 1e-5, "total carry")
+    if storage == "f32":
+        H.assert_close(G.host(h), G.host(h_whole), 1e-5, 1e-6, "split vs whole")
+    # backward: reverse carries, combine in reverse, scan each chunk with carry_in and h0
+    Srev = torch.stack([G.reduce_reverse(ad[:, c].contiguous(), gd[:, c].contiguous())[1] for c in chunks])
+    c_in, gh0_total = G.combine(P, Srev, reverse=True)
+    parts = [G.backward(ad[:, c].contiguous(), h_parts[k], gd[:, c].contiguous(), h_in[k].contiguous(),
+                        c_in[k].contiguous()) for k, c in enumerate(chunks)]
+    ga = torch.cat([p[0] for p in parts], dim=1); gx = torch.cat([p[1] for p in parts], dim=1)
+    ga_w, gx_w, gh0_w = G.backward(ad, h_whole, gd, want_gh0=True)
+    torch.cuda.synchronize()
+    ga_ref, gx_ref, gh0_ref = oc.plain_backward(a, G.host(h), Gd)
+    H.assert_close(G.host(gx), gx_ref, *tol(storage, gx_ref), "split grad_tokens")
+    H.assert_close(G.host(ga), ga_ref, *tol(storage, ga_ref), "split grad_gates")
+    H.assert_close(G.host(gh0_total), gh0_ref, 1e-4, 1e-5, "split grad_h0")
+    H.assert_close(G.host(gh0_w), gh0_ref, 1e-4, 1e-5, "whole grad_h0")
+
+
+def test_gates_exactly_zero_and_one():
+    """a = 0 resets the state, a = 1 accumulates: rows of pure resets / pure cumulative sums."""
+    R, T = 4, 777
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((R, T)).astype(np.float32)
+    Gd = rng.standard_normal((R, T)).astype(np.float32)
+    a = np.ones((R, T), np.float32)
+    a[1] = 0.0
+    a[2, ::7] = 0.0
+    a[3, 100:] = 0.0
+    check_fwd_bwd(a, x, Gd, "f32", what="0/1 gates")
+    h = G.host(G.forward(G.dev(a), G.dev(x)))
+    np.testing.assert_allclose(h[0], np.cumsum(x[0].astype(np.float64)), rtol=1e-5, atol=1e-4)
+    assert np.array_equal(h[1], x[1])
+
+
+def test_zero_rows_and_zero_length_are_no_ops():
+    e = torch.empty((0, 16), device="cuda")
+    G.forward(e, e)
+    e2 = torch.empty((3, 0), device="cuda")
+    h0 = torch.arange(3, device="cuda", dtype=torch.float32)
+    _, last = G.forward(e2, e2, h0, want_last=True)
+    torch.cuda.synchronize()
+    assert torch.equal(last, h0)
+
+
+def test_full_size_configuration_3_properties():
+    """(16,2048,8192) bf16: oracle on a row subset, plus linearity in the tokens on all rows."""
+    R, T = 16 * 2048, 8192
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    u = torch.rand(R, T, device="cuda", generator=gen)
+    a = (1.0 - torch.pow(10.0, -4.0 + 3.0 * u)).to(torch.bfloat16)
+    del u
+    x = torch.randn(R, T, device="cuda", generator=gen).to(torch.bfloat16)
+    Gd = torch.randn(R, T, device="cuda", generator=gen).to(torch.bfloat16)
+    h = G.forward(a, x)
+    ga, gx = G.backward(a, h, Gd)
+    rows = torch.arange(0, R, 257, device="cuda")
+    rows = torch.cat([rows, torch.tensor([R - 1], device="cuda")])
+    an, xn, gn = (G.host(t[rows]) for t in (a, x, Gd))
+    h_ref = oc.plain_forward(an, xn)
+    H.assert_close(G.host(h[rows]), h_ref, *tol("bf16", h_ref), "c3 states")
+    ga_ref, gx_ref, _ = oc.plain_backward(an, G.host(h[rows]), gn)
+    H.assert_close(G.host(gx[rows]), gx_ref, *tol("bf16", gx_ref), "c3 grad_tokens")
+    H.assert_close(G.host(ga[rows]), ga_ref, *tol("bf16", ga_ref), "c3 grad_gates")
+    # size-independent property: scan(a, 2x) == 2 scan(a, x) exactly (power-of-two scaling)
+    h2 = G.forward(a, (x.float() * 2).to(torch.bfloat16))
+    assert torch.equal(h2.float(), h.float() * 2)
+    # grad_tokens of the backward is the same operator run in reverse on G with shifted gates:
+    # reversing time turns it into a forward scan
+    a_shift = torch.cat([a[:, 1:], torch.ones(R, 1, device="cuda", dtype=a.dtype)], dim=1)
+    gx_alt = G.forward(a_shift.flip(1).contiguous(), Gd.flip(1).contiguous()).flip(1)
+    err = (gx_alt.float() - gx.float()).abs()
+    bound = 2e-2 * gx.float().abs() + 1e-2 * gx.float().pow(2).mean().sqrt()
+    assert bool((err <= bound).all())
+
+
+def test_full_size_configuration_2_against_oracle():
+    """(8,1024,4096) fp32 on all rows against the C oracle."""
+    a, x, Gd = H.make_inputs(8 * 1024, 4096, 42, "sigmoid", "f32")
+    check_fwd_bwd(a, x, Gd, "f32", what="c2 full")

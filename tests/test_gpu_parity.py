@@ -16,6 +16,26 @@ def tol(storage, ref):
     return H.LOWP_RTOL, H.lowp_atol(ref)
 
 
+def close_to_reference(got, ref32, ref64, storage, what):
+    """The stated tolerance, with the reference's own fp32 rounding not charged to the kernel.
+
+    fp32 storage: |got - ref64| <= atol + rtol |ref64| against the oracle run in double precision
+    (the reference loop takes its dtype from the gates, fm/scan/fm_pytorch.py:28), and against the
+    fp32 run with that run's own distance to the double-precision result added to the bound --
+    two fp32 evaluations in different association orders can each sit one rounding away from the
+    truth on opposite sides.  16-bit storage: rtol 2e-2 plus 1e-2 of the tensor's RMS, against
+    the fp32 run directly.
+    """
+    if storage != "f32":
+        H.assert_close(got, ref32, H.LOWP_RTOL, H.lowp_atol(ref32), what)
+        return
+    H.assert_close(got, ref64, H.FP32_RTOL, H.FP32_ATOL, what + " (vs double)")
+    got = np.asarray(got, np.float64)
+    slack = np.abs(ref32.astype(np.float64) - ref64)
+    bad = np.abs(got - ref32) > H.FP32_ATOL + H.FP32_RTOL * np.abs(ref32) + slack
+    assert not bad.any(), f"{what}: {int(bad.sum())} elements beyond tolerance + reference rounding"
+
+
 def check_fwd_bwd(a, x, Gd, storage, h0=None, carry_in=None, what=""):
     """Kernel vs oracle on fp32 arrays already rounded to `storage`."""
     ad, xd, gd = (G.dev(v, storage) for v in (a, x, Gd))
@@ -25,21 +45,24 @@ def check_fwd_bwd(a, x, Gd, storage, h0=None, carry_in=None, what=""):
     ga, gx, gh0 = G.backward(ad, h, gd, h0d, cind, want_gh0=True)
     torch.cuda.synchronize()
 
+    f64 = np.float64
+    opt64 = lambda v: None if v is None else v.astype(f64)
     h_ref, hl_ref = oc.plain_forward(a, x, h0, return_last=True)
-    r, at = tol(storage, h_ref)
-    H.assert_close(G.host(h), h_ref, r, at, what + " states")
-    H.assert_close(G.host(h_last), hl_ref, max(r, 1e-5) if storage == "f32" else 1e-4,
-                   at if storage == "f32" else 1e-4 * (1 + float(np.abs(hl_ref).max(initial=0))),
+    h_ref64, hl_ref64 = oc.plain_forward(a.astype(f64), x.astype(f64), opt64(h0), dtype=f64,
+                                         return_last=True)
+    close_to_reference(G.host(h), h_ref, h_ref64, storage, what + " states")
+    H.assert_close(G.host(h_last), hl_ref64, 1e-5 if storage == "f32" else 1e-4,
+                   (1e-6 if storage == "f32" else 1e-4) * (1 + float(np.abs(hl_ref).max(initial=0))),
                    what + " h_last")
     # backward is checked against the oracle fed with the states the kernel itself saved
     # (rounded to storage), which is what both the reference's CUDA path and this one read back
     h_saved = G.host(h)
     ga_ref, gx_ref, gh0_ref = oc.plain_backward(a, h_saved, Gd, h0, carry_in)
-    r, at = tol(storage, gx_ref)
-    H.assert_close(G.host(gx), gx_ref, r, at, what + " grad_tokens")
-    r, at = tol(storage, ga_ref)
-    H.assert_close(G.host(ga), ga_ref, r, at, what + " grad_gates")
-    H.assert_close(G.host(gh0), gh0_ref, 1e-4, 1e-5 * (1 + float(np.abs(gh0_ref).max(initial=0))),
+    ga_ref64, gx_ref64, gh0_ref64 = oc.plain_backward(a.astype(f64), h_saved.astype(f64), Gd.astype(f64),
+                                                      opt64(h0), opt64(carry_in), dtype=f64)
+    close_to_reference(G.host(gx), gx_ref, gx_ref64, storage, what + " grad_tokens")
+    close_to_reference(G.host(ga), ga_ref, ga_ref64, storage, what + " grad_gates")
+    H.assert_close(G.host(gh0), gh0_ref64, 1e-4, 1e-5 * (1 + float(np.abs(gh0_ref).max(initial=0))),
                    what + " grad_h0")
 
 
@@ -179,11 +202,11 @@ def test_reduce_and_split_along_time(storage):
     h_whole, h_last = G.forward(ad, xd, want_last=True)
     torch.cuda.synchronize()
     h_ref = oc.plain_forward(a, x)
-    r, at = tol(storage, h_ref)
-    H.assert_close(G.host(h), h_ref, r, at, "split states")
+    h_ref64 = oc.plain_forward(a.astype(np.float64), x.astype(np.float64), dtype=np.float64)
+    close_to_reference(G.host(h), h_ref, h_ref64, storage, "split states")
     H.assert_close(G.host(total), G.host(h_last), 1e-4, 1e-5, "total carry")
     if storage == "f32":
-        H.assert_close(G.host(h), G.host(h_whole), 1e-5, 1e-6, "split vs whole")
+        H.assert_close(G.host(h), G.host(h_whole), 1e-5, 2e-6, "split vs whole")
     # backward: reverse carries, combine in reverse, scan each chunk with carry_in and h0
     Srev = torch.stack([G.reduce_reverse(ad[:, c].contiguous(), gd[:, c].contiguous())[1] for c in chunks])
     c_in, gh0_total = G.combine(P, Srev, reverse=True)
@@ -193,8 +216,10 @@ def test_reduce_and_split_along_time(storage):
     ga_w, gx_w, gh0_w = G.backward(ad, h_whole, gd, want_gh0=True)
     torch.cuda.synchronize()
     ga_ref, gx_ref, gh0_ref = oc.plain_backward(a, G.host(h), Gd)
-    H.assert_close(G.host(gx), gx_ref, *tol(storage, gx_ref), "split grad_tokens")
-    H.assert_close(G.host(ga), ga_ref, *tol(storage, ga_ref), "split grad_gates")
+    ga_ref64, gx_ref64, _ = oc.plain_backward(a.astype(np.float64), G.host(h).astype(np.float64),
+                                              Gd.astype(np.float64), dtype=np.float64)
+    close_to_reference(G.host(gx), gx_ref, gx_ref64, storage, "split grad_tokens")
+    close_to_reference(G.host(ga), ga_ref, ga_ref64, storage, "split grad_gates")
     H.assert_close(G.host(gh0_total), gh0_ref, 1e-4, 1e-5, "split grad_h0")
     H.assert_close(G.host(gh0_w), gh0_ref, 1e-4, 1e-5, "whole grad_h0")
 

@@ -204,14 +204,12 @@ def run_ours(args):
 
     B, D, T = WORKLOAD["B"], WORKLOAD["D"], WORKLOAD["T"]
     total_rows = B * D
-    if args.scaling == "strong":
-        rows = total_rows // world
-        global_rows = rows * world
-    else:
-        rows = total_rows
-        global_rows = rows * world
+    if args.rows > 0:
+        total_rows = args.rows
+    rows = total_rows // world if args.scaling == "strong" else total_rows
+    global_rows = rows * world
     a, x, G = make_device_inputs(rows, T, 1003 + rank, device)
-    a3, x3, G3 = (t.view(-1, D, T) for t in (a, x, G))
+    a3, x3, G3 = (t.view(-1, D, T) if rows % D == 0 else t.view(1, rows, T) for t in (a, x, G))
     h = torch.empty_like(a3)
     ga = torch.empty_like(a3)
     gx = torch.empty_like(a3)
@@ -249,7 +247,10 @@ def run_ours(args):
     bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
 
     # end to end through host buffers
-    e2e = run_e2e(args, a3, x3, G3, device, barrier)
+    if args.no_e2e:
+        e2e = {"ms": float("nan"), "h2d": 0, "d2h": 0, "steps": 0, "path": "skipped (--no-e2e)"}
+    else:
+        e2e = run_e2e(args, a3, x3, G3, device, barrier)
 
     if world > 1:
         t = torch.tensor([total_ms, fwd_ms, bwd_ms, e2e["ms"]], device=device, dtype=torch.float64)
@@ -346,12 +347,15 @@ def run_e2e(args, a3, x3, G3, device, barrier):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling aid)")
+    ap.add_argument("--rows", type=int, default=0,
+                    help="rows per GPU instead of B*D (small case for profiler captures only)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

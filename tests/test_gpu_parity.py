@@ -16,7 +16,7 @@ def tol(storage, ref):
     return H.LOWP_RTOL, H.lowp_atol(ref)
 
 
-def close_to_reference(got, ref32, ref64, storage, what):
+def close_to_reference(got, ref32, ref64, storage, what, scaled=False):
     """The stated tolerance, with the reference's own fp32 rounding not charged to the kernel.
 
     fp32 storage: |got - ref64| <= atol + rtol |ref64| against the oracle run in double precision
@@ -25,18 +25,25 @@ def close_to_reference(got, ref32, ref64, storage, what):
     two fp32 evaluations in different association orders can each sit one rounding away from the
     truth on opposite sides.  16-bit storage: rtol 2e-2 plus 1e-2 of the tensor's RMS, against
     the fp32 run directly.
+
+    `scaled` is for long-memory fp32 data (a ~ 0.95, |h| up to ~14, |grad_gates| up to ~100): one
+    fp32 rounding of such a value already exceeds 1e-6, and the next element can be near zero, so
+    the absolute term is taken relative to the tensor's largest magnitude:
+    atol = 1e-6 * max(1, max|ref|).  The benchmark's fp32 configurations with sigmoid gates are
+    checked with the unscaled tolerance.
     """
     if storage != "f32":
         H.assert_close(got, ref32, H.LOWP_RTOL, H.lowp_atol(ref32), what)
         return
-    H.assert_close(got, ref64, H.FP32_RTOL, H.FP32_ATOL, what + " (vs double)")
+    atol = H.FP32_ATOL * (max(1.0, float(np.abs(ref64).max(initial=0))) if scaled else 1.0)
+    H.assert_close(got, ref64, H.FP32_RTOL, atol, what + " (vs double)")
     got = np.asarray(got, np.float64)
     slack = np.abs(ref32.astype(np.float64) - ref64)
-    bad = np.abs(got - ref32) > H.FP32_ATOL + H.FP32_RTOL * np.abs(ref32) + slack
+    bad = np.abs(got - ref32) > atol + H.FP32_RTOL * np.abs(ref32) + slack
     assert not bad.any(), f"{what}: {int(bad.sum())} elements beyond tolerance + reference rounding"
 
 
-def check_fwd_bwd(a, x, Gd, storage, h0=None, carry_in=None, what=""):
+def check_fwd_bwd(a, x, Gd, storage, h0=None, carry_in=None, what="", scaled=False):
     """Kernel vs oracle on fp32 arrays already rounded to `storage`."""
     ad, xd, gd = (G.dev(v, storage) for v in (a, x, Gd))
     h0d = None if h0 is None else G.dev(h0)
@@ -50,7 +57,7 @@ def check_fwd_bwd(a, x, Gd, storage, h0=None, carry_in=None, what=""):
     h_ref, hl_ref = oc.plain_forward(a, x, h0, return_last=True)
     h_ref64, hl_ref64 = oc.plain_forward(a.astype(f64), x.astype(f64), opt64(h0), dtype=f64,
                                          return_last=True)
-    close_to_reference(G.host(h), h_ref, h_ref64, storage, what + " states")
+    close_to_reference(G.host(h), h_ref, h_ref64, storage, what + " states", scaled)
     H.assert_close(G.host(h_last), hl_ref64, 1e-5 if storage == "f32" else 1e-4,
                    (1e-6 if storage == "f32" else 1e-4) * (1 + float(np.abs(hl_ref).max(initial=0))),
                    what + " h_last")
@@ -60,8 +67,8 @@ def check_fwd_bwd(a, x, Gd, storage, h0=None, carry_in=None, what=""):
     ga_ref, gx_ref, gh0_ref = oc.plain_backward(a, h_saved, Gd, h0, carry_in)
     ga_ref64, gx_ref64, gh0_ref64 = oc.plain_backward(a.astype(f64), h_saved.astype(f64), Gd.astype(f64),
                                                       opt64(h0), opt64(carry_in), dtype=f64)
-    close_to_reference(G.host(gx), gx_ref, gx_ref64, storage, what + " grad_tokens")
-    close_to_reference(G.host(ga), ga_ref, ga_ref64, storage, what + " grad_gates")
+    close_to_reference(G.host(gx), gx_ref, gx_ref64, storage, what + " grad_tokens", scaled)
+    close_to_reference(G.host(ga), ga_ref, ga_ref64, storage, what + " grad_gates", scaled)
     H.assert_close(G.host(gh0), gh0_ref64, 1e-4, 1e-5 * (1 + float(np.abs(gh0_ref).max(initial=0))),
                    what + " grad_h0")
 
@@ -128,7 +135,7 @@ def test_benchmark_configurations(storage, R, T, gates):
         Gd = H.round_storage(rng.standard_normal((R, T), dtype=np.float32), storage)
     else:
         a, x, Gd = H.make_inputs(R, T, 2000 + T, gates, storage)
-    check_fwd_bwd(a, x, Gd, storage, what=f"{storage} {R}x{T} {gates}")
+    check_fwd_bwd(a, x, Gd, storage, what=f"{storage} {R}x{T} {gates}", scaled=(gates == "sigmoid+3"))
 
 
 @pytest.mark.parametrize("storage", ["f32", "f16"])
@@ -203,10 +210,10 @@ def test_reduce_and_split_along_time(storage):
     torch.cuda.synchronize()
     h_ref = oc.plain_forward(a, x)
     h_ref64 = oc.plain_forward(a.astype(np.float64), x.astype(np.float64), dtype=np.float64)
-    close_to_reference(G.host(h), h_ref, h_ref64, storage, "split states")
+    close_to_reference(G.host(h), h_ref, h_ref64, storage, "split states", scaled=True)
     H.assert_close(G.host(total), G.host(h_last), 1e-4, 1e-5, "total carry")
     if storage == "f32":
-        H.assert_close(G.host(h), G.host(h_whole), 1e-5, 2e-6, "split vs whole")
+        H.assert_close(G.host(h), G.host(h_whole), 1e-5, 2e-5, "split vs whole")
     # backward: reverse carries, combine in reverse, scan each chunk with carry_in and h0
     Srev = torch.stack([G.reduce_reverse(ad[:, c].contiguous(), gd[:, c].contiguous())[1] for c in chunks])
     c_in, gh0_total = G.combine(P, Srev, reverse=True)
@@ -218,8 +225,8 @@ def test_reduce_and_split_along_time(storage):
     ga_ref, gx_ref, gh0_ref = oc.plain_backward(a, G.host(h), Gd)
     ga_ref64, gx_ref64, _ = oc.plain_backward(a.astype(np.float64), G.host(h).astype(np.float64),
                                               Gd.astype(np.float64), dtype=np.float64)
-    close_to_reference(G.host(gx), gx_ref, gx_ref64, storage, "split grad_tokens")
-    close_to_reference(G.host(ga), ga_ref, ga_ref64, storage, "split grad_gates")
+    close_to_reference(G.host(gx), gx_ref, gx_ref64, storage, "split grad_tokens", scaled=True)
+    close_to_reference(G.host(ga), ga_ref, ga_ref64, storage, "split grad_gates", scaled=True)
     H.assert_close(G.host(gh0_total), gh0_ref, 1e-4, 1e-5, "split grad_h0")
     H.assert_close(G.host(gh0_w), gh0_ref, 1e-4, 1e-5, "whole grad_h0")
 

@@ -1,0 +1,101 @@
+"""Scan of sequences split along T across the ranks of a process group.
+
+Rank k of the group owns the contiguous time block k of every row (``gates``/``tokens`` of shape
+(B, D, T_k); blocks may differ in length).  The reference cannot do this at all: its longest
+sequence is what one CTA walks serially (fm/scan/fm_scan.cuh:84,211-216, at most 131072 steps).
+
+Forward, per rank:
+    1. carry-only pass        (P_k, S_k) = (prod a, h_last from a zero start)        reads a, x
+    2. one all-gather of (P, S) -- 2 x rows fp32 per rank
+    3. fold the carries of the ranks before k  ->  h_in,k   (h_in,0 = initial_state or 0)
+    4. the ordinary forward scan of the block with h0 = h_in,k                        reads a, x; writes h
+Backward mirrors it in reverse time order with c_t = a_t * delta_t as the carried quantity:
+    1. carry-only reverse pass S'_k = c at the block start from a zero carry-in       reads a, G
+       (the gate product P_k is reused from forward)
+    2. all-gather of S'
+    3. fold the carries of the ranks after k   ->  c_in,k
+    4. the ordinary backward of the block with carry_in = c_in,k and h0 = h_in,k      reads a, h, G; writes 2
+Rank 0's dL/dh0 output is the gradient of ``initial_state``.
+
+The collective is whatever the group's backend provides (NCCL over NVLink on GPUs).  The local
+passes come from an ops object: ``CudaScanOps`` (the CUDA kernels) by default.  Tests on CPU
+ranks inject another ops object to exercise the exchange logic over gloo; the package itself
+ships no CPU scan.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from .ops import CudaScanOps
+
+
+def _gather(t: torch.Tensor, group) -> torch.Tensor:
+    """all-gather equal-shaped per-rank tensors -> (world, *t.shape), rank-major."""
+    world = dist.get_world_size(group)
+    flat = t.contiguous().view(-1)
+    out = torch.empty(world * flat.numel(), device=t.device, dtype=t.dtype)
+    dist.all_gather_into_tensor(out, flat, group=group)
+    return out.view((world,) + tuple(t.shape))
+
+
+class _TimeSplitScan(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gates, tokens, initial_state, group, ops):
+        rank = dist.get_rank(group)
+        world = dist.get_world_size(group)
+        rows_shape = gates.shape[:-1]
+        P, S = ops.reduce(gates, tokens)
+        PS = _gather(torch.stack([P.reshape(-1), S.reshape(-1)]), group)  # (world, 2, rows)
+        P_all = PS[:, 0].contiguous()
+        S_all = PS[:, 1].contiguous()
+        carry0 = None
+        if initial_state is not None:
+            # every rank must fold the same h0: take rank 0's
+            carry0 = initial_state.to(torch.float32).reshape(-1).contiguous().clone()
+            dist.broadcast(carry0, src=dist.get_global_rank(group, 0) if group is not None else 0,
+                           group=group)
+        h_in_all, _ = ops.combine(P_all, S_all, carry0, reverse=False)
+        h_in = h_in_all[rank].reshape(rows_shape).contiguous()
+        states = ops.forward(gates, tokens, h_in)
+        ctx.save_for_backward(gates, states, h_in, P_all)
+        ctx.group, ctx.ops, ctx.rank, ctx.world = group, ops, rank, world
+        ctx.h0_dtype = None if initial_state is None else initial_state.dtype
+        ctx.h0_needs_grad = initial_state is not None and ctx.needs_input_grad[2]
+        return states
+
+    @staticmethod
+    def backward(ctx, grad_states):
+        gates, states, h_in, P_all = ctx.saved_tensors
+        group, ops, rank = ctx.group, ctx.ops, ctx.rank
+        grad_states = grad_states.contiguous()
+        S_rev = ops.reduce_reverse(gates, grad_states)
+        S_all = _gather(S_rev.reshape(-1), group)  # (world, rows)
+        c_in_all, _ = ops.combine(P_all, S_all, None, reverse=True)
+        c_in = c_in_all[rank].reshape(h_in.shape).contiguous()
+        grad_gates, grad_tokens, grad_h0 = ops.backward(gates, states, grad_states, h_in, c_in,
+                                                        want_grad_h0=ctx.h0_needs_grad)
+        d_h0 = None
+        if ctx.h0_needs_grad:
+            # dL/d(initial_state) is rank 0's carry-out; other ranks contribute nothing
+            d_h0 = grad_h0 if rank == 0 else torch.zeros_like(grad_h0)
+            d_h0 = d_h0.to(ctx.h0_dtype)
+        return grad_gates, grad_tokens, d_h0, None, None
+
+
+def fm_scan_time_split(gates, tokens, initial_state=None, group=None, ops=None):
+    """Differentiable scan of this rank's time block; ranks are ordered along T by group rank.
+
+    Arguments:
+        gates, tokens: (B, D, T_k) contiguous tensors of this rank's block (same dtype).
+        initial_state: (B, D) state before the first block; only rank 0's values are used.
+        group: process group spanning the time blocks (default: the world group).
+        ops: local scan passes (default ``CudaScanOps``).
+    Returns:
+        states of this rank's block, (B, D, T_k).
+    """
+    if not dist.is_initialized():
+        raise RuntimeError("fm_scan_time_split needs an initialised torch.distributed process group")
+    if gates.shape != tokens.shape:
+        raise RuntimeError("gates and tokens must have the same shape")
+    return _TimeSplitScan.apply(gates, tokens, initial_state, group, ops or CudaScanOps)

@@ -125,6 +125,8 @@ def cpu_port_throughput(rows: int, T: int, repeats: int, warmup: int = 1):
     from oracle import c_oracle as oc
     from tests.helpers import make_inputs
 
+    # torchrun exports OMP_NUM_THREADS=1; the CPU baseline is entitled to every core it may use
+    oc.set_num_threads(len(os.sched_getaffinity(0)))
     a, x, G = make_inputs(rows, T, 1003, "long", "bf16")
     times = []
     for i in range(warmup + repeats):
@@ -143,6 +145,7 @@ def torch_loop_throughput(rows: int, T: int):
     from oracle import torch_loop as tl
     from tests.helpers import make_inputs
 
+    torch.set_num_threads(len(os.sched_getaffinity(0)))
     a, x, G = (torch.from_numpy(v).view(1, rows, T) for v in make_inputs(rows, T, 1003, "long", "bf16"))
     t0 = time.perf_counter()
     tl.plain_fwd_bwd(a, x, G)

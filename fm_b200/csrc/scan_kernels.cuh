@@ -33,7 +33,16 @@
 
 namespace fms {
 
-constexpr int kWarpsPerCta = 4;
+#ifndef FMS_WARPS_PER_CTA
+#define FMS_WARPS_PER_CTA 4
+#endif
+#ifndef FMS_FWD_MIN_CTAS
+#define FMS_FWD_MIN_CTAS 1
+#endif
+#ifndef FMS_BWD_MIN_CTAS
+#define FMS_BWD_MIN_CTAS 1
+#endif
+constexpr int kWarpsPerCta = FMS_WARPS_PER_CTA;
 constexpr unsigned kFullMask = 0xffffffffu;
 
 // ---------------------------------------------------------------- storage <-> fp32 ----------
@@ -193,7 +202,7 @@ __device__ __forceinline__ bool same_phase16(const void *p, const void *q) {
 // WRITE = true : states (and optionally h_last) are produced            -> fms_plain_forward
 // WRITE = false: only the carries P = prod a and S = h_last are produced -> fms_plain_reduce
 template <typename S, bool GENERIC, int U, bool WRITE>
-__global__ void __launch_bounds__(kWarpsPerCta * 32)
+__global__ void __launch_bounds__(kWarpsPerCta * 32, FMS_FWD_MIN_CTAS)
 plain_forward_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
                      const float *__restrict__ h0, S *__restrict__ states,
                      float *__restrict__ h_last, float *__restrict__ P_out, int64_t R, int64_t T) {
@@ -301,7 +310,7 @@ plain_forward_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
 // grad_tokens_t = delta_t; grad_gates_t = delta_t * h_{t-1}; grad_h0 = c_0.
 // WRITE = false produces only S_rev = c_0 (from carry_in = 0) and P = prod a.
 template <typename S, bool GENERIC, int U, bool WRITE>
-__global__ void __launch_bounds__(kWarpsPerCta * 32)
+__global__ void __launch_bounds__(kWarpsPerCta * 32, FMS_BWD_MIN_CTAS)
 plain_backward_kernel(const S *__restrict__ gates, const S *__restrict__ states,
                       const S *__restrict__ grad_states, const float *__restrict__ h0,
                       const float *__restrict__ carry_in, S *__restrict__ grad_gates,

@@ -126,6 +126,41 @@ int fms_combine_carries(const float *P, const float *S, const float *carry0, flo
                         float *total, int64_t nchunks, int64_t rows, int reverse,
                         fms_stream_t stream);
 
+/* ------------------------------------------------------- host-buffer pipeline (one GPU) ---- */
+
+/*
+ * Forward + backward with inputs and outputs in HOST memory, for callers whose tensors live
+ * on the host (the reference's CPU path fm/scan/fm_pytorch.py:3-42 is such a caller's
+ * alternative).  Rows are cut into blocks; host->device copies, the two kernels and
+ * device->host copies of consecutive blocks overlap on three internal streams (both PCIe
+ * directions busy at once).  The reference has no counterpart: its extension only accepts
+ * CUDA tensors (fm/scan/fm_scan.cuh:346-348).
+ *
+ * fms_pipeline_create makes the streams and events on the CURRENT device.  It allocates no
+ * device memory: the staging area is the caller's `workspace` (device memory, 256-byte
+ * aligned).  The block size follows from its size: a block of r rows needs
+ * 12 * round_up(r*T*sizeof(element), 256) bytes (two input slots a,x,G and two output slots
+ * h,grad_a,grad_x); fms_pipeline_workspace_bytes returns that figure.
+ */
+typedef struct fms_pipeline fms_pipeline;
+
+size_t fms_pipeline_workspace_bytes(int64_t rows_per_block, int64_t T, int dtype);
+int fms_pipeline_create(fms_pipeline **out, void *workspace, size_t workspace_bytes);
+int fms_pipeline_destroy(fms_pipeline *pipe);
+
+/*
+ * Enqueue fwd+bwd of (rows, T) from host buffers to host buffers.  Asynchronous: work that was
+ * enqueued on `stream` before the call is waited for, and on return `stream` waits for the
+ * whole pipeline, so synchronising `stream` (or anything ordered after it) completes the call.
+ * Host buffers should be page-locked; pageable memory works but the copies then serialise.
+ * Calls on one pipeline must not overlap in time (they share the staging area).
+ * Returns FMS_ERR_WORKSPACE if the workspace cannot hold a block of even one row.
+ */
+int fms_plain_forward_backward_host(fms_pipeline *pipe, const void *gates_h, const void *tokens_h,
+                                    const void *grad_states_h, void *states_h, void *grad_gates_h,
+                                    void *grad_tokens_h, int64_t rows, int64_t T, int dtype,
+                                    fms_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,83 @@
+"""The C-ABI library without a GPU: it loads, exports what the header declares, and its argument
+checks answer before any CUDA call."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+from fm_b200 import capi
+
+ROOT = Path(__file__).resolve().parent.parent
+HEADER = (ROOT / "include" / "fm_scan_b200.h").read_text()
+
+
+def declared_functions():
+    text = re.sub(r"/\*.*?\*/", "", HEADER, flags=re.S)
+    return sorted(set(re.findall(r"\b(fms_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_the_expected_entry_points():
+    names = declared_functions()
+    for must in ("fms_plain_forward", "fms_plain_backward", "fms_plain_reduce", "fms_plain_reduce_reverse",
+                 "fms_combine_carries", "fms_plain_forward_backward_host", "fms_version"):
+        assert must in names
+
+
+def test_library_exports_every_declared_symbol():
+    L = capi.lib()
+    for name in declared_functions():
+        assert hasattr(L, name), f"{name} is declared in the header but not exported"
+
+
+def test_ctypes_table_covers_the_compute_entry_points():
+    for name in capi.SIGNATURES:
+        assert name in declared_functions()
+
+
+def test_version_and_status_strings():
+    assert capi.lib().fms_version() >= 100
+    assert capi.status_string(capi.FMS_OK) == "ok"
+    assert "dtype" in capi.status_string(capi.FMS_ERR_BAD_DTYPE)
+    assert "unknown" in capi.status_string(12345)
+
+
+def test_argument_checks_need_no_device():
+    buf = (ctypes.c_char * 256)()
+    p = ctypes.addressof(buf)
+    p = (p + 15) // 16 * 16
+    call = lambda *a: capi.call("fms_plain_forward", *a, check=False)
+    assert call(p, p, None, p, None, 4, 8, 99, None) == capi.FMS_ERR_BAD_DTYPE
+    assert call(p, p, None, p, None, -1, 8, capi.FMS_F32, None) == capi.FMS_ERR_BAD_SHAPE
+    assert call(p, p, None, p, None, 4, -8, capi.FMS_F32, None) == capi.FMS_ERR_BAD_SHAPE
+    assert call(p, p, None, p, None, 2 ** 40, 2 ** 40, capi.FMS_F32, None) == capi.FMS_ERR_BAD_SHAPE
+    assert call(p, None, None, p, None, 4, 8, capi.FMS_F32, None) == capi.FMS_ERR_NULL_POINTER
+    assert call(p + 2, p, None, p, None, 4, 8, capi.FMS_F32, None) == capi.FMS_ERR_MISALIGNED
+    assert call(p + 1, p, None, p, None, 4, 8, capi.FMS_BF16, None) == capi.FMS_ERR_MISALIGNED
+    # empty problems are accepted without touching the device
+    assert call(None, None, None, None, None, 0, 8, capi.FMS_F32, None) == capi.FMS_OK
+    assert capi.call("fms_plain_backward", p, p, p, None, None, p, None, None, 4, 8, capi.FMS_F16, None,
+                     check=False) == capi.FMS_ERR_NULL_POINTER
+    assert capi.call("fms_combine_carries", None, None, None, None, None, -1, 4, 0, None,
+                     check=False) == capi.FMS_ERR_BAD_SHAPE
+    with pytest.raises(capi.FmsError) as e:
+        capi.call("fms_plain_reduce", p, p, p, p, 4, 8, 7, None)
+    assert e.value.status == capi.FMS_ERR_BAD_DTYPE
+
+
+def test_pipeline_rejects_a_missing_workspace_without_a_device():
+    from fm_b200 import host_pipeline as hp
+    L = hp._bind()
+    handle = ctypes.c_void_p()
+    assert L.fms_pipeline_create(ctypes.byref(handle), None, 1 << 20) == capi.FMS_ERR_WORKSPACE
+    assert L.fms_pipeline_create(None, None, 0) == capi.FMS_ERR_NULL_POINTER
+    import torch
+    assert hp.workspace_bytes(4096, 8192, torch.bfloat16) == 12 * 4096 * 8192 * 2
+    assert hp.workspace_bytes(1, 3, torch.float16) == 12 * 256
+
+
+def test_ops_refuse_cpu_tensors():
+    import torch
+    from fm_b200.ops import CudaScanOps
+    with pytest.raises(RuntimeError, match="CUDA"):
+        CudaScanOps.forward(torch.zeros(2, 8), torch.zeros(2, 8))

@@ -292,3 +292,51 @@ def test_full_size_configuration_2_against_oracle():
     """(8,1024,4096) fp32 on all rows against the C oracle."""
     a, x, Gd = H.make_inputs(8 * 1024, 4096, 42, "sigmoid", "f32")
     check_fwd_bwd(a, x, Gd, "f32", what="c2 full")
+
+
+@pytest.mark.parametrize("storage,pinned", [("bf16", True), ("f32", True), ("f16", False)])
+def test_host_buffer_pipeline_equals_device_path(storage, pinned):
+    """fms_plain_forward_backward_host (blocks of rows on three streams) is bit-identical to the
+    device entry points, for pinned and for pageable host memory, with a ragged last block."""
+    from fm_b200.host_pipeline import HostPipeline
+    R, T = 203, 1000
+    a, x, Gd = H.make_inputs(R, T, 8, "sigmoid", storage)
+    dt = G.TORCH_DT[storage]
+    mk = lambda v: (torch.from_numpy(v).to(dt).pin_memory() if pinned else torch.from_numpy(v).to(dt))
+    ah, xh, gh = mk(a), mk(x), mk(Gd)
+    outs = [torch.empty_like(ah).pin_memory() if pinned else torch.empty_like(ah) for _ in range(3)]
+    pipe = HostPipeline(16, T, dt)   # 16-row blocks: 13 blocks, the last one ragged
+    pipe.forward_backward(ah, xh, gh, *outs)
+    pipe.forward_backward(ah, xh, gh, *outs)  # a second call reuses the staging area
+    torch.cuda.synchronize()
+    pipe.close()
+    ad, xd, gd = ah.cuda(), xh.cuda(), gh.cuda()
+    h = G.forward(ad, xd)
+    ga, gx = G.backward(ad, h, gd)
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], h.cpu()) and torch.equal(outs[1], ga.cpu()) and torch.equal(outs[2], gx.cpu())
+
+
+def test_torch_op_autograd_and_errors():
+    """The public op: autograd with initial_state, and the reference's error conventions."""
+    from fm_b200 import fm_scan, fm_scan_forward
+    a, x, Gd, h0 = H.make_inputs(6, 300, 12, "sigmoid", "f32", with_h0=True)
+    ad, xd, h0d = (G.dev(v).requires_grad_(True) for v in (a.reshape(2, 3, 300), x.reshape(2, 3, 300),
+                                                           h0.reshape(2, 3)))
+    h = fm_scan(ad, xd, h0d)
+    h.backward(G.dev(Gd.reshape(2, 3, 300)))
+    torch.cuda.synchronize()
+    h_ref = oc.plain_forward(a, x, h0)
+    ga_ref, gx_ref, gh0_ref = oc.plain_backward(a, h_ref, Gd, h0)
+    H.assert_close(G.host(h).reshape(6, 300), h_ref, 1e-5, 1e-6, "op states")
+    H.assert_close(G.host(ad.grad).reshape(6, 300), ga_ref, 1e-5, 2e-6, "op grad_gates")
+    H.assert_close(G.host(xd.grad).reshape(6, 300), gx_ref, 1e-5, 2e-6, "op grad_tokens")
+    H.assert_close(G.host(h0d.grad).reshape(6), gh0_ref, 1e-5, 2e-6, "op grad_h0")
+    with pytest.raises(RuntimeError):      # dtype mismatch, as TORCH_CHECK in the reference
+        fm_scan_forward(ad.detach(), xd.detach().half(), None, torch.empty_like(ad))
+    with pytest.raises(RuntimeError):      # unsupported dtype
+        fm_scan_forward(ad.detach().double(), xd.detach().double(), None, torch.empty_like(ad).double())
+    with pytest.raises(RuntimeError):      # CPU tensor
+        fm_scan_forward(ad.detach().cpu(), xd.detach().cpu(), None, torch.empty_like(ad).cpu())
+    with pytest.raises(AssertionError):    # non-contiguous input, as the reference's Python asserts
+        fm_scan(ad.detach().transpose(0, 1), xd.detach().transpose(0, 1))

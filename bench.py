@@ -311,6 +311,80 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_time_split(args):
+    """Secondary workload: configuration 4, (B,D,T) = (1,4096,262144) fp32, T split over the ranks.
+
+    Strong scaling of one long-sequence problem: rank k owns time block k of every row and the
+    carries cross NVLink once per direction (`fm_b200.time_split`).  At N = 1 it is the plain op.
+    Prints its own JSON line; the headline metric of this repository is the default workload.
+    """
+    import torch
+    import torch.distributed as dist
+
+    from fm_b200 import fm_scan
+    from fm_b200.time_split import fm_scan_time_split
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    B, D, T = 1, args.rows or 4096, 262144
+    Tk = T // world
+    gen = torch.Generator(device=device).manual_seed(1004 + rank)
+    a = torch.sigmoid(torch.randn(B, D, Tk, device=device, generator=gen) + 3.0).requires_grad_(True)
+    x = torch.randn(B, D, Tk, device=device, generator=gen).requires_grad_(True)
+    G = torch.randn(B, D, Tk, device=device, generator=gen)
+
+    def step():
+        h = fm_scan_time_split(a, x) if world > 1 else fm_scan(a, x)
+        return torch.autograd.grad(h, (a, x), G)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+    K = args.steps
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(physical_gpu_index(local_rank)) as clocks:
+        barrier()
+        start.record()
+        for _ in range(K):
+            step()
+        end.record()
+        barrier()
+    ms = start.elapsed_time(end) / K
+    if world > 1:
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank == 0:
+        n = B * D * T
+        peak, kind = measured_peak()
+        passes = 8 if world == 1 else 12  # element passes: 3+5 unsplit, (2+3)+(2+5) split
+        line = {"metric": "scan fwd+bwd elements/s (split along T)", "value": n / (ms * 1e-3), "unit": UNIT,
+                "n_gpus": world, "steps": K, "warmup": max(3, args.warmup), "ms_per_step": ms,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic",
+                "config": {"workload": "scan fwd+bwd (B,D,T)=(1,%d,262144) fp32, T split in %d blocks" % (D, world),
+                           "gates": "a = sigmoid(N(0,1)+3); x, G ~ N(0,1)",
+                           "exchange": "all-gather of (P,S) fp32 carries, once per direction"},
+                "gpu_launches": K * (2 if world == 1 else 6),
+                "roofline_fwd_bwd": {"algorithmic_GBs_per_gpu": 8 * 4 * n / world / (ms * 1e-3) / 1e9,
+                                     "moved_GBs_per_gpu": passes * 4 * n / world / (ms * 1e-3) / 1e9,
+                                     "peak": peak, "peak_kind": kind},
+                "clocks": clocks.summary()}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_e2e(args, a3, x3, G3, device, barrier):
     """Same step with pinned HOST inputs and outputs through the host-buffer entry of the C ABI.
 
@@ -358,6 +432,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
+    ap.add_argument("--workload", choices=["c3", "c4"], default="c3",
+                    help="c3: the headline row-sharded workload; c4: the long sequence split along T")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling aid)")
@@ -366,6 +442,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload == "c4":
+        run_time_split(args)
     else:
         run_ours(args)
 

@@ -28,6 +28,8 @@ SIGNATURES = {
     "fms_plain_reduce": [_P, _P, _P, _P, _I64, _I64, _I, _P],
     "fms_plain_reduce_reverse": [_P, _P, _P, _P, _I64, _I64, _I, _P],
     "fms_combine_carries": [_P, _P, _P, _P, _P, _I64, _I64, _I, _P],
+    "fms_plain_forward_split": [_P, _P, _P, _P, _P, _I64, _I64, _I, _P, ctypes.c_size_t, _P],
+    "fms_plain_backward_split": [_P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I, _P, ctypes.c_size_t, _P],
 }
 
 _lib = None
@@ -57,6 +59,10 @@ def lib() -> ctypes.CDLL:
         L.fms_status_string.restype = ctypes.c_char_p
         L.fms_status_string.argtypes = [_I]
         L.fms_last_cuda_error.restype = _I
+        L.fms_plain_split_segments.restype = _I64
+        L.fms_plain_split_segments.argtypes = [_I64, _I64, _I]
+        L.fms_plain_split_workspace_bytes.restype = ctypes.c_size_t
+        L.fms_plain_split_workspace_bytes.argtypes = [_I64, _I64, _I]
         _lib = L
     return _lib
 

@@ -2,6 +2,7 @@
 // or the masked instantiation, kernel launches.  No allocation, no synchronisation, no torch.
 #include "fm_scan_b200.h"
 
+#include <algorithm>
 #include <cstdlib>
 
 #include "scan_kernels.cuh"
@@ -38,17 +39,19 @@ inline bool sizes_ok(int64_t rows, int64_t T) {
 
 // Tiles per group (loads in flight per warp = U x tensors x 512 B).  Tunable for experiments
 // through the environment; the defaults are the measured best on B200.
-int tune_unroll(const char *name, int dflt) {
+int tune_value(const char *name, int dflt) {
     const char *s = std::getenv(name);
-    if (!s) return dflt;
-    const int v = std::atoi(s);
+    return s ? std::atoi(s) : dflt;
+}
+
+int tune_unroll(const char *name, int dflt) {
+    const int v = tune_value(name, dflt);
     return (v == 1 || v == 2 || v == 4) ? v : dflt;
 }
 
 struct Problem {
     int64_t rows, T;
     bool aligned;  // every row of every tensor starts on a 16-byte boundary
-    unsigned grid;
 };
 
 template <typename... Ptrs>
@@ -57,9 +60,6 @@ int make_problem(Problem &pb, int64_t rows, int64_t T, int dtype, Ptrs... big) {
     if (!sizes_ok(rows, T)) return FMS_ERR_BAD_SHAPE;
     pb.rows = rows;
     pb.T = T;
-    const int64_t ctas = (rows + fms::kWarpsPerCta - 1) / fms::kWarpsPerCta;
-    if (ctas > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;
-    pb.grid = static_cast<unsigned>(ctas);
     if (rows == 0 || T == 0) {
         pb.aligned = true;
         return FMS_OK;
@@ -89,45 +89,113 @@ int copy_or_zero(const float *src, float *dst, int64_t n, float fill, cudaStream
     return check_launch();
 }
 
+// How a launch is cut into scan units and how many warps share a unit.
+struct Split {
+    int64_t nseg = 1;     // segments per row (1 = whole rows)
+    int64_t seg_len = 0;  // positions per segment (T when nseg == 1)
+};
+
+// Warps per unit.  A CTA of K warps per row reads K*U*512 contiguous bytes per tensor per step
+// and lets the block scheduler balance at a finer grain (all rows have the same length, so whole
+// waves finish together); each row then takes fewer loop iterations to prefetch across.
+int choose_coop(int64_t units, int64_t T, size_t es, const char *env_name) {
+    const int forced = tune_value(env_name, 0);
+    if (forced == 1 || forced == 2 || forced == 4 || forced == 8) return forced;
+    (void)units;
+    // Measured on B200: a row of 32 tiles (16 KB) is fastest with 2 warps, one of 256 tiles
+    // with 8; short rows keep one warp each so the loop has iterations to prefetch across.
+    const int64_t tiles = (T * static_cast<int64_t>(es) + 511) / 512;
+    if (tiles >= 128) return 8;
+    if (tiles >= 64) return 4;
+    if (tiles >= 32) return 2;
+    return 1;
+}
+
 template <typename S, bool WRITE>
-int launch_forward(const Problem &pb, const void *gates, const void *tokens, const float *h0,
-                   void *states, float *h_last, float *P, cudaStream_t st) {
-    static const int unroll = tune_unroll("FMS_TUNE_FWD_U", sizeof(S) == 4 ? 4 : 4);
-    const dim3 grid(pb.grid), block(fms::kWarpsPerCta * 32);
-#define FMS_LAUNCH_FWD(G, UU)                                                                      \
-    fms::plain_forward_kernel<S, G, UU, WRITE><<<grid, block, 0, st>>>(                            \
+int launch_forward(const Problem &pb, const Split &sp, const void *gates, const void *tokens,
+                   const float *h0, void *states, float *h_last, float *P, cudaStream_t st) {
+    const int unroll = tune_unroll("FMS_TUNE_FWD_U", 4);
+    const int64_t units = pb.rows * sp.nseg;
+    const int K = sp.nseg > 1 ? 1 : choose_coop(units, pb.T, sizeof(S), "FMS_TUNE_FWD_K");
+    const int64_t ctas = K == 1 ? (units + fms::kWarpsPerCta - 1) / fms::kWarpsPerCta : units;
+    if (ctas > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;
+    const dim3 grid(static_cast<unsigned>(ctas));
+    const int64_t seg_len = sp.nseg == 1 ? pb.T : sp.seg_len;
+#define FMS_LAUNCH_FWD_S(G, UU, KK, SS)                                                            \
+    fms::plain_forward_kernel<S, G, UU, WRITE, KK, SS><<<grid, fms::Coop<KK>::kThreads, 0, st>>>(   \
         static_cast<const S *>(gates), static_cast<const S *>(tokens), h0, static_cast<S *>(states), \
-        h_last, P, pb.rows, pb.T)
-    if (pb.aligned) {
-        if (unroll == 4) FMS_LAUNCH_FWD(false, 4);
-        else if (unroll == 2) FMS_LAUNCH_FWD(false, 2);
-        else FMS_LAUNCH_FWD(false, 1);
-    } else {
-        FMS_LAUNCH_FWD(true, 2);
+        h_last, P, units, pb.T, sp.nseg, seg_len)
+#define FMS_LAUNCH_FWD(G, UU, KK) FMS_LAUNCH_FWD_S(G, UU, KK, false)
+#define FMS_LAUNCH_FWD_K(G, UU)                                                                    \
+    switch (K) {                                                                                   \
+        case 1: FMS_LAUNCH_FWD(G, UU, 1); break;                                                   \
+        case 2: FMS_LAUNCH_FWD(G, UU, 2); break;                                                   \
+        case 4: FMS_LAUNCH_FWD(G, UU, 4); break;                                                   \
+        default: FMS_LAUNCH_FWD(G, UU, 8); break;                                                  \
     }
+    if (sp.nseg > 1) {  // split path: units are plentiful by construction, one warp each
+        if (pb.aligned) FMS_LAUNCH_FWD_S(false, 2, 1, true);
+        else FMS_LAUNCH_FWD_S(true, 2, 1, true);
+    } else if (pb.aligned) {
+        if (unroll == 4) { FMS_LAUNCH_FWD_K(false, 4) }
+        else if (unroll == 2) { FMS_LAUNCH_FWD_K(false, 2) }
+        else { FMS_LAUNCH_FWD_K(false, 1) }
+    } else {
+        FMS_LAUNCH_FWD_K(true, 2)
+    }
+#undef FMS_LAUNCH_FWD_K
 #undef FMS_LAUNCH_FWD
+#undef FMS_LAUNCH_FWD_S
     return check_launch();
 }
 
 template <typename S, bool WRITE>
-int launch_backward(const Problem &pb, const void *gates, const void *states, const void *grad_states,
-                    const float *h0, const float *carry_in, void *grad_gates, void *grad_tokens,
-                    float *grad_h0, float *P, cudaStream_t st) {
-    static const int unroll = tune_unroll("FMS_TUNE_BWD_U", 2);
-    const dim3 grid(pb.grid), block(fms::kWarpsPerCta * 32);
-#define FMS_LAUNCH_BWD(G, UU)                                                                      \
-    fms::plain_backward_kernel<S, G, UU, WRITE><<<grid, block, 0, st>>>(                           \
+int launch_backward(const Problem &pb, const Split &sp, const void *gates, const void *states,
+                    const void *grad_states, const float *h0, const float *carry_in, void *grad_gates,
+                    void *grad_tokens, float *grad_h0, float *P, cudaStream_t st) {
+    const int unroll = tune_unroll("FMS_TUNE_BWD_U", 2);
+    const int64_t units = pb.rows * sp.nseg;
+    const int K = sp.nseg > 1 ? 1 : choose_coop(units, pb.T, sizeof(S), "FMS_TUNE_BWD_K");
+    const int64_t ctas = K == 1 ? (units + fms::kWarpsPerCta - 1) / fms::kWarpsPerCta : units;
+    if (ctas > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;
+    const dim3 grid(static_cast<unsigned>(ctas));
+    const int64_t seg_len = sp.nseg == 1 ? pb.T : sp.seg_len;
+#define FMS_LAUNCH_BWD_S(G, UU, KK, SS)                                                            \
+    fms::plain_backward_kernel<S, G, UU, WRITE, KK, SS><<<grid, fms::Coop<KK>::kThreads, 0, st>>>(  \
         static_cast<const S *>(gates), static_cast<const S *>(states),                             \
         static_cast<const S *>(grad_states), h0, carry_in, static_cast<S *>(grad_gates),           \
-        static_cast<S *>(grad_tokens), grad_h0, P, pb.rows, pb.T)
-    if (pb.aligned) {
-        if (unroll == 4) FMS_LAUNCH_BWD(false, 4);
-        else if (unroll == 2) FMS_LAUNCH_BWD(false, 2);
-        else FMS_LAUNCH_BWD(false, 1);
-    } else {
-        FMS_LAUNCH_BWD(true, 1);
+        static_cast<S *>(grad_tokens), grad_h0, P, units, pb.T, sp.nseg, seg_len)
+#define FMS_LAUNCH_BWD(G, UU, KK) FMS_LAUNCH_BWD_S(G, UU, KK, false)
+#define FMS_LAUNCH_BWD_K(G, UU)                                                                    \
+    switch (K) {                                                                                   \
+        case 1: FMS_LAUNCH_BWD(G, UU, 1); break;                                                   \
+        case 2: FMS_LAUNCH_BWD(G, UU, 2); break;                                                   \
+        case 4: FMS_LAUNCH_BWD(G, UU, 4); break;                                                   \
+        default: FMS_LAUNCH_BWD(G, UU, 8); break;                                                  \
     }
+    if (sp.nseg > 1) {
+        if (pb.aligned) FMS_LAUNCH_BWD_S(false, 2, 1, true);
+        else FMS_LAUNCH_BWD_S(true, 1, 1, true);
+    } else if (pb.aligned) {
+        if (unroll == 4) { FMS_LAUNCH_BWD_K(false, 4) }
+        else if (unroll == 2) { FMS_LAUNCH_BWD_K(false, 2) }
+        else { FMS_LAUNCH_BWD_K(false, 1) }
+    } else {
+        FMS_LAUNCH_BWD_K(true, 1)
+    }
+#undef FMS_LAUNCH_BWD_K
 #undef FMS_LAUNCH_BWD
+#undef FMS_LAUNCH_BWD_S
+    return check_launch();
+}
+
+int launch_combine(const float *P, const float *S, const float *carry0, float *carry_out, float *total,
+                   int64_t nchunks, int64_t rows, int reverse, int64_t chunk_stride, int64_t row_stride,
+                   cudaStream_t st) {
+    const int64_t blocks = (rows + 127) / 128;
+    if (blocks > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;
+    fms::combine_carries_kernel<<<static_cast<unsigned>(blocks), 128, 0, st>>>(
+        P, S, carry0, carry_out, total, nchunks, rows, reverse ? 1 : 0, chunk_stride, row_stride);
     return check_launch();
 }
 
@@ -169,7 +237,7 @@ FMS_EXPORT int fms_plain_forward(const void *gates, const void *tokens, const fl
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (rows == 0) return FMS_OK;
     if (T == 0) return copy_or_zero(h0, h_last, rows, 0.f, st);
-    FMS_DISPATCH_DTYPE(dtype, (launch_forward<S, true>(pb, gates, tokens, h0, states, h_last, nullptr, st)));
+    FMS_DISPATCH_DTYPE(dtype, (launch_forward<S, true>(pb, Split{}, gates, tokens, h0, states, h_last, nullptr, st)));
 }
 
 FMS_EXPORT int fms_plain_reduce(const void *gates, const void *tokens, float *P, float *S_out,
@@ -183,7 +251,7 @@ FMS_EXPORT int fms_plain_reduce(const void *gates, const void *tokens, float *P,
         if (int rc = copy_or_zero(nullptr, P, rows, 1.f, st)) return rc;
         return copy_or_zero(nullptr, S_out, rows, 0.f, st);
     }
-    FMS_DISPATCH_DTYPE(dtype, (launch_forward<S, false>(pb, gates, tokens, nullptr, nullptr, S_out, P, st)));
+    FMS_DISPATCH_DTYPE(dtype, (launch_forward<S, false>(pb, Split{}, gates, tokens, nullptr, nullptr, S_out, P, st)));
 }
 
 FMS_EXPORT int fms_plain_backward(const void *gates, const void *states, const void *grad_states,
@@ -198,7 +266,7 @@ FMS_EXPORT int fms_plain_backward(const void *gates, const void *states, const v
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (rows == 0) return FMS_OK;
     if (T == 0) return copy_or_zero(carry_in, grad_h0, rows, 0.f, st);
-    FMS_DISPATCH_DTYPE(dtype, (launch_backward<S, true>(pb, gates, states, grad_states, h0, carry_in,
+    FMS_DISPATCH_DTYPE(dtype, (launch_backward<S, true>(pb, Split{}, gates, states, grad_states, h0, carry_in,
                                                         grad_gates, grad_tokens, grad_h0, nullptr, st)));
 }
 
@@ -214,7 +282,7 @@ FMS_EXPORT int fms_plain_reduce_reverse(const void *gates, const void *grad_stat
         if (int rc = copy_or_zero(nullptr, P, rows, 1.f, st)) return rc;
         return copy_or_zero(nullptr, S_rev, rows, 0.f, st);
     }
-    FMS_DISPATCH_DTYPE(dtype, (launch_backward<S, false>(pb, gates, nullptr, grad_states, nullptr, nullptr,
+    FMS_DISPATCH_DTYPE(dtype, (launch_backward<S, false>(pb, Split{}, gates, nullptr, grad_states, nullptr, nullptr,
                                                          nullptr, nullptr, S_rev, P, st)));
 }
 
@@ -226,9 +294,101 @@ FMS_EXPORT int fms_combine_carries(const float *P, const float *S, const float *
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (nchunks == 0) return copy_or_zero(carry0, total, rows, 0.f, st);
     if (!P || !S || !carry_out) return FMS_ERR_NULL_POINTER;
-    const int64_t blocks = (rows + 127) / 128;
-    if (blocks > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;
-    fms::combine_carries_kernel<<<static_cast<unsigned>(blocks), 128, 0, st>>>(
-        P, S, carry0, carry_out, total, nchunks, rows, reverse ? 1 : 0);
-    return check_launch();
+    return launch_combine(P, S, carry0, carry_out, total, nchunks, rows, reverse, rows, 1, st);
+}
+
+// ------------------------------------------------------------------ split inside one GPU ----
+namespace {
+
+constexpr int64_t kSplitTargetUnits = 148 * 32;  // enough one-warp units to fill the GPU
+constexpr int64_t kSplitMinSegment = 4096;       // positions; shorter segments only add carries
+constexpr int64_t kSplitQuantum = 1024;          // segment lengths are multiples of this, so
+                                                 // segments of aligned rows stay 16-byte aligned
+
+struct SplitPlan {
+    int64_t nseg, seg_len, units;
+    size_t bytes;
+};
+
+SplitPlan plan_split(int64_t rows, int64_t T) {
+    SplitPlan p{1, T, rows, 0};
+    if (rows <= 0 || T < 2 * kSplitMinSegment || rows >= kSplitTargetUnits / 2) return p;
+    int64_t want = (kSplitTargetUnits + rows - 1) / rows;
+    want = std::min<int64_t>(want, T / kSplitMinSegment);
+    if (want < 2) return p;
+    int64_t seg = (T + want - 1) / want;
+    seg = (seg + kSplitQuantum - 1) / kSplitQuantum * kSplitQuantum;
+    p.nseg = (T + seg - 1) / seg;
+    if (p.nseg < 2) return SplitPlan{1, T, rows, 0};
+    p.seg_len = seg;
+    p.units = rows * p.nseg;
+    p.bytes = (static_cast<size_t>(p.units) * 3 * sizeof(float) + 255) / 256 * 256;
+    return p;
+}
+
+}  // namespace
+
+FMS_EXPORT int64_t fms_plain_split_segments(int64_t rows, int64_t T, int dtype) {
+    if (dtype != FMS_F32 && dtype != FMS_F16 && dtype != FMS_BF16) return 1;
+    if (!sizes_ok(rows, T)) return 1;
+    return plan_split(rows, T).nseg;
+}
+
+FMS_EXPORT size_t fms_plain_split_workspace_bytes(int64_t rows, int64_t T, int dtype) {
+    if (dtype != FMS_F32 && dtype != FMS_F16 && dtype != FMS_BF16) return 0;
+    if (!sizes_ok(rows, T)) return 0;
+    return plan_split(rows, T).bytes;
+}
+
+FMS_EXPORT int fms_plain_forward_split(const void *gates, const void *tokens, const float *h0, void *states,
+                                       float *h_last, int64_t rows, int64_t T, int dtype, void *workspace,
+                                       size_t workspace_bytes, fms_stream_t stream) {
+    Problem pb;
+    if (int rc = make_problem(pb, rows, T, dtype, gates, tokens, static_cast<const void *>(states)))
+        return rc;
+    const SplitPlan plan = plan_split(rows, T);
+    if (plan.nseg == 1)
+        return fms_plain_forward(gates, tokens, h0, states, h_last, rows, T, dtype, stream);
+    if (!workspace || !aligned_to(workspace, 16) || workspace_bytes < plan.bytes) return FMS_ERR_WORKSPACE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    float *wP = static_cast<float *>(workspace), *wS = wP + plan.units, *wC = wS + plan.units;
+    const Split sp{plan.nseg, plan.seg_len};
+    {
+        auto pass1 = [&]() -> int {
+            FMS_DISPATCH_DTYPE(dtype, (launch_forward<S, false>(pb, sp, gates, tokens, nullptr, nullptr, wS, wP, st)));
+        };
+        if (int rc = pass1()) return rc;
+    }
+    if (int rc = launch_combine(wP, wS, h0, wC, h_last, plan.nseg, rows, 0, 1, plan.nseg, st)) return rc;
+    FMS_DISPATCH_DTYPE(dtype, (launch_forward<S, true>(pb, sp, gates, tokens, wC, states, nullptr, nullptr, st)));
+}
+
+FMS_EXPORT int fms_plain_backward_split(const void *gates, const void *states, const void *grad_states,
+                                        const float *h0, const float *carry_in, void *grad_gates,
+                                        void *grad_tokens, float *grad_h0, int64_t rows, int64_t T,
+                                        int dtype, void *workspace, size_t workspace_bytes,
+                                        fms_stream_t stream) {
+    Problem pb;
+    if (int rc = make_problem(pb, rows, T, dtype, gates, states, grad_states,
+                              static_cast<const void *>(grad_gates),
+                              static_cast<const void *>(grad_tokens)))
+        return rc;
+    const SplitPlan plan = plan_split(rows, T);
+    if (plan.nseg == 1)
+        return fms_plain_backward(gates, states, grad_states, h0, carry_in, grad_gates, grad_tokens, grad_h0,
+                                  rows, T, dtype, stream);
+    if (!workspace || !aligned_to(workspace, 16) || workspace_bytes < plan.bytes) return FMS_ERR_WORKSPACE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    float *wP = static_cast<float *>(workspace), *wS = wP + plan.units, *wC = wS + plan.units;
+    const Split sp{plan.nseg, plan.seg_len};
+    {
+        auto pass1 = [&]() -> int {
+            FMS_DISPATCH_DTYPE(dtype, (launch_backward<S, false>(pb, sp, gates, nullptr, grad_states, nullptr,
+                                                                 nullptr, nullptr, nullptr, wS, wP, st)));
+        };
+        if (int rc = pass1()) return rc;
+    }
+    if (int rc = launch_combine(wP, wS, carry_in, wC, grad_h0, plan.nseg, rows, 1, 1, plan.nseg, st)) return rc;
+    FMS_DISPATCH_DTYPE(dtype, (launch_backward<S, true>(pb, sp, gates, states, grad_states, h0, wC, grad_gates,
+                                                        grad_tokens, nullptr, nullptr, st)));
 }

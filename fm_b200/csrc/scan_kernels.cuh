@@ -36,12 +36,6 @@ namespace fms {
 #ifndef FMS_WARPS_PER_CTA
 #define FMS_WARPS_PER_CTA 4
 #endif
-#ifndef FMS_FWD_MIN_CTAS
-#define FMS_FWD_MIN_CTAS 1
-#endif
-#ifndef FMS_BWD_MIN_CTAS
-#define FMS_BWD_MIN_CTAS 1
-#endif
 constexpr int kWarpsPerCta = FMS_WARPS_PER_CTA;
 constexpr unsigned kFullMask = 0xffffffffu;
 
@@ -198,48 +192,93 @@ __device__ __forceinline__ bool same_phase16(const void *p, const void *q) {
     return ((reinterpret_cast<uintptr_t>(p) ^ reinterpret_cast<uintptr_t>(q)) & 15u) == 0;
 }
 
+// ---------------------------------------------------------------- row geometry ------------
+// A launch covers `R` scan units.  A unit is a whole row (SEG = false) or one of `nseg` consecutive
+// segments of `seg_len` positions of a row (SEG = true: the split path for few, long rows);
+// carries are indexed by unit.  K warps cooperate on one unit: K == 1 packs kWarpsPerCta independent units
+// into a CTA (no block barrier at all); K > 1 gives a CTA of K warps per unit, which walk
+// "super-tiles" of K*U tiles and exchange their aggregates through shared memory with one
+// __syncthreads per super-tile (double-buffered slots).
+struct Unit {
+    int64_t offset;  // element offset of the unit's first position
+    int64_t len;     // number of positions
+    bool first;      // unit starts at t = 0 of its row
+};
+
+template <bool SEG>
+__device__ __forceinline__ Unit unit_of(int64_t u, int64_t T, int64_t nseg, int64_t seg_len) {
+    Unit q;
+    if constexpr (!SEG) {
+        q.offset = u * T;
+        q.len = T;
+        q.first = true;
+    } else {
+        const int64_t r = u / nseg, k = u - r * nseg;
+        q.offset = r * T + k * seg_len;
+        q.len = min(seg_len, T - k * seg_len);
+        q.first = (k == 0);
+    }
+    return q;
+}
+
+template <int K>
+struct Coop {
+    static constexpr int kThreads = (K == 1 ? kWarpsPerCta : K) * 32;
+    static __device__ __forceinline__ int64_t unit_index() {
+        return K == 1 ? static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5)
+                      : static_cast<int64_t>(blockIdx.x);
+    }
+    static __device__ __forceinline__ int warp_in_unit() { return K == 1 ? 0 : (threadIdx.x >> 5); }
+};
+
 // ---------------------------------------------------------------- forward / reduce ----------
 // WRITE = true : states (and optionally h_last) are produced            -> fms_plain_forward
 // WRITE = false: only the carries P = prod a and S = h_last are produced -> fms_plain_reduce
-template <typename S, bool GENERIC, int U, bool WRITE>
-__global__ void __launch_bounds__(kWarpsPerCta * 32, FMS_FWD_MIN_CTAS)
+template <typename S, bool GENERIC, int U, bool WRITE, int K, bool SEG>
+__global__ void __launch_bounds__(Coop<K>::kThreads)
 plain_forward_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
                      const float *__restrict__ h0, S *__restrict__ states,
-                     float *__restrict__ h_last, float *__restrict__ P_out, int64_t R, int64_t T) {
+                     float *__restrict__ h_last, float *__restrict__ P_out, int64_t R, int64_t T,
+                     int64_t nseg, int64_t seg_len) {
     constexpr int E = Store<S>::E;
     constexpr int TILE = 32 * E;
+    __shared__ float2 agg[2][K > 1 ? K : 1];
     const int lane = threadIdx.x & 31;
-    const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
-    if (row >= R) return;
+    const int w = Coop<K>::warp_in_unit();
+    const int64_t unit = Coop<K>::unit_index();
+    if (unit >= R) return;  // K == 1 only: with K > 1 the grid has exactly R CTAs
 
-    const S *ar = gates + row * T;
-    const S *xr = tokens + row * T;
-    S *hr = WRITE ? states + row * T : nullptr;
+    const Unit q = unit_of<SEG>(unit, T, nseg, seg_len);
+    const int64_t L = q.len;
+    const S *ar = gates + q.offset;
+    const S *xr = tokens + q.offset;
+    S *hr = WRITE ? states + q.offset : nullptr;
     const int64_t vbase = row_phase<S, GENERIC>(ar);
     const bool ph_x = !GENERIC || same_phase16(ar, xr);
     const bool ph_h = !GENERIC || !WRITE || same_phase16(ar, hr);
-    const int64_t ngroups = (T - vbase + TILE * U - 1) / (TILE * U);
+    constexpr int64_t SUPER = static_cast<int64_t>(TILE) * U * K;
+    const int64_t ngroups = (L - vbase + SUPER - 1) / SUPER;
 
-    float carry = h0 ? h0[row] : 0.f;  // state entering the current tile
-    float prod = 1.f;                  // product of all gates so far (reduce only)
+    float carry = h0 ? h0[unit] : 0.f;  // state entering the current super-tile
+    float prod = 1.f;                   // product of all gates so far (reduce only)
 
-    int64_t v = vbase + lane * E;  // this lane's vector in tile 0 of the current group
+    int64_t v = vbase + static_cast<int64_t>(w) * (TILE * U) + lane * E;
     uint4 ra[U], rx[U];
 #pragma unroll
     for (int j = 0; j < U; ++j) {
-        ra[j] = load_vec<S, GENERIC>(ar, v + j * TILE, T, true, Store<S>::kOne);
-        rx[j] = load_vec<S, GENERIC>(xr, v + j * TILE, T, ph_x, 0u);
+        ra[j] = load_vec<S, GENERIC>(ar, v + j * TILE, L, true, Store<S>::kOne);
+        rx[j] = load_vec<S, GENERIC>(xr, v + j * TILE, L, ph_x, 0u);
     }
 
     for (int64_t g = 0; g < ngroups; ++g) {
-        // Prefetch the next group (vectors past the row end return the identity without a
-        // memory access).
+        // Prefetch this warp's tiles of the next super-tile (vectors past the end return the
+        // identity without a memory access).
         uint4 na[U], nx[U];
-        const int64_t vn = v + TILE * U;
+        const int64_t vn = v + SUPER;
 #pragma unroll
         for (int j = 0; j < U; ++j) {
-            na[j] = load_vec<S, GENERIC>(ar, vn + j * TILE, T, true, Store<S>::kOne);
-            nx[j] = load_vec<S, GENERIC>(xr, vn + j * TILE, T, ph_x, 0u);
+            na[j] = load_vec<S, GENERIC>(ar, vn + j * TILE, L, true, Store<S>::kOne);
+            nx[j] = load_vec<S, GENERIC>(xr, vn + j * TILE, L, ph_x, 0u);
         }
 
         float fa[U][E], fx[U][E], A[U], H[U];
@@ -268,17 +307,42 @@ plain_forward_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
                 }
             }
         }
+        float next_carry = 0.f;
+        if constexpr (K > 1) {
+            // Publish this warp's aggregate over its U tiles, then fold the K aggregates in time
+            // order: `carry` becomes the state entering this warp's first tile, `next_carry` the
+            // state leaving the super-tile (every warp computes the same value).
+            float WA = __shfl_sync(kFullMask, A[0], 31), WH = __shfl_sync(kFullMask, H[0], 31);
+#pragma unroll
+            for (int j = 1; j < U; ++j) {
+                const float tA = __shfl_sync(kFullMask, A[j], 31);
+                WH = fmaf(tA, WH, __shfl_sync(kFullMask, H[j], 31));
+                WA *= tA;
+            }
+            const int buf = static_cast<int>(g & 1);
+            if (lane == 0) agg[buf][w] = make_float2(WA, WH);
+            __syncthreads();
+            float run = carry;
+#pragma unroll
+            for (int ww = 0; ww < K; ++ww) {
+                if (ww == w) carry = run;
+                const float2 p = agg[buf][ww];
+                run = fmaf(p.x, run, p.y);
+                if constexpr (!WRITE) prod *= p.x;
+            }
+            next_carry = run;
+        }
 #pragma unroll
         for (int j = 0; j < U; ++j) {
-            float eA = __shfl_up_sync(kFullMask, A[j], 1);
-            float eH = __shfl_up_sync(kFullMask, H[j], 1);
-            if (lane == 0) {
-                eA = 1.f;
-                eH = 0.f;
-            }
             const float tA = __shfl_sync(kFullMask, A[j], 31);
             const float tH = __shfl_sync(kFullMask, H[j], 31);
             if constexpr (WRITE) {
+                float eA = __shfl_up_sync(kFullMask, A[j], 1);
+                float eH = __shfl_up_sync(kFullMask, H[j], 1);
+                if (lane == 0) {
+                    eA = 1.f;
+                    eH = 0.f;
+                }
                 float s = fmaf(eA, carry, eH);  // state entering this lane's elements
                 float out[E];
 #pragma unroll
@@ -286,12 +350,13 @@ plain_forward_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
                     s = fmaf(fa[j][i], s, fx[j][i]);
                     out[i] = s;
                 }
-                store_vec<S, GENERIC>(hr, v + j * TILE, T, ph_h, Store<S>::pack(out));
-            } else {
+                store_vec<S, GENERIC>(hr, v + j * TILE, L, ph_h, Store<S>::pack(out));
+            } else if constexpr (K == 1) {
                 prod *= tA;
             }
             carry = fmaf(tA, carry, tH);
         }
+        if constexpr (K > 1) carry = next_carry;
 #pragma unroll
         for (int j = 0; j < U; ++j) {
             ra[j] = na[j];
@@ -299,9 +364,9 @@ plain_forward_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
         }
         v = vn;
     }
-    if (lane == 0) {
-        if (h_last) h_last[row] = carry;
-        if (!WRITE && P_out) P_out[row] = prod;
+    if (lane == 0 && w == 0) {
+        if (h_last) h_last[unit] = carry;
+        if (!WRITE && P_out) P_out[unit] = prod;
     }
 }
 
@@ -309,51 +374,63 @@ plain_forward_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
 // c_t = a_t * (G_t + c_{t+1}) scanned from the row end; delta_t = G_t + c_{t+1};
 // grad_tokens_t = delta_t; grad_gates_t = delta_t * h_{t-1}; grad_h0 = c_0.
 // WRITE = false produces only S_rev = c_0 (from carry_in = 0) and P = prod a.
-template <typename S, bool GENERIC, int U, bool WRITE>
-__global__ void __launch_bounds__(kWarpsPerCta * 32, FMS_BWD_MIN_CTAS)
+template <typename S, bool GENERIC, int U, bool WRITE, int K, bool SEG>
+__global__ void __launch_bounds__(Coop<K>::kThreads)
 plain_backward_kernel(const S *__restrict__ gates, const S *__restrict__ states,
                       const S *__restrict__ grad_states, const float *__restrict__ h0,
                       const float *__restrict__ carry_in, S *__restrict__ grad_gates,
                       S *__restrict__ grad_tokens, float *__restrict__ grad_h0,
-                      float *__restrict__ P_out, int64_t R, int64_t T) {
+                      float *__restrict__ P_out, int64_t R, int64_t T, int64_t nseg,
+                      int64_t seg_len) {
     constexpr int E = Store<S>::E;
     constexpr int TILE = 32 * E;
+    __shared__ float2 agg[2][K > 1 ? K : 1];
     const int lane = threadIdx.x & 31;
-    const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
-    if (row >= R) return;
+    const int w = Coop<K>::warp_in_unit();
+    const int64_t unit = Coop<K>::unit_index();
+    if (unit >= R) return;
 
-    const S *ar = gates + row * T;
-    const S *gr = grad_states + row * T;
-    const S *hr = WRITE ? states + row * T : nullptr;
-    S *gar = WRITE ? grad_gates + row * T : nullptr;
-    S *gxr = WRITE ? grad_tokens + row * T : nullptr;
+    const Unit q = unit_of<SEG>(unit, T, nseg, seg_len);
+    const int64_t L = q.len;
+    const S *ar = gates + q.offset;
+    const S *gr = grad_states + q.offset;
+    const S *hr = WRITE ? states + q.offset : nullptr;
+    S *gar = WRITE ? grad_gates + q.offset : nullptr;
+    S *gxr = WRITE ? grad_tokens + q.offset : nullptr;
     const int64_t vbase = row_phase<S, GENERIC>(ar);
     const bool ph_g = !GENERIC || same_phase16(ar, gr);
     const bool ph_h = !GENERIC || !WRITE || same_phase16(ar, hr);
     const bool ph_ga = !GENERIC || !WRITE || same_phase16(ar, gar);
     const bool ph_gx = !GENERIC || !WRITE || same_phase16(ar, gxr);
-    const int64_t ngroups = (T - vbase + TILE * U - 1) / (TILE * U);
+    constexpr int64_t SUPER = static_cast<int64_t>(TILE) * U * K;
+    const int64_t ngroups = (L - vbase + SUPER - 1) / SUPER;
 
-    const float h_init = (WRITE && h0) ? h0[row] : 0.f;
-    float carry = carry_in ? carry_in[row] : 0.f;  // c at the first position after the tile
+    // State just before the unit: the row's initial state, or (split path) the last state of
+    // the previous segment of the same row.
+    float h_before = 0.f;
+    if constexpr (WRITE) {
+        if (q.first) h_before = h0 ? h0[SEG ? unit / nseg : unit] : 0.f;
+        else h_before = Store<S>::to_float(hr[-1]);
+    }
+    float carry = carry_in ? carry_in[unit] : 0.f;  // c at the first position after the super-tile
     float prod = 1.f;
 
     // State just before a tile (h_{t-1} of the tile's first element); needed by lane 0 only.
     auto load_halo = [&](int64_t vt) -> float {
         if (!WRITE || lane != 0) return 0.f;
         const int64_t t = vt - 1;
-        return (t >= 0 && t < T) ? Store<S>::to_float(hr[t]) : h_init;
+        return (t >= 0 && t < L) ? Store<S>::to_float(hr[t]) : h_before;
     };
 
-    int64_t v = vbase + (ngroups - 1) * (TILE * U) + lane * E;  // last group first
+    int64_t v = vbase + (ngroups - 1) * SUPER + static_cast<int64_t>(w) * (TILE * U) + lane * E;
     uint4 ra[U], rg[U], rh[U];
     float halo[U];
 #pragma unroll
     for (int j = 0; j < U; ++j) {
-        ra[j] = load_vec<S, GENERIC>(ar, v + j * TILE, T, true, Store<S>::kOne);
-        rg[j] = load_vec<S, GENERIC>(gr, v + j * TILE, T, ph_g, 0u);
+        ra[j] = load_vec<S, GENERIC>(ar, v + j * TILE, L, true, Store<S>::kOne);
+        rg[j] = load_vec<S, GENERIC>(gr, v + j * TILE, L, ph_g, 0u);
         if constexpr (WRITE) {
-            rh[j] = load_vec<S, GENERIC>(hr, v + j * TILE, T, ph_h, 0u);
+            rh[j] = load_vec<S, GENERIC>(hr, v + j * TILE, L, ph_h, 0u);
             halo[j] = load_halo(v + j * TILE);
         }
     }
@@ -361,15 +438,14 @@ plain_backward_kernel(const S *__restrict__ gates, const S *__restrict__ states,
     for (int64_t g = ngroups - 1; g >= 0; --g) {
         uint4 na[U], ng[U], nh[U];
         float nhalo[U];
-        const int64_t vn = v - TILE * U;
+        const int64_t vn = v - SUPER;
 #pragma unroll
         for (int j = 0; j < U; ++j) {
-            // vn + j*TILE + E <= vbase means the whole vector lies before the row: identity.
-            const int64_t vv = (g > 0) ? vn + j * TILE : T;  // T = "outside" for every path
-            na[j] = load_vec<S, GENERIC>(ar, vv, T, true, Store<S>::kOne);
-            ng[j] = load_vec<S, GENERIC>(gr, vv, T, ph_g, 0u);
+            const int64_t vv = (g > 0) ? vn + j * TILE : L;  // L = "outside" for every path
+            na[j] = load_vec<S, GENERIC>(ar, vv, L, true, Store<S>::kOne);
+            ng[j] = load_vec<S, GENERIC>(gr, vv, L, ph_g, 0u);
             if constexpr (WRITE) {
-                nh[j] = load_vec<S, GENERIC>(hr, vv, T, ph_h, 0u);
+                nh[j] = load_vec<S, GENERIC>(hr, vv, L, ph_h, 0u);
                 nhalo[j] = (g > 0) ? load_halo(vv) : 0.f;
             }
         }
@@ -400,17 +476,39 @@ plain_backward_kernel(const S *__restrict__ gates, const S *__restrict__ states,
                 }
             }
         }
+        float next_carry = 0.f;
+        if constexpr (K > 1) {
+            float WA = __shfl_sync(kFullMask, A[U - 1], 0), WC = __shfl_sync(kFullMask, C[U - 1], 0);
+#pragma unroll
+            for (int j = U - 2; j >= 0; --j) {
+                const float tA = __shfl_sync(kFullMask, A[j], 0);
+                WC = fmaf(tA, WC, __shfl_sync(kFullMask, C[j], 0));
+                WA *= tA;
+            }
+            const int buf = static_cast<int>(g & 1);
+            if (lane == 0) agg[buf][w] = make_float2(WA, WC);
+            __syncthreads();
+            float run = carry;
+#pragma unroll
+            for (int ww = K - 1; ww >= 0; --ww) {
+                if (ww == w) carry = run;
+                const float2 p = agg[buf][ww];
+                run = fmaf(p.x, run, p.y);
+                if constexpr (!WRITE) prod *= p.x;
+            }
+            next_carry = run;
+        }
 #pragma unroll
         for (int j = U - 1; j >= 0; --j) {
-            float eA = __shfl_down_sync(kFullMask, A[j], 1);
-            float eC = __shfl_down_sync(kFullMask, C[j], 1);
-            if (lane == 31) {
-                eA = 1.f;
-                eC = 0.f;
-            }
             const float tA = __shfl_sync(kFullMask, A[j], 0);
             const float tC = __shfl_sync(kFullMask, C[j], 0);
             if constexpr (WRITE) {
+                float eA = __shfl_down_sync(kFullMask, A[j], 1);
+                float eC = __shfl_down_sync(kFullMask, C[j], 1);
+                if (lane == 31) {
+                    eA = 1.f;
+                    eC = 0.f;
+                }
                 float fh[E];
                 Store<S>::unpack(rh[j], fh);
                 // h_{t-1} of this lane's first element: last state of the lane below, or the halo.
@@ -424,18 +522,19 @@ plain_backward_kernel(const S *__restrict__ gates, const S *__restrict__ states,
                     c = fa[j][i] * delta;
                     float hp = (i > 0) ? fh[i > 0 ? i - 1 : 0] : hprev0;
                     if constexpr (GENERIC) {
-                        if (v + j * TILE + i == 0) hp = h_init;  // row start inside a vector
+                        if (v + j * TILE + i == 0) hp = h_before;  // unit start inside a vector
                     }
                     dx[i] = delta;
                     da[i] = delta * hp;
                 }
-                store_vec<S, GENERIC>(gxr, v + j * TILE, T, ph_gx, Store<S>::pack(dx));
-                store_vec<S, GENERIC>(gar, v + j * TILE, T, ph_ga, Store<S>::pack(da));
-            } else {
+                store_vec<S, GENERIC>(gxr, v + j * TILE, L, ph_gx, Store<S>::pack(dx));
+                store_vec<S, GENERIC>(gar, v + j * TILE, L, ph_ga, Store<S>::pack(da));
+            } else if constexpr (K == 1) {
                 prod *= tA;
             }
             carry = fmaf(tA, carry, tC);
         }
+        if constexpr (K > 1) carry = next_carry;
 #pragma unroll
         for (int j = 0; j < U; ++j) {
             ra[j] = na[j];
@@ -447,26 +546,31 @@ plain_backward_kernel(const S *__restrict__ gates, const S *__restrict__ states,
         }
         v = vn;
     }
-    if (lane == 0) {
-        if (grad_h0) grad_h0[row] = carry;
-        if (!WRITE && P_out) P_out[row] = prod;
+    if (lane == 0 && w == 0) {
+        if (grad_h0) grad_h0[unit] = carry;
+        if (!WRITE && P_out) P_out[unit] = prod;
     }
 }
 
 // ---------------------------------------------------------------- carry combination ---------
 // One thread per row folds the per-block carries serially in scan order (nchunks is the number
 // of ranks or time blocks: small).
+// Element (chunk k, row r) of P, S and carry_out lives at k*chunk_stride + r*row_stride:
+// (R, 1) for the chunk-major layout an all-gather produces, (1, nchunks) for the row-major
+// layout of the one-GPU split path.
 __global__ void combine_carries_kernel(const float *__restrict__ P, const float *__restrict__ S,
                                        const float *__restrict__ carry0,
                                        float *__restrict__ carry_out, float *__restrict__ total,
-                                       int64_t nchunks, int64_t R, int reverse) {
+                                       int64_t nchunks, int64_t R, int reverse,
+                                       int64_t chunk_stride, int64_t row_stride) {
     const int64_t r = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (r >= R) return;
     float c = carry0 ? carry0[r] : 0.f;
     for (int64_t i = 0; i < nchunks; ++i) {
         const int64_t k = reverse ? nchunks - 1 - i : i;
-        carry_out[k * R + r] = c;
-        c = fmaf(P[k * R + r], c, S[k * R + r]);
+        const int64_t at = k * chunk_stride + r * row_stride;
+        carry_out[at] = c;
+        c = fmaf(P[at], c, S[at]);
     }
     if (total) total[r] = c;
 }

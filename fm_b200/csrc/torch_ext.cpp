@@ -77,6 +77,15 @@ at::Tensor fm_scan_forward(const at::Tensor &gates, const at::Tensor &tokens,
     const c10::cuda::CUDAGuard guard(gates.device());
     at::Tensor h0 = carry_f32(initial_state, rows, gates, "initial_state");
     auto stream = at::cuda::getCurrentCUDAStream().stream();
+    // A handful of very long rows: cut them into segments so the whole GPU works (needs scratch).
+    const size_t scratch = fms_plain_split_workspace_bytes(rows, T, dtype);
+    if (scratch > 0) {
+        at::Tensor ws = at::empty({static_cast<int64_t>(scratch)}, gates.options().dtype(at::kByte));
+        check_status(fms_plain_forward_split(gates.data_ptr(), tokens.data_ptr(), fptr(h0), out.data_ptr(),
+                                             nullptr, rows, T, dtype, ws.data_ptr(), scratch, stream),
+                     "fm_scan_forward");
+        return out;
+    }
     check_status(fms_plain_forward(gates.data_ptr(), tokens.data_ptr(), fptr(h0), out.data_ptr(),
                                    nullptr, rows, T, dtype, stream),
                  "fm_scan_forward");
@@ -115,6 +124,16 @@ void fm_scan_backward_ex(const at::Tensor &gates, const at::Tensor &outGrad,
         gh0 = grad_initial_state.data_ptr<float>();
     }
     auto stream = at::cuda::getCurrentCUDAStream().stream();
+    const size_t scratch = fms_plain_split_workspace_bytes(rows, T, dtype);
+    if (scratch > 0) {
+        at::Tensor ws = at::empty({static_cast<int64_t>(scratch)}, gates.options().dtype(at::kByte));
+        check_status(fms_plain_backward_split(gates.data_ptr(), cached_output.data_ptr(), outGrad.data_ptr(),
+                                              fptr(h0), fptr(cin), gateGradOut.data_ptr(),
+                                              tokenGradOut.data_ptr(), gh0, rows, T, dtype, ws.data_ptr(),
+                                              scratch, stream),
+                     "fm_scan_backward");
+        return;
+    }
     check_status(fms_plain_backward(gates.data_ptr(), cached_output.data_ptr(), outGrad.data_ptr(),
                                     fptr(h0), fptr(cin), gateGradOut.data_ptr(),
                                     tokenGradOut.data_ptr(), gh0, rows, T, dtype, stream),

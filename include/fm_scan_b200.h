@@ -126,6 +126,34 @@ int fms_combine_carries(const float *P, const float *S, const float *carry0, flo
                         float *total, int64_t nchunks, int64_t rows, int reverse,
                         fms_stream_t stream);
 
+/* ------------------------------------------------- few, long rows: split inside one GPU ---- */
+
+/*
+ * With fewer rows than the GPU has warps to fill (a handful of very long sequences), one warp
+ * per row leaves most of the machine idle.  The split entry points cut every row into `nseg`
+ * segments and run three launches: carries of every segment, a fold per row, then the ordinary
+ * scan of every segment from its true carry-in.  Results equal the unsplit entry points' up to
+ * fp32 re-association of the carries.  The reference has no counterpart (one CTA walks a whole
+ * row serially, fm/scan/fm_scan.cuh:84).
+ *
+ * fms_plain_split_segments: segments per row the library would use for this shape (1 = the
+ * split does not pay; call the ordinary entry points).
+ * fms_plain_split_workspace_bytes: device scratch the split entry points need for this shape
+ * (3 fp32 per segment, rounded up; 0 when segments == 1).  The caller owns the scratch; it may
+ * be reused by the next call on the same stream.
+ * Arguments of the two entry points are those of fms_plain_forward / fms_plain_backward plus
+ * the scratch.  With segments == 1 they forward to the ordinary entry points.
+ */
+int64_t fms_plain_split_segments(int64_t rows, int64_t T, int dtype);
+size_t fms_plain_split_workspace_bytes(int64_t rows, int64_t T, int dtype);
+int fms_plain_forward_split(const void *gates, const void *tokens, const float *h0, void *states,
+                            float *h_last, int64_t rows, int64_t T, int dtype, void *workspace,
+                            size_t workspace_bytes, fms_stream_t stream);
+int fms_plain_backward_split(const void *gates, const void *states, const void *grad_states,
+                             const float *h0, const float *carry_in, void *grad_gates,
+                             void *grad_tokens, float *grad_h0, int64_t rows, int64_t T, int dtype,
+                             void *workspace, size_t workspace_bytes, fms_stream_t stream);
+
 /* ------------------------------------------------------- host-buffer pipeline (one GPU) ---- */
 
 /*

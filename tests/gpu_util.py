@@ -74,3 +74,34 @@ def combine(P, S, carry0=None, reverse=False):
     capi.call("fms_combine_carries", capi.ptr(P), capi.ptr(S), capi.ptr(carry0), capi.ptr(out),
               capi.ptr(total), nchunks, rows, int(reverse), stream_ptr())
     return out, total
+
+
+def split_plan(rows, T, dtype):
+    L = capi.lib()
+    tag = capi.dtype_tag(dtype)
+    return int(L.fms_plain_split_segments(rows, T, tag)), int(L.fms_plain_split_workspace_bytes(rows, T, tag))
+
+
+def forward_split(a, x, h0=None, want_last=False):
+    T = a.shape[-1]
+    rows = a.numel() // T
+    nseg, nbytes = split_plan(rows, T, a.dtype)
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=a.device)
+    h = torch.empty_like(a)
+    h_last = torch.empty(a.shape[:-1], device=a.device, dtype=torch.float32) if want_last else None
+    capi.call("fms_plain_forward_split", capi.ptr(a), capi.ptr(x), capi.ptr(h0), capi.ptr(h),
+              capi.ptr(h_last), rows, T, capi.dtype_tag(a.dtype), ws.data_ptr(), nbytes, stream_ptr())
+    return (h, h_last) if want_last else h
+
+
+def backward_split(a, h, G, h0=None, carry_in=None, want_gh0=False):
+    T = a.shape[-1]
+    rows = a.numel() // T
+    nseg, nbytes = split_plan(rows, T, a.dtype)
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=a.device)
+    ga, gx = torch.empty_like(a), torch.empty_like(a)
+    gh0 = torch.empty(a.shape[:-1], device=a.device, dtype=torch.float32) if want_gh0 else None
+    capi.call("fms_plain_backward_split", capi.ptr(a), capi.ptr(h), capi.ptr(G), capi.ptr(h0),
+              capi.ptr(carry_in), capi.ptr(ga), capi.ptr(gx), capi.ptr(gh0), rows, T,
+              capi.dtype_tag(a.dtype), ws.data_ptr(), nbytes, stream_ptr())
+    return (ga, gx, gh0) if want_gh0 else (ga, gx)

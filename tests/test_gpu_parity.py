@@ -340,3 +340,62 @@ def test_torch_op_autograd_and_errors():
         fm_scan_forward(ad.detach().cpu(), xd.detach().cpu(), None, torch.empty_like(ad).cpu())
     with pytest.raises(AssertionError):    # non-contiguous input, as the reference's Python asserts
         fm_scan(ad.detach().transpose(0, 1), xd.detach().transpose(0, 1))
+
+
+@pytest.mark.parametrize("storage,R,T", [("f32", 3, 200_000), ("bf16", 1, 1_000_003), ("f16", 16, 65_536),
+                                         ("f32", 1, 8191)])
+def test_split_inside_one_gpu_for_few_long_rows(storage, R, T):
+    """Rows cut into segments (carries, fold, scan): same results as the oracle and as the
+    unsplit entry points; the last shape is too short to split and must fall through."""
+    a, x, Gd, h0 = H.make_inputs(R, T, 55, "sigmoid+3", storage, with_h0=True)
+    cin = np.linspace(-0.5, 0.5, R).astype(np.float32)
+    ad, xd, gd = (G.dev(v, storage) for v in (a, x, Gd))
+    h0d, cind = G.dev(h0), G.dev(cin)
+    nseg, nbytes = G.split_plan(R, T, ad.dtype)
+    assert (nseg > 1) == (T >= 8192) and (nbytes > 0) == (nseg > 1)
+    h, h_last = G.forward_split(ad, xd, h0d, want_last=True)
+    ga, gx, gh0 = G.backward_split(ad, h, gd, h0d, cind, want_gh0=True)
+    h_u, h_last_u = G.forward(ad, xd, h0d, want_last=True)
+    ga_u, gx_u, gh0_u = G.backward(ad, h, gd, h0d, cind, want_gh0=True)
+    torch.cuda.synchronize()
+    f64 = np.float64
+    h_ref = oc.plain_forward(a, x, h0)
+    h_ref64 = oc.plain_forward(a.astype(f64), x.astype(f64), h0.astype(f64), dtype=f64)
+    close_to_reference(G.host(h), h_ref, h_ref64, storage, "split states", scaled=True)
+    hs = G.host(h)
+    ga_ref, gx_ref, gh0_ref = oc.plain_backward(a, hs, Gd, h0, cin)
+    ga_ref64, gx_ref64, gh0_ref64 = oc.plain_backward(a.astype(f64), hs.astype(f64), Gd.astype(f64),
+                                                      h0.astype(f64), cin.astype(f64), dtype=f64)
+    close_to_reference(G.host(gx), gx_ref, gx_ref64, storage, "split grad_tokens", scaled=True)
+    close_to_reference(G.host(ga), ga_ref, ga_ref64, storage, "split grad_gates", scaled=True)
+    H.assert_close(G.host(gh0), gh0_ref64, 1e-4, 1e-4, "split grad_h0")
+    H.assert_close(G.host(h_last), h_ref64[:, -1], 1e-4, 1e-4, "split h_last")
+    # against the unsplit kernels: same values up to the re-association of the carries
+    r, at = (1e-5, 2e-5) if storage == "f32" else (H.LOWP_RTOL, H.lowp_atol(h_ref))
+    H.assert_close(G.host(h), G.host(h_u), r, at, "split vs unsplit states")
+    H.assert_close(G.host(gx), G.host(gx_u), r, at * 4, "split vs unsplit grad_tokens")
+    H.assert_close(G.host(gh0), G.host(gh0_u), 1e-4, 1e-4, "split vs unsplit grad_h0")
+
+
+@pytest.mark.parametrize("K", [1, 2, 4, 8])
+@pytest.mark.parametrize("storage,T", [("f32", 5000), ("bf16", 8192), ("f16", 3073), ("bf16", 100)])
+def test_warps_per_row_variants_agree(monkeypatch, K, storage, T):
+    """K warps cooperating on a row (shared-memory carry exchange) against the oracle."""
+    monkeypatch.setenv("FMS_TUNE_FWD_K", str(K))
+    monkeypatch.setenv("FMS_TUNE_BWD_K", str(K))
+    a, x, Gd, h0 = H.make_inputs(7, T, 400 + T, "sigmoid01", storage, with_h0=True)
+    cin = np.linspace(-1, 1, 7).astype(np.float32)
+    check_fwd_bwd(a, x, Gd, storage, h0, cin, f"K={K} {storage} T={T}")
+    ad, xd = G.dev(a, storage), G.dev(x, storage)
+    P, S = G.reduce(ad, xd)
+    P_ref, S_ref = oc.plain_reduce(a.astype(np.float64), x.astype(np.float64), dtype=np.float64)
+    H.assert_close(G.host(P), P_ref, 1e-4, 1e-30, "P")
+    H.assert_close(G.host(S), S_ref, 1e-4, 1e-5, "S")
+
+
+@pytest.mark.parametrize("U", [1, 2, 4])
+def test_unroll_variants_agree(monkeypatch, U):
+    monkeypatch.setenv("FMS_TUNE_FWD_U", str(U))
+    monkeypatch.setenv("FMS_TUNE_BWD_U", str(U))
+    a, x, Gd = H.make_inputs(9, 4096 + 512, 17, "sigmoid", "bf16")
+    check_fwd_bwd(a, x, Gd, "bf16", what=f"U={U}")

@@ -29,6 +29,7 @@ SIGNATURES = {
     "fms_plain_reduce_reverse": [_P, _P, _P, _P, _I64, _I64, _I, _P],
     "fms_combine_carries": [_P, _P, _P, _P, _P, _I64, _I64, _I, _P],
     "fms_plain_forward_split": [_P, _P, _P, _P, _P, _I64, _I64, _I, _P, ctypes.c_size_t, _P],
+    "fms_plain_forward_split_static": [_P, _P, _P, _P, _P, _I64, _I64, _I, _P],
     "fms_plain_backward_split": [_P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I, _P, ctypes.c_size_t, _P],
 }
 

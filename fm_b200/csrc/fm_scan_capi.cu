@@ -4,6 +4,7 @@
 
 #include <algorithm>
 #include <cstdlib>
+#include <mutex>
 
 #include "scan_kernels.cuh"
 
@@ -391,4 +392,59 @@ FMS_EXPORT int fms_plain_backward_split(const void *gates, const void *states, c
     if (int rc = launch_combine(wP, wS, carry_in, wC, grad_h0, plan.nseg, rows, 1, 1, plan.nseg, st)) return rc;
     FMS_DISPATCH_DTYPE(dtype, (launch_backward<S, true>(pb, sp, gates, states, grad_states, h0, wC, grad_gates,
                                                         grad_tokens, nullptr, nullptr, st)));
+}
+
+// ------------------------------------------------- split forward with built-in scratch ----
+// The carries of fms_plain_forward_split_static live here, in the library's device image, so
+// the entry point never touches the allocator.  In host code the name below is only a handle:
+// the address kernels may use is looked up per device with cudaGetSymbolAddress.
+static __device__ __align__(256) float g_static_scratch[3 * FMS_STATIC_SCRATCH_MAX_UNITS];
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+float *g_static_scratch_ptr[kMaxDevices] = {};
+
+// Device address of g_static_scratch on the current device (resolved once per device).
+int static_scratch_on_current_device(float **out) {
+    int dev = -1;
+    if (int rc = record(cudaGetDevice(&dev))) return rc;
+    if (dev < 0 || dev >= kMaxDevices) return FMS_ERR_NO_DEVICE;
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!g_static_scratch_ptr[dev]) {
+        void *p = nullptr;
+        if (int rc = record(cudaGetSymbolAddress(&p, g_static_scratch))) return rc;
+        if (!p) return FMS_ERR_LAUNCH;
+        g_static_scratch_ptr[dev] = static_cast<float *>(p);
+    }
+    *out = g_static_scratch_ptr[dev];
+    return FMS_OK;
+}
+
+}  // namespace
+
+FMS_EXPORT int fms_plain_forward_split_static(const void *gates, const void *tokens, const float *h0,
+                                              void *states, float *h_last, int64_t rows, int64_t T,
+                                              int dtype, fms_stream_t stream) {
+    Problem pb;
+    if (int rc = make_problem(pb, rows, T, dtype, gates, tokens, static_cast<const void *>(states)))
+        return rc;
+    const SplitPlan plan = plan_split(rows, T);
+    if (plan.nseg == 1)  // no scratch involved
+        return fms_plain_forward(gates, tokens, h0, states, h_last, rows, T, dtype, stream);
+    if (plan.units > FMS_STATIC_SCRATCH_MAX_UNITS) return FMS_ERR_TOO_LARGE;
+    float *scratch = nullptr;
+    if (int rc = static_scratch_on_current_device(&scratch)) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    float *wP = scratch, *wS = wP + plan.units, *wC = wS + plan.units;
+    const Split sp{plan.nseg, plan.seg_len};
+    {
+        auto pass1 = [&]() -> int {
+            FMS_DISPATCH_DTYPE(dtype, (launch_forward<S, false>(pb, sp, gates, tokens, nullptr, nullptr, wS, wP, st)));
+        };
+        if (int rc = pass1()) return rc;
+    }
+    if (int rc = launch_combine(wP, wS, h0, wC, h_last, plan.nseg, rows, 0, 1, plan.nseg, st)) return rc;
+    FMS_DISPATCH_DTYPE(dtype, (launch_forward<S, true>(pb, sp, gates, tokens, wC, states, nullptr, nullptr, st)));
 }

@@ -154,6 +154,39 @@ int fms_plain_backward_split(const void *gates, const void *states, const void *
                              void *grad_tokens, float *grad_h0, int64_t rows, int64_t T, int dtype,
                              void *workspace, size_t workspace_bytes, fms_stream_t stream);
 
+/*
+ * Forward scan of few, long rows for callers that must not allocate device memory.
+ * (No counterpart in the reference.)
+ *
+ * Some hosts of this library cannot hand it scratch: a plugin inside a serving framework that
+ * owns every byte of device memory and forbids its plugins the CUDA allocator; a control loop
+ * that cannot afford the device-wide synchronisation cudaMalloc implies; a process whose memory
+ * pool has already taken the whole GPU, so that an allocation would simply fail.  For them this
+ * entry point does what fms_plain_forward_split does, with the per-segment carries kept in a
+ * fixed array inside the library's device image instead of a caller workspace.  It calls no
+ * cudaMalloc / cudaFree and no allocating library routine; inputs and outputs are still the
+ * caller's.
+ *
+ * Limit: at most FMS_STATIC_SCRATCH_MAX_UNITS = 4096 scan units (rows x segments per row, see
+ * fms_plain_split_segments); the array is 3 x 4096 fp32 = 48 KiB and every GPU that loads the
+ * library holds it until the process exits.  A larger problem is refused with
+ * FMS_ERR_TOO_LARGE and nothing is launched.  Shapes that need no split (segments == 1) use no
+ * scratch and are always accepted.
+ *
+ * Set-up: the first call on each device looks up the array's device address (once per device,
+ * with that device current) and caches it.  Make that first call during initialisation, before
+ * any stream capture is begun on the device.
+ *
+ * Sharing: all calls on a device use the same array and it keeps the last call's contents.
+ * Nothing in it has to start at zero -- every call overwrites each slot it later reads -- but
+ * two calls whose kernels overlap on the GPU (different streams, no ordering between them)
+ * race on it.  Order such calls on one stream or with events.
+ */
+#define FMS_STATIC_SCRATCH_MAX_UNITS 4096
+int fms_plain_forward_split_static(const void *gates, const void *tokens, const float *h0,
+                                   void *states, float *h_last, int64_t rows, int64_t T, int dtype,
+                                   fms_stream_t stream);
+
 /* ------------------------------------------------------- host-buffer pipeline (one GPU) ---- */
 
 /*

@@ -38,16 +38,12 @@ inline bool sizes_ok(int64_t rows, int64_t T) {
     return rows <= (INT64_MAX / 8) / T;
 }
 
-// Tiles per group (loads in flight per warp = U x tensors x 512 B).  Tunable for experiments
-// through the environment; the defaults are the measured best on B200.
+// Tuning knobs read from the environment on every launch (FMS_TUNE_*): warps per row K, tiles
+// per warp and step U, persistence, a cap on the grid.  Unset, the choices below apply, which
+// are the measured best on B200.
 int tune_value(const char *name, int dflt) {
     const char *s = std::getenv(name);
     return s ? std::atoi(s) : dflt;
-}
-
-int tune_unroll(const char *name, int dflt) {
-    const int v = tune_value(name, dflt);
-    return (v == 1 || v == 2 || v == 4) ? v : dflt;
 }
 
 struct Problem {
@@ -90,6 +86,26 @@ int copy_or_zero(const float *src, float *dst, int64_t n, float fill, cudaStream
     return check_launch();
 }
 
+// Grid of a persistent launch: no more CTAs than the GPU holds at once (each then walks several
+// units and prefetches across their boundaries), never more than there is work.  Measured on
+// B200 the hardware block scheduler with one unit per CTA is 1-5 % faster than this static
+// walk for every benchmark shape, so persistence is off unless FMS_TUNE_PERSIST=1 asks for it
+// (the kernels support both; the multi-unit walk is covered by the tests).
+int sm_count() {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+    return n;
+}
+
+template <typename Kernel>
+int64_t resident_ctas(Kernel kernel, int threads) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0) != cudaSuccess || per_sm <= 0)
+        per_sm = 1;
+    return static_cast<int64_t>(per_sm) * sm_count();
+}
+
 // How a launch is cut into scan units and how many warps share a unit.
 struct Split {
     int64_t nseg = 1;     // segments per row (1 = whole rows)
@@ -102,30 +118,48 @@ struct Split {
 int choose_coop(int64_t units, int64_t T, size_t es, const char *env_name) {
     const int forced = tune_value(env_name, 0);
     if (forced == 1 || forced == 2 || forced == 4 || forced == 8) return forced;
-    (void)units;
-    // Measured on B200: a row of 32 tiles (16 KB) is fastest with 2 warps, one of 256 tiles
-    // with 8; short rows keep one warp each so the loop has iterations to prefetch across.
+    // Measured on B200 (CUDA events, fwd+bwd GB/s): 16 KB rows x 32768 rows: K=2 6306, K=4 6182,
+    // K=1 5797; 16 KB rows x 8192 rows: K=4 6026, K=2 5761; 128 KB rows x 4096 rows: K=8 6284,
+    // K=4 6143.  Rows shorter than 32 tiles keep one warp each.
     const int64_t tiles = (T * static_cast<int64_t>(es) + 511) / 512;
-    if (tiles >= 128) return 8;
-    if (tiles >= 64) return 4;
-    if (tiles >= 32) return 2;
+    int k = tiles >= 128 ? 8 : tiles >= 64 ? 4 : tiles >= 32 ? 2 : 1;
+    if (k > 1 && k < 8 && units <= 8192) k *= 2;  // small launches: finer-grained CTAs shorten the tail
+    return k;
+}
+
+// Tiles per warp and step: 4 unless the row is too short to fill K*4 tiles.
+int choose_unroll(int64_t T, size_t es, int K, const char *env_name) {
+    const int forced = tune_value(env_name, 0);
+    if (forced == 1 || forced == 2 || forced == 4) return forced;
+    const int64_t tiles = (T * static_cast<int64_t>(es) + 511) / 512;
+    if (tiles >= 4 * K) return 4;
+    if (tiles >= 2 * K) return 2;
     return 1;
 }
 
 template <typename S, bool WRITE>
 int launch_forward(const Problem &pb, const Split &sp, const void *gates, const void *tokens,
                    const float *h0, void *states, float *h_last, float *P, cudaStream_t st) {
-    const int unroll = tune_unroll("FMS_TUNE_FWD_U", 4);
     const int64_t units = pb.rows * sp.nseg;
     const int K = sp.nseg > 1 ? 1 : choose_coop(units, pb.T, sizeof(S), "FMS_TUNE_FWD_K");
+    const int unroll = choose_unroll(pb.T, sizeof(S), K, "FMS_TUNE_FWD_U");
     const int64_t ctas = K == 1 ? (units + fms::kWarpsPerCta - 1) / fms::kWarpsPerCta : units;
     if (ctas > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;
-    const dim3 grid(static_cast<unsigned>(ctas));
     const int64_t seg_len = sp.nseg == 1 ? pb.T : sp.seg_len;
+    const int64_t max_ctas = std::max(1, tune_value("FMS_TUNE_MAX_CTAS", 0x7fffffff));  // test knob
+    const bool persist = tune_value("FMS_TUNE_PERSIST", 0) != 0;
 #define FMS_LAUNCH_FWD_S(G, UU, KK, SS)                                                            \
-    fms::plain_forward_kernel<S, G, UU, WRITE, KK, SS><<<grid, fms::Coop<KK>::kThreads, 0, st>>>(   \
-        static_cast<const S *>(gates), static_cast<const S *>(tokens), h0, static_cast<S *>(states), \
-        h_last, P, units, pb.T, sp.nseg, seg_len)
+    do {                                                                                           \
+        auto kern = fms::plain_forward_kernel<S, G, UU, WRITE, KK, SS>;                            \
+        int64_t nctas = ctas;                                                                      \
+        if (!(G) && !(SS) && persist) { /* persistent instantiation */                             \
+            static const int64_t resident = resident_ctas(kern, fms::Coop<KK>::kThreads);          \
+            nctas = std::min(ctas, std::min(resident, max_ctas));                                  \
+        }                                                                                          \
+        kern<<<static_cast<unsigned>(nctas), fms::Coop<KK>::kThreads, 0, st>>>(                    \
+            static_cast<const S *>(gates), static_cast<const S *>(tokens), h0,                     \
+            static_cast<S *>(states), h_last, P, units, pb.T, sp.nseg, seg_len);                   \
+    } while (0)
 #define FMS_LAUNCH_FWD(G, UU, KK) FMS_LAUNCH_FWD_S(G, UU, KK, false)
 #define FMS_LAUNCH_FWD_K(G, UU)                                                                    \
     switch (K) {                                                                                   \
@@ -154,18 +188,29 @@ template <typename S, bool WRITE>
 int launch_backward(const Problem &pb, const Split &sp, const void *gates, const void *states,
                     const void *grad_states, const float *h0, const float *carry_in, void *grad_gates,
                     void *grad_tokens, float *grad_h0, float *P, cudaStream_t st) {
-    const int unroll = tune_unroll("FMS_TUNE_BWD_U", 2);
     const int64_t units = pb.rows * sp.nseg;
     const int K = sp.nseg > 1 ? 1 : choose_coop(units, pb.T, sizeof(S), "FMS_TUNE_BWD_K");
+    // one warp per row: 2 tiles per step (4 costs occupancy: 141+ registers for three inputs)
+    const int unroll = K == 1 ? std::min(2, choose_unroll(pb.T, sizeof(S), K, "FMS_TUNE_BWD_U"))
+                              : choose_unroll(pb.T, sizeof(S), K, "FMS_TUNE_BWD_U");
     const int64_t ctas = K == 1 ? (units + fms::kWarpsPerCta - 1) / fms::kWarpsPerCta : units;
     if (ctas > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;
-    const dim3 grid(static_cast<unsigned>(ctas));
     const int64_t seg_len = sp.nseg == 1 ? pb.T : sp.seg_len;
+    const int64_t max_ctas = std::max(1, tune_value("FMS_TUNE_MAX_CTAS", 0x7fffffff));  // test knob
+    const bool persist = tune_value("FMS_TUNE_PERSIST", 0) != 0;
 #define FMS_LAUNCH_BWD_S(G, UU, KK, SS)                                                            \
-    fms::plain_backward_kernel<S, G, UU, WRITE, KK, SS><<<grid, fms::Coop<KK>::kThreads, 0, st>>>(  \
-        static_cast<const S *>(gates), static_cast<const S *>(states),                             \
-        static_cast<const S *>(grad_states), h0, carry_in, static_cast<S *>(grad_gates),           \
-        static_cast<S *>(grad_tokens), grad_h0, P, units, pb.T, sp.nseg, seg_len)
+    do {                                                                                           \
+        auto kern = fms::plain_backward_kernel<S, G, UU, WRITE, KK, SS>;                           \
+        int64_t nctas = ctas;                                                                      \
+        if (!(G) && !(SS) && persist) {                                                            \
+            static const int64_t resident = resident_ctas(kern, fms::Coop<KK>::kThreads);          \
+            nctas = std::min(ctas, std::min(resident, max_ctas));                                  \
+        }                                                                                          \
+        kern<<<static_cast<unsigned>(nctas), fms::Coop<KK>::kThreads, 0, st>>>(                    \
+            static_cast<const S *>(gates), static_cast<const S *>(states),                         \
+            static_cast<const S *>(grad_states), h0, carry_in, static_cast<S *>(grad_gates),       \
+            static_cast<S *>(grad_tokens), grad_h0, P, units, pb.T, sp.nseg, seg_len);             \
+    } while (0)
 #define FMS_LAUNCH_BWD(G, UU, KK) FMS_LAUNCH_BWD_S(G, UU, KK, false)
 #define FMS_LAUNCH_BWD_K(G, UU)                                                                    \
     switch (K) {                                                                                   \

@@ -224,9 +224,14 @@ __device__ __forceinline__ Unit unit_of(int64_t u, int64_t T, int64_t nseg, int6
 template <int K>
 struct Coop {
     static constexpr int kThreads = (K == 1 ? kWarpsPerCta : K) * 32;
-    static __device__ __forceinline__ int64_t unit_index() {
+    // Index of the first unit this warp (K == 1) or CTA (K > 1) works on, and the distance to
+    // its next one when the grid is smaller than the number of units.
+    static __device__ __forceinline__ int64_t first_unit() {
         return K == 1 ? static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5)
                       : static_cast<int64_t>(blockIdx.x);
+    }
+    static __device__ __forceinline__ int64_t unit_stride() {
+        return K == 1 ? static_cast<int64_t>(gridDim.x) * kWarpsPerCta : static_cast<int64_t>(gridDim.x);
     }
     static __device__ __forceinline__ int warp_in_unit() { return K == 1 ? 0 : (threadIdx.x >> 5); }
 };
@@ -234,6 +239,12 @@ struct Coop {
 // ---------------------------------------------------------------- forward / reduce ----------
 // WRITE = true : states (and optionally h_last) are produced            -> fms_plain_forward
 // WRITE = false: only the carries P = prod a and S = h_last are produced -> fms_plain_reduce
+//
+// Aligned whole-row launches (!GENERIC && !SEG) are persistent: the grid is sized to what the
+// GPU holds at once, each warp (or CTA) walks units first, first+stride, ... and the prefetch
+// at the last group of a unit already fetches the first group of the next one, so the load
+// pipeline never drains at a row boundary.  The masked and the segmented instantiations get one
+// unit per warp/CTA (their geometry changes from unit to unit).
 template <typename S, bool GENERIC, int U, bool WRITE, int K, bool SEG>
 __global__ void __launch_bounds__(Coop<K>::kThreads)
 plain_forward_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
@@ -242,43 +253,55 @@ plain_forward_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
                      int64_t nseg, int64_t seg_len) {
     constexpr int E = Store<S>::E;
     constexpr int TILE = 32 * E;
+    constexpr bool PERSIST = !GENERIC && !SEG;
+    constexpr int64_t SUPER = static_cast<int64_t>(TILE) * U * K;
     __shared__ float2 agg[2][K > 1 ? K : 1];
     const int lane = threadIdx.x & 31;
     const int w = Coop<K>::warp_in_unit();
-    const int64_t unit = Coop<K>::unit_index();
-    if (unit >= R) return;  // K == 1 only: with K > 1 the grid has exactly R CTAs
+    int64_t unit = Coop<K>::first_unit();
+    if (unit >= R) return;  // K == 1 only: with K > 1 the grid never exceeds R CTAs
+    const int64_t stride = Coop<K>::unit_stride();
 
     const Unit q = unit_of<SEG>(unit, T, nseg, seg_len);
-    const int64_t L = q.len;
-    const S *ar = gates + q.offset;
-    const S *xr = tokens + q.offset;
-    S *hr = WRITE ? states + q.offset : nullptr;
-    const int64_t vbase = row_phase<S, GENERIC>(ar);
-    const bool ph_x = !GENERIC || same_phase16(ar, xr);
-    const bool ph_h = !GENERIC || !WRITE || same_phase16(ar, hr);
-    constexpr int64_t SUPER = static_cast<int64_t>(TILE) * U * K;
+    const int64_t L = q.len;  // PERSIST: every unit has length T
+    int64_t off = q.offset;   // element offset of the current unit
+    const int64_t vbase = row_phase<S, GENERIC>(gates + off);
+    const bool ph_x = !GENERIC || same_phase16(gates + off, tokens + off);
+    const bool ph_h = !GENERIC || !WRITE || same_phase16(gates + off, states + off);
     const int64_t ngroups = (L - vbase + SUPER - 1) / SUPER;
+    const int64_t v0 = vbase + static_cast<int64_t>(w) * (TILE * U) + lane * E;
 
     float carry = h0 ? h0[unit] : 0.f;  // state entering the current super-tile
-    float prod = 1.f;                   // product of all gates so far (reduce only)
+    float prod = 1.f;                   // product of the unit's gates so far (reduce only)
 
-    int64_t v = vbase + static_cast<int64_t>(w) * (TILE * U) + lane * E;
+    int64_t v = v0;  // this lane's first vector of the current group, relative to the unit
+    int64_t g = 0;
     uint4 ra[U], rx[U];
 #pragma unroll
     for (int j = 0; j < U; ++j) {
-        ra[j] = load_vec<S, GENERIC>(ar, v + j * TILE, L, true, Store<S>::kOne);
-        rx[j] = load_vec<S, GENERIC>(xr, v + j * TILE, L, ph_x, 0u);
+        ra[j] = load_vec<S, GENERIC>(gates + off, v + j * TILE, L, true, Store<S>::kOne);
+        rx[j] = load_vec<S, GENERIC>(tokens + off, v + j * TILE, L, ph_x, 0u);
     }
 
-    for (int64_t g = 0; g < ngroups; ++g) {
-        // Prefetch this warp's tiles of the next super-tile (vectors past the end return the
-        // identity without a memory access).
+    for (unsigned it = 0;; ++it) {
+        // Where the next group lives: same unit, or the first group of this warp's next unit.
+        const bool last_group = (g + 1 == ngroups);
+        int64_t noff = off, nv = v + SUPER;
+        bool more = true;
+        if (last_group) {
+            if (PERSIST && unit + stride < R) {
+                noff = (unit + stride) * T;
+                nv = v0;
+            } else {
+                more = false;
+                nv = L;  // "outside": the prefetch below returns the identity, no memory access
+            }
+        }
         uint4 na[U], nx[U];
-        const int64_t vn = v + SUPER;
 #pragma unroll
         for (int j = 0; j < U; ++j) {
-            na[j] = load_vec<S, GENERIC>(ar, vn + j * TILE, L, true, Store<S>::kOne);
-            nx[j] = load_vec<S, GENERIC>(xr, vn + j * TILE, L, ph_x, 0u);
+            na[j] = load_vec<S, GENERIC>(gates + noff, nv + j * TILE, L, true, Store<S>::kOne);
+            nx[j] = load_vec<S, GENERIC>(tokens + noff, nv + j * TILE, L, ph_x, 0u);
         }
 
         float fa[U][E], fx[U][E], A[U], H[U];
@@ -319,7 +342,7 @@ plain_forward_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
                 WH = fmaf(tA, WH, __shfl_sync(kFullMask, H[j], 31));
                 WA *= tA;
             }
-            const int buf = static_cast<int>(g & 1);
+            const int buf = static_cast<int>(it & 1u);
             if (lane == 0) agg[buf][w] = make_float2(WA, WH);
             __syncthreads();
             float run = carry;
@@ -350,23 +373,34 @@ plain_forward_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
                     s = fmaf(fa[j][i], s, fx[j][i]);
                     out[i] = s;
                 }
-                store_vec<S, GENERIC>(hr, v + j * TILE, L, ph_h, Store<S>::pack(out));
+                store_vec<S, GENERIC>(states + off, v + j * TILE, L, ph_h, Store<S>::pack(out));
             } else if constexpr (K == 1) {
                 prod *= tA;
             }
             carry = fmaf(tA, carry, tH);
         }
         if constexpr (K > 1) carry = next_carry;
+
+        if (last_group) {  // the unit is complete
+            if (lane == 0 && w == 0) {
+                if (h_last) h_last[unit] = carry;
+                if (!WRITE && P_out) P_out[unit] = prod;
+            }
+            if (!more) break;
+            unit += stride;
+            carry = h0 ? h0[unit] : 0.f;
+            prod = 1.f;
+            g = 0;
+        } else {
+            ++g;
+        }
 #pragma unroll
         for (int j = 0; j < U; ++j) {
             ra[j] = na[j];
             rx[j] = nx[j];
         }
-        v = vn;
-    }
-    if (lane == 0 && w == 0) {
-        if (h_last) h_last[unit] = carry;
-        if (!WRITE && P_out) P_out[unit] = prod;
+        off = noff;
+        v = nv;
     }
 }
 
@@ -374,6 +408,7 @@ plain_forward_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
 // c_t = a_t * (G_t + c_{t+1}) scanned from the row end; delta_t = G_t + c_{t+1};
 // grad_tokens_t = delta_t; grad_gates_t = delta_t * h_{t-1}; grad_h0 = c_0.
 // WRITE = false produces only S_rev = c_0 (from carry_in = 0) and P = prod a.
+// Same persistence rule as the forward kernel.
 template <typename S, bool GENERIC, int U, bool WRITE, int K, bool SEG>
 __global__ void __launch_bounds__(Coop<K>::kThreads)
 plain_backward_kernel(const S *__restrict__ gates, const S *__restrict__ states,
@@ -384,69 +419,85 @@ plain_backward_kernel(const S *__restrict__ gates, const S *__restrict__ states,
                       int64_t seg_len) {
     constexpr int E = Store<S>::E;
     constexpr int TILE = 32 * E;
+    constexpr bool PERSIST = !GENERIC && !SEG;
+    constexpr int64_t SUPER = static_cast<int64_t>(TILE) * U * K;
     __shared__ float2 agg[2][K > 1 ? K : 1];
     const int lane = threadIdx.x & 31;
     const int w = Coop<K>::warp_in_unit();
-    const int64_t unit = Coop<K>::unit_index();
+    int64_t unit = Coop<K>::first_unit();
     if (unit >= R) return;
+    const int64_t stride = Coop<K>::unit_stride();
 
     const Unit q = unit_of<SEG>(unit, T, nseg, seg_len);
     const int64_t L = q.len;
-    const S *ar = gates + q.offset;
-    const S *gr = grad_states + q.offset;
-    const S *hr = WRITE ? states + q.offset : nullptr;
-    S *gar = WRITE ? grad_gates + q.offset : nullptr;
-    S *gxr = WRITE ? grad_tokens + q.offset : nullptr;
-    const int64_t vbase = row_phase<S, GENERIC>(ar);
-    const bool ph_g = !GENERIC || same_phase16(ar, gr);
-    const bool ph_h = !GENERIC || !WRITE || same_phase16(ar, hr);
-    const bool ph_ga = !GENERIC || !WRITE || same_phase16(ar, gar);
-    const bool ph_gx = !GENERIC || !WRITE || same_phase16(ar, gxr);
-    constexpr int64_t SUPER = static_cast<int64_t>(TILE) * U * K;
+    int64_t off = q.offset;
+    const int64_t vbase = row_phase<S, GENERIC>(gates + off);
+    const bool ph_g = !GENERIC || same_phase16(gates + off, grad_states + off);
+    const bool ph_h = !GENERIC || !WRITE || same_phase16(gates + off, states + off);
+    const bool ph_ga = !GENERIC || !WRITE || same_phase16(gates + off, grad_gates + off);
+    const bool ph_gx = !GENERIC || !WRITE || same_phase16(gates + off, grad_tokens + off);
     const int64_t ngroups = (L - vbase + SUPER - 1) / SUPER;
+    // this lane's first vector in the LAST group of a unit (the first one the reverse walk visits)
+    const int64_t v_last = vbase + (ngroups - 1) * SUPER + static_cast<int64_t>(w) * (TILE * U) + lane * E;
 
     // State just before the unit: the row's initial state, or (split path) the last state of
     // the previous segment of the same row.
-    float h_before = 0.f;
-    if constexpr (WRITE) {
-        if (q.first) h_before = h0 ? h0[SEG ? unit / nseg : unit] : 0.f;
-        else h_before = Store<S>::to_float(hr[-1]);
-    }
+    auto state_before = [&](int64_t u, int64_t o) -> float {
+        if constexpr (!WRITE) return 0.f;
+        if constexpr (SEG) {
+            if (!q.first) return Store<S>::to_float(states[o - 1]);
+            return h0 ? h0[u / nseg] : 0.f;
+        }
+        return h0 ? h0[u] : 0.f;
+    };
+    float h_before = state_before(unit, off);
     float carry = carry_in ? carry_in[unit] : 0.f;  // c at the first position after the super-tile
     float prod = 1.f;
 
-    // State just before a tile (h_{t-1} of the tile's first element); needed by lane 0 only.
-    auto load_halo = [&](int64_t vt) -> float {
+    // State just before a tile (h_{t-1} of the tile's first element), read by lane 0; positions
+    // before the unit are replaced by h_before when the tile is computed.
+    auto load_halo = [&](int64_t o, int64_t vt) -> float {
         if (!WRITE || lane != 0) return 0.f;
         const int64_t t = vt - 1;
-        return (t >= 0 && t < L) ? Store<S>::to_float(hr[t]) : h_before;
+        return (t >= 0 && t < L) ? Store<S>::to_float(states[o + t]) : 0.f;
     };
 
-    int64_t v = vbase + (ngroups - 1) * SUPER + static_cast<int64_t>(w) * (TILE * U) + lane * E;
+    int64_t v = v_last;
+    int64_t g = ngroups - 1;
     uint4 ra[U], rg[U], rh[U];
     float halo[U];
 #pragma unroll
     for (int j = 0; j < U; ++j) {
-        ra[j] = load_vec<S, GENERIC>(ar, v + j * TILE, L, true, Store<S>::kOne);
-        rg[j] = load_vec<S, GENERIC>(gr, v + j * TILE, L, ph_g, 0u);
+        ra[j] = load_vec<S, GENERIC>(gates + off, v + j * TILE, L, true, Store<S>::kOne);
+        rg[j] = load_vec<S, GENERIC>(grad_states + off, v + j * TILE, L, ph_g, 0u);
         if constexpr (WRITE) {
-            rh[j] = load_vec<S, GENERIC>(hr, v + j * TILE, L, ph_h, 0u);
-            halo[j] = load_halo(v + j * TILE);
+            rh[j] = load_vec<S, GENERIC>(states + off, v + j * TILE, L, ph_h, 0u);
+            halo[j] = load_halo(off, v + j * TILE);
         }
     }
 
-    for (int64_t g = ngroups - 1; g >= 0; --g) {
+    for (unsigned it = 0;; ++it) {
+        const bool last_group = (g == 0);  // last in walking order = first in time
+        int64_t noff = off, nv = v - SUPER;
+        bool more = true;
+        if (last_group) {
+            if (PERSIST && unit + stride < R) {
+                noff = (unit + stride) * T;
+                nv = v_last;
+            } else {
+                more = false;
+            }
+        }
         uint4 na[U], ng[U], nh[U];
         float nhalo[U];
-        const int64_t vn = v - SUPER;
 #pragma unroll
         for (int j = 0; j < U; ++j) {
-            const int64_t vv = (g > 0) ? vn + j * TILE : L;  // L = "outside" for every path
-            na[j] = load_vec<S, GENERIC>(ar, vv, L, true, Store<S>::kOne);
-            ng[j] = load_vec<S, GENERIC>(gr, vv, L, ph_g, 0u);
+            const int64_t vv = more ? nv + j * TILE : L;  // L = "outside" for every path
+            na[j] = load_vec<S, GENERIC>(gates + noff, vv, L, true, Store<S>::kOne);
+            ng[j] = load_vec<S, GENERIC>(grad_states + noff, vv, L, ph_g, 0u);
             if constexpr (WRITE) {
-                nh[j] = load_vec<S, GENERIC>(hr, vv, L, ph_h, 0u);
-                nhalo[j] = (g > 0) ? load_halo(vv) : 0.f;
+                nh[j] = load_vec<S, GENERIC>(states + noff, vv, L, ph_h, 0u);
+                nhalo[j] = more ? load_halo(noff, vv) : 0.f;
             }
         }
 
@@ -485,7 +536,7 @@ plain_backward_kernel(const S *__restrict__ gates, const S *__restrict__ states,
                 WC = fmaf(tA, WC, __shfl_sync(kFullMask, C[j], 0));
                 WA *= tA;
             }
-            const int buf = static_cast<int>(g & 1);
+            const int buf = static_cast<int>(it & 1u);
             if (lane == 0) agg[buf][w] = make_float2(WA, WC);
             __syncthreads();
             float run = carry;
@@ -513,7 +564,7 @@ plain_backward_kernel(const S *__restrict__ gates, const S *__restrict__ states,
                 Store<S>::unpack(rh[j], fh);
                 // h_{t-1} of this lane's first element: last state of the lane below, or the halo.
                 float hprev0 = __shfl_up_sync(kFullMask, fh[E - 1], 1);
-                if (lane == 0) hprev0 = halo[j];
+                if (lane == 0) hprev0 = (v + j * TILE - 1 >= 0) ? halo[j] : h_before;
                 float c = fmaf(eA, carry, eC);  // c just after this lane's elements
                 float dx[E], da[E];
 #pragma unroll
@@ -527,14 +578,29 @@ plain_backward_kernel(const S *__restrict__ gates, const S *__restrict__ states,
                     dx[i] = delta;
                     da[i] = delta * hp;
                 }
-                store_vec<S, GENERIC>(gxr, v + j * TILE, L, ph_gx, Store<S>::pack(dx));
-                store_vec<S, GENERIC>(gar, v + j * TILE, L, ph_ga, Store<S>::pack(da));
+                store_vec<S, GENERIC>(grad_tokens + off, v + j * TILE, L, ph_gx, Store<S>::pack(dx));
+                store_vec<S, GENERIC>(grad_gates + off, v + j * TILE, L, ph_ga, Store<S>::pack(da));
             } else if constexpr (K == 1) {
                 prod *= tA;
             }
             carry = fmaf(tA, carry, tC);
         }
         if constexpr (K > 1) carry = next_carry;
+
+        if (last_group) {
+            if (lane == 0 && w == 0) {
+                if (grad_h0) grad_h0[unit] = carry;
+                if (!WRITE && P_out) P_out[unit] = prod;
+            }
+            if (!more) break;
+            unit += stride;
+            h_before = state_before(unit, noff);
+            carry = carry_in ? carry_in[unit] : 0.f;
+            prod = 1.f;
+            g = ngroups - 1;
+        } else {
+            --g;
+        }
 #pragma unroll
         for (int j = 0; j < U; ++j) {
             ra[j] = na[j];
@@ -544,11 +610,8 @@ plain_backward_kernel(const S *__restrict__ gates, const S *__restrict__ states,
                 halo[j] = nhalo[j];
             }
         }
-        v = vn;
-    }
-    if (lane == 0 && w == 0) {
-        if (grad_h0) grad_h0[unit] = carry;
-        if (!WRITE && P_out) P_out[unit] = prod;
+        off = noff;
+        v = nv;
     }
 }
 

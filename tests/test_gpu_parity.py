@@ -399,3 +399,28 @@ def test_unroll_variants_agree(monkeypatch, U):
     monkeypatch.setenv("FMS_TUNE_BWD_U", str(U))
     a, x, Gd = H.make_inputs(9, 4096 + 512, 17, "sigmoid", "bf16")
     check_fwd_bwd(a, x, Gd, "bf16", what=f"U={U}")
+
+
+@pytest.mark.parametrize("K", [1, 2, 8])
+@pytest.mark.parametrize("storage,R,T,ctas", [("f32", 37, 1024, 2), ("bf16", 53, 2048 + 256, 3),
+                                              ("f16", 19, 8, 1), ("f32", 4, 4096, 1)])
+def test_persistent_walk_over_several_rows(monkeypatch, K, storage, R, T, ctas):
+    """A grid smaller than the number of rows: every warp/CTA walks several rows, prefetching the
+    next row while it finishes the current one; carries must reset at every row boundary."""
+    monkeypatch.setenv("FMS_TUNE_MAX_CTAS", str(ctas))
+    monkeypatch.setenv("FMS_TUNE_FWD_K", str(K))
+    monkeypatch.setenv("FMS_TUNE_BWD_K", str(K))
+    a, x, Gd, h0 = H.make_inputs(R, T, 600 + R, "sigmoid01", storage, with_h0=True)
+    cin = np.linspace(-1, 1, R).astype(np.float32)
+    check_fwd_bwd(a, x, Gd, storage, h0, cin, f"persistent K={K} {storage} {R}x{T}")
+    ad, xd, gd = (G.dev(v, storage) for v in (a, x, Gd))
+    P, S = G.reduce(ad, xd)
+    P2, S2 = G.reduce_reverse(ad, gd)
+    torch.cuda.synchronize()
+    f64 = np.float64
+    P_ref, S_ref = oc.plain_reduce(a.astype(f64), x.astype(f64), dtype=f64)
+    H.assert_close(G.host(P), P_ref, 1e-4, 1e-30, "P")
+    H.assert_close(G.host(S), S_ref, 1e-4, 1e-5, "S")
+    _, _, Srev_ref = oc.plain_backward(a.astype(f64), np.zeros_like(a, dtype=f64), Gd.astype(f64), dtype=f64)
+    H.assert_close(G.host(P2), P_ref, 1e-4, 1e-30, "P (reverse)")
+    H.assert_close(G.host(S2), Srev_ref, 1e-4, 1e-5, "S_rev")

@@ -29,6 +29,8 @@ SIGNATURES = {
     "fms_plain_reduce_reverse": [_P, _P, _P, _P, _I64, _I64, _I, _P],
     "fms_combine_carries": [_P, _P, _P, _P, _P, _I64, _I64, _I, _P],
     "fms_plain_forward_split": [_P, _P, _P, _P, _P, _I64, _I64, _I, _P, ctypes.c_size_t, _P],
+    "fms_fm_forward": [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _I, _P],
+    "fms_fm_backward": [_P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I, _P, ctypes.c_size_t, _P],
     "fms_plain_forward_split_static": [_P, _P, _P, _P, _P, _I64, _I64, _I, _P],
     "fms_plain_backward_split": [_P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I, _P, ctypes.c_size_t, _P],
 }
@@ -64,6 +66,8 @@ def lib() -> ctypes.CDLL:
         L.fms_plain_split_segments.argtypes = [_I64, _I64, _I]
         L.fms_plain_split_workspace_bytes.restype = ctypes.c_size_t
         L.fms_plain_split_workspace_bytes.argtypes = [_I64, _I64, _I]
+        L.fms_fm_backward_workspace_bytes.restype = ctypes.c_size_t
+        L.fms_fm_backward_workspace_bytes.argtypes = [_I64, _I64, _I64, _I64, _I]
         _lib = L
     return _lib
 

@@ -141,7 +141,9 @@ template <typename S, bool WRITE>
 int launch_forward(const Problem &pb, const Split &sp, const void *gates, const void *tokens,
                    const float *h0, void *states, float *h_last, float *P, cudaStream_t st) {
     const int64_t units = pb.rows * sp.nseg;
-    const int K = sp.nseg > 1 ? 1 : choose_coop(units, pb.T, sizeof(S), "FMS_TUNE_FWD_K");
+    int K = sp.nseg > 1 ? 1 : choose_coop(units, pb.T, sizeof(S), "FMS_TUNE_FWD_K");
+    // masked path (measured on 2304 rows x 16385 fp16): one warp per row is fastest forward
+    if (!pb.aligned && tune_value("FMS_TUNE_FWD_K", 0) == 0) K = 1;
     const int unroll = choose_unroll(pb.T, sizeof(S), K, "FMS_TUNE_FWD_U");
     const int64_t ctas = K == 1 ? (units + fms::kWarpsPerCta - 1) / fms::kWarpsPerCta : units;
     if (ctas > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;
@@ -150,7 +152,7 @@ int launch_forward(const Problem &pb, const Split &sp, const void *gates, const 
     const bool persist = tune_value("FMS_TUNE_PERSIST", 0) != 0;
 #define FMS_LAUNCH_FWD_S(G, UU, KK, SS)                                                            \
     do {                                                                                           \
-        auto kern = fms::plain_forward_kernel<S, G, UU, WRITE, KK, SS>;                            \
+        auto kern = fms::plain_forward_kernel<S, G, UU, WRITE, KK, SS, false>;                            \
         int64_t nctas = ctas;                                                                      \
         if (!(G) && !(SS) && persist) { /* persistent instantiation */                             \
             static const int64_t resident = resident_ctas(kern, fms::Coop<KK>::kThreads);          \
@@ -158,7 +160,7 @@ int launch_forward(const Problem &pb, const Split &sp, const void *gates, const 
         }                                                                                          \
         kern<<<static_cast<unsigned>(nctas), fms::Coop<KK>::kThreads, 0, st>>>(                    \
             static_cast<const S *>(gates), static_cast<const S *>(tokens), h0,                     \
-            static_cast<S *>(states), h_last, P, units, pb.T, sp.nseg, seg_len);                   \
+            static_cast<S *>(states), h_last, P, units, pb.T, sp.nseg, seg_len, 0, 0);             \
     } while (0)
 #define FMS_LAUNCH_FWD(G, UU, KK) FMS_LAUNCH_FWD_S(G, UU, KK, false)
 #define FMS_LAUNCH_FWD_K(G, UU)                                                                    \
@@ -189,7 +191,9 @@ int launch_backward(const Problem &pb, const Split &sp, const void *gates, const
                     const void *grad_states, const float *h0, const float *carry_in, void *grad_gates,
                     void *grad_tokens, float *grad_h0, float *P, cudaStream_t st) {
     const int64_t units = pb.rows * sp.nseg;
-    const int K = sp.nseg > 1 ? 1 : choose_coop(units, pb.T, sizeof(S), "FMS_TUNE_BWD_K");
+    int K = sp.nseg > 1 ? 1 : choose_coop(units, pb.T, sizeof(S), "FMS_TUNE_BWD_K");
+    // masked path (same measurement): two warps per row are fastest backward
+    if (!pb.aligned && tune_value("FMS_TUNE_BWD_K", 0) == 0) K = std::min(K, 2);
     // one warp per row: 2 tiles per step (4 costs occupancy: 141+ registers for three inputs)
     const int unroll = K == 1 ? std::min(2, choose_unroll(pb.T, sizeof(S), K, "FMS_TUNE_BWD_U"))
                               : choose_unroll(pb.T, sizeof(S), K, "FMS_TUNE_BWD_U");
@@ -200,7 +204,7 @@ int launch_backward(const Problem &pb, const Split &sp, const void *gates, const
     const bool persist = tune_value("FMS_TUNE_PERSIST", 0) != 0;
 #define FMS_LAUNCH_BWD_S(G, UU, KK, SS)                                                            \
     do {                                                                                           \
-        auto kern = fms::plain_backward_kernel<S, G, UU, WRITE, KK, SS>;                           \
+        auto kern = fms::plain_backward_kernel<S, G, UU, WRITE, KK, SS, false>;                           \
         int64_t nctas = ctas;                                                                      \
         if (!(G) && !(SS) && persist) {                                                            \
             static const int64_t resident = resident_ctas(kern, fms::Coop<KK>::kThreads);          \
@@ -209,7 +213,8 @@ int launch_backward(const Problem &pb, const Split &sp, const void *gates, const
         kern<<<static_cast<unsigned>(nctas), fms::Coop<KK>::kThreads, 0, st>>>(                    \
             static_cast<const S *>(gates), static_cast<const S *>(states),                         \
             static_cast<const S *>(grad_states), h0, carry_in, static_cast<S *>(grad_gates),       \
-            static_cast<S *>(grad_tokens), grad_h0, P, units, pb.T, sp.nseg, seg_len);             \
+            static_cast<S *>(grad_tokens), grad_h0, P, units, pb.T, sp.nseg, seg_len, nullptr,     \
+            nullptr, nullptr, 0, 0);                                                               \
     } while (0)
 #define FMS_LAUNCH_BWD(G, UU, KK) FMS_LAUNCH_BWD_S(G, UU, KK, false)
 #define FMS_LAUNCH_BWD_K(G, UU)                                                                    \
@@ -341,6 +346,177 @@ FMS_EXPORT int fms_combine_carries(const float *P, const float *S, const float *
     if (nchunks == 0) return copy_or_zero(carry0, total, rows, 0.f, st);
     if (!P || !S || !carry_out) return FMS_ERR_NULL_POINTER;
     return launch_combine(P, S, carry0, carry_out, total, nchunks, rows, reverse, rows, 1, st);
+}
+
+// ------------------------------------------------------------------ FM mode -----------------
+namespace {
+
+struct FmShape {
+    int64_t B, M, D, L, rows;  // rows = B*M*D output rows
+};
+
+int make_fm_shape(FmShape &sh, int64_t B, int64_t M, int64_t D, int64_t L, int dtype) {
+    if (dtype != FMS_F32 && dtype != FMS_F16 && dtype != FMS_BF16) return FMS_ERR_BAD_DTYPE;
+    if (B < 0 || M < 0 || D < 0 || L < 0) return FMS_ERR_BAD_SHAPE;
+    sh = FmShape{B, M, D, L, 0};
+    if (B == 0 || M == 0 || D == 0) return FMS_OK;
+    if (B > INT64_MAX / M || B * M > INT64_MAX / D) return FMS_ERR_BAD_SHAPE;
+    sh.rows = B * M * D;
+    if (!sizes_ok(sh.rows, L)) return FMS_ERR_BAD_SHAPE;
+    return FMS_OK;
+}
+
+template <typename S>
+int launch_fm_forward(const FmShape &sh, bool aligned, const void *gates, const void *tokens, const float *h0,
+                      void *states, cudaStream_t st) {
+    const int K = choose_coop(sh.rows, sh.L, sizeof(S), "FMS_TUNE_FWD_K");
+    const int unroll = std::min(2, choose_unroll(sh.L, sizeof(S), K, "FMS_TUNE_FWD_U"));
+    const int64_t ctas = K == 1 ? (sh.rows + fms::kWarpsPerCta - 1) / fms::kWarpsPerCta : sh.rows;
+    if (ctas > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;
+#define FMS_LAUNCH_FM_FWD(G, UU, KK)                                                               \
+    fms::plain_forward_kernel<S, G, UU, true, KK, false, true>                                     \
+        <<<static_cast<unsigned>(ctas), fms::Coop<KK>::kThreads, 0, st>>>(                         \
+            static_cast<const S *>(gates), static_cast<const S *>(tokens), h0,                     \
+            static_cast<S *>(states), nullptr, nullptr, sh.rows, sh.L, 1, sh.L, sh.M, sh.D)
+#define FMS_LAUNCH_FM_FWD_K(G, UU)                                                                 \
+    switch (K) {                                                                                   \
+        case 1: FMS_LAUNCH_FM_FWD(G, UU, 1); break;                                                \
+        case 2: FMS_LAUNCH_FM_FWD(G, UU, 2); break;                                                \
+        case 4: FMS_LAUNCH_FM_FWD(G, UU, 4); break;                                                \
+        default: FMS_LAUNCH_FM_FWD(G, UU, 8); break;                                               \
+    }
+    if (!aligned) { FMS_LAUNCH_FM_FWD_K(true, 1) }
+    else if (unroll == 2) { FMS_LAUNCH_FM_FWD_K(false, 2) }
+    else { FMS_LAUNCH_FM_FWD_K(false, 1) }
+#undef FMS_LAUNCH_FM_FWD_K
+#undef FMS_LAUNCH_FM_FWD
+    return check_launch();
+}
+
+template <typename S>
+int launch_fm_backward(const FmShape &sh, bool aligned, const void *gates, const void *tokens,
+                       const void *states, const void *grad_states, const float *h0, float *acc_gates,
+                       float *acc_tokens, float *grad_h0, cudaStream_t st) {
+    const int K = choose_coop(sh.rows, sh.L, sizeof(S), "FMS_TUNE_BWD_K");
+    const int unroll = std::min(2, choose_unroll(sh.L, sizeof(S), K, "FMS_TUNE_BWD_U"));
+    const int64_t ctas = K == 1 ? (sh.rows + fms::kWarpsPerCta - 1) / fms::kWarpsPerCta : sh.rows;
+    if (ctas > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;
+#define FMS_LAUNCH_FM_BWD(G, UU, KK)                                                               \
+    fms::plain_backward_kernel<S, G, UU, true, KK, false, true>                                    \
+        <<<static_cast<unsigned>(ctas), fms::Coop<KK>::kThreads, 0, st>>>(                         \
+            static_cast<const S *>(gates), static_cast<const S *>(states),                         \
+            static_cast<const S *>(grad_states), h0, nullptr, nullptr, nullptr, grad_h0, nullptr,  \
+            sh.rows, sh.L, 1, sh.L, static_cast<const S *>(tokens), acc_gates, acc_tokens, sh.M, sh.D)
+#define FMS_LAUNCH_FM_BWD_K(G, UU)                                                                 \
+    switch (K) {                                                                                   \
+        case 1: FMS_LAUNCH_FM_BWD(G, UU, 1); break;                                                \
+        case 2: FMS_LAUNCH_FM_BWD(G, UU, 2); break;                                                \
+        case 4: FMS_LAUNCH_FM_BWD(G, UU, 4); break;                                                \
+        default: FMS_LAUNCH_FM_BWD(G, UU, 8); break;                                               \
+    }
+    if (!aligned) { FMS_LAUNCH_FM_BWD_K(true, 1) }
+    else if (unroll == 2) { FMS_LAUNCH_FM_BWD_K(false, 2) }
+    else { FMS_LAUNCH_FM_BWD_K(false, 1) }
+#undef FMS_LAUNCH_FM_BWD_K
+#undef FMS_LAUNCH_FM_BWD
+    return check_launch();
+}
+
+template <typename S>
+int launch_cast(const float *src, void *dst, int64_t n, cudaStream_t st) {
+    if (n == 0) return FMS_OK;
+    const int64_t blocks = (n + 255) / 256;
+    if (blocks > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;
+    fms::cast_from_f32_kernel<S><<<static_cast<unsigned>(blocks), 256, 0, st>>>(src, static_cast<S *>(dst), n);
+    return check_launch();
+}
+
+// 16-byte alignment of every row of every tensor involved (rows are L elements long).
+template <typename... Ptrs>
+int fm_alignment(bool &aligned, int64_t L, int dtype, Ptrs... big) {
+    const size_t es = elem_size(dtype);
+    const void *ptrs[] = {big...};
+    aligned = (static_cast<uint64_t>(L) * es) % 16 == 0;
+    for (const void *p : ptrs) {
+        if (!p) return FMS_ERR_NULL_POINTER;
+        if (!aligned_to(p, es)) return FMS_ERR_MISALIGNED;
+        aligned = aligned && aligned_to(p, 16);
+    }
+    return FMS_OK;
+}
+
+inline size_t fm_acc_elems(const FmShape &sh) {
+    return static_cast<size_t>(sh.B) * static_cast<size_t>(sh.M + sh.D) * static_cast<size_t>(sh.L);
+}
+
+}  // namespace
+
+FMS_EXPORT int fms_fm_forward(const void *gates, const void *tokens, const float *h0, void *states,
+                              int64_t B, int64_t M, int64_t D, int64_t L, int dtype, fms_stream_t stream) {
+    FmShape sh;
+    if (int rc = make_fm_shape(sh, B, M, D, L, dtype)) return rc;
+    if (sh.rows == 0 || L == 0) return FMS_OK;
+    bool aligned = false;
+    if (int rc = fm_alignment(aligned, L, dtype, gates, tokens, static_cast<const void *>(states))) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    FMS_DISPATCH_DTYPE(dtype, (launch_fm_forward<S>(sh, aligned, gates, tokens, h0, states, st)));
+}
+
+FMS_EXPORT size_t fms_fm_backward_workspace_bytes(int64_t B, int64_t M, int64_t D, int64_t L, int dtype) {
+    FmShape sh;
+    if (make_fm_shape(sh, B, M, D, L, dtype) != FMS_OK || sh.rows == 0 || L == 0) return 0;
+    if (dtype == FMS_F32) return 0;  // fp32 outputs are accumulated in place
+    return (fm_acc_elems(sh) * sizeof(float) + 255) / 256 * 256;
+}
+
+FMS_EXPORT int fms_fm_backward(const void *gates, const void *tokens, const void *states,
+                               const void *grad_states, const float *h0, void *grad_gates, void *grad_tokens,
+                               float *grad_h0, int64_t B, int64_t M, int64_t D, int64_t L, int dtype,
+                               void *workspace, size_t workspace_bytes, fms_stream_t stream) {
+    FmShape sh;
+    if (int rc = make_fm_shape(sh, B, M, D, L, dtype)) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t es = elem_size(dtype);
+    const size_t n_g = static_cast<size_t>(B) * M * L, n_x = static_cast<size_t>(B) * D * L;
+    if (sh.rows == 0 || L == 0) {
+        // a sum over an empty axis is zero
+        if (grad_gates && n_g) if (int rc = record(cudaMemsetAsync(grad_gates, 0, n_g * es, st))) return rc;
+        if (grad_tokens && n_x) if (int rc = record(cudaMemsetAsync(grad_tokens, 0, n_x * es, st))) return rc;
+        return FMS_OK;
+    }
+    bool aligned = false;
+    if (int rc = fm_alignment(aligned, L, dtype, gates, tokens, states, grad_states,
+                              static_cast<const void *>(grad_gates), static_cast<const void *>(grad_tokens)))
+        return rc;
+    float *acc_g, *acc_x;
+    if (dtype == FMS_F32) {
+        acc_g = static_cast<float *>(grad_gates);
+        acc_x = static_cast<float *>(grad_tokens);
+        if (int rc = record(cudaMemsetAsync(acc_g, 0, n_g * sizeof(float), st))) return rc;
+        if (int rc = record(cudaMemsetAsync(acc_x, 0, n_x * sizeof(float), st))) return rc;
+    } else {
+        const size_t need = fms_fm_backward_workspace_bytes(B, M, D, L, dtype);
+        if (!workspace || !aligned_to(workspace, 16) || workspace_bytes < need) return FMS_ERR_WORKSPACE;
+        acc_g = static_cast<float *>(workspace);
+        acc_x = acc_g + n_g;
+        if (int rc = record(cudaMemsetAsync(acc_g, 0, (n_g + n_x) * sizeof(float), st))) return rc;
+    }
+    // vector reductions need 16-byte aligned fp32 rows as well
+    aligned = aligned && (static_cast<uint64_t>(L) * sizeof(float)) % 16 == 0 && aligned_to(acc_g, 16) &&
+              aligned_to(acc_x, 16);
+    {
+        auto pass = [&]() -> int {
+            FMS_DISPATCH_DTYPE(dtype, (launch_fm_backward<S>(sh, aligned, gates, tokens, states, grad_states, h0,
+                                                             acc_g, acc_x, grad_h0, st)));
+        };
+        if (int rc = pass()) return rc;
+    }
+    if (dtype == FMS_F32) return FMS_OK;
+    {
+        auto cast_g = [&]() -> int { FMS_DISPATCH_DTYPE(dtype, (launch_cast<S>(acc_g, grad_gates, n_g, st))); };
+        if (int rc = cast_g()) return rc;
+    }
+    FMS_DISPATCH_DTYPE(dtype, (launch_cast<S>(acc_x, grad_tokens, n_x, st)));
 }
 
 // ------------------------------------------------------------------ split inside one GPU ----

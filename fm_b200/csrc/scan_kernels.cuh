@@ -178,6 +178,28 @@ __device__ __forceinline__ void store_vec(S *__restrict__ row, int64_t v, int64_
     }
 }
 
+// Accumulate one lane's E fp32 values into an fp32 buffer (FM-mode gradient reductions): vector
+// reductions (red.global.add.v4.f32) when the vector is wholly inside the row and 16-byte
+// aligned, scalar atomics under the mask otherwise.
+template <int E, bool GENERIC>
+__device__ __forceinline__ void red_vec(float *__restrict__ row, int64_t v, int64_t T, const float (&f)[E]) {
+    bool whole = (v >= 0) && (v + E <= T);
+    if constexpr (GENERIC) whole = whole && ((reinterpret_cast<uintptr_t>(row + v) & 15u) == 0);
+    if (whole) {
+#pragma unroll
+        for (int k = 0; k < E; k += 4)
+            asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(row + v + k), "f"(f[k]),
+                         "f"(f[k + 1]), "f"(f[k + 2]), "f"(f[k + 3])
+                         : "memory");
+    } else if constexpr (GENERIC) {
+#pragma unroll
+        for (int i = 0; i < E; ++i) {
+            const int64_t t = v + i;
+            if (t >= 0 && t < T) atomicAdd(row + t, f[i]);
+        }
+    }
+}
+
 // Row geometry shared by all kernels: where the first (virtual) vector of the row starts and
 // how many groups of U tiles cover it.
 template <typename S, bool GENERIC>
@@ -245,15 +267,21 @@ struct Coop {
 // at the last group of a unit already fetches the first group of the next one, so the load
 // pipeline never drains at a row boundary.  The masked and the segmented instantiations get one
 // unit per warp/CTA (their geometry changes from unit to unit).
-template <typename S, bool GENERIC, int U, bool WRITE, int K, bool SEG>
+//
+// FM = true is the reference's literal operator (fm/scan/fm_pytorch.py:19-42): unit (b,m,d) reads
+// gate row (b,m) and token row (b,d), the token is weighted by 1 - gate as it is unpacked
+// (fm/scan/fm_scan.cuh:116), and the state row (b,m,d) is written.  The gate and token rows are
+// re-read D and M times, from L2.
+template <typename S, bool GENERIC, int U, bool WRITE, int K, bool SEG, bool FM>
 __global__ void __launch_bounds__(Coop<K>::kThreads)
 plain_forward_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
                      const float *__restrict__ h0, S *__restrict__ states,
                      float *__restrict__ h_last, float *__restrict__ P_out, int64_t R, int64_t T,
-                     int64_t nseg, int64_t seg_len) {
+                     int64_t nseg, int64_t seg_len, int64_t M, int64_t D) {
+    static_assert(!(FM && SEG), "FM mode has no segmented variant");
     constexpr int E = Store<S>::E;
     constexpr int TILE = 32 * E;
-    constexpr bool PERSIST = !GENERIC && !SEG;
+    constexpr bool PERSIST = !GENERIC && !SEG && !FM;
     constexpr int64_t SUPER = static_cast<int64_t>(TILE) * U * K;
     __shared__ float2 agg[2][K > 1 ? K : 1];
     const int lane = threadIdx.x & 31;
@@ -264,10 +292,18 @@ plain_forward_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
 
     const Unit q = unit_of<SEG>(unit, T, nseg, seg_len);
     const int64_t L = q.len;  // PERSIST: every unit has length T
-    int64_t off = q.offset;   // element offset of the current unit
-    const int64_t vbase = row_phase<S, GENERIC>(gates + off);
-    const bool ph_x = !GENERIC || same_phase16(gates + off, tokens + off);
-    const bool ph_h = !GENERIC || !WRITE || same_phase16(gates + off, states + off);
+    int64_t off = q.offset;   // element offset of the current unit (states; also gates/tokens unless FM)
+    int64_t goff_fm = 0, toff_fm = 0;
+    if constexpr (FM) {
+        const int64_t bm = unit / D, d = unit - bm * D, b = bm / M;
+        goff_fm = bm * T;
+        toff_fm = (b * D + d) * T;
+    }
+#define FMS_GOFF (FM ? goff_fm : off)
+#define FMS_TOFF (FM ? toff_fm : off)
+    const int64_t vbase = row_phase<S, GENERIC>(gates + FMS_GOFF);
+    const bool ph_x = !GENERIC || same_phase16(gates + FMS_GOFF, tokens + FMS_TOFF);
+    const bool ph_h = !GENERIC || !WRITE || same_phase16(gates + FMS_GOFF, states + off);
     const int64_t ngroups = (L - vbase + SUPER - 1) / SUPER;
     const int64_t v0 = vbase + static_cast<int64_t>(w) * (TILE * U) + lane * E;
 
@@ -279,8 +315,8 @@ plain_forward_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
     uint4 ra[U], rx[U];
 #pragma unroll
     for (int j = 0; j < U; ++j) {
-        ra[j] = load_vec<S, GENERIC>(gates + off, v + j * TILE, L, true, Store<S>::kOne);
-        rx[j] = load_vec<S, GENERIC>(tokens + off, v + j * TILE, L, ph_x, 0u);
+        ra[j] = load_vec<S, GENERIC>(gates + FMS_GOFF, v + j * TILE, L, true, Store<S>::kOne);
+        rx[j] = load_vec<S, GENERIC>(tokens + FMS_TOFF, v + j * TILE, L, ph_x, 0u);
     }
 
     for (unsigned it = 0;; ++it) {
@@ -300,8 +336,8 @@ plain_forward_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
         uint4 na[U], nx[U];
 #pragma unroll
         for (int j = 0; j < U; ++j) {
-            na[j] = load_vec<S, GENERIC>(gates + noff, nv + j * TILE, L, true, Store<S>::kOne);
-            nx[j] = load_vec<S, GENERIC>(tokens + noff, nv + j * TILE, L, ph_x, 0u);
+            na[j] = load_vec<S, GENERIC>(gates + (FM ? goff_fm : noff), nv + j * TILE, L, true, Store<S>::kOne);
+            nx[j] = load_vec<S, GENERIC>(tokens + (FM ? toff_fm : noff), nv + j * TILE, L, ph_x, 0u);
         }
 
         float fa[U][E], fx[U][E], A[U], H[U];
@@ -309,6 +345,10 @@ plain_forward_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
         for (int j = 0; j < U; ++j) {
             Store<S>::unpack(ra[j], fa[j]);
             Store<S>::unpack(rx[j], fx[j]);
+            if constexpr (FM) {
+#pragma unroll
+                for (int i = 0; i < E; ++i) fx[j][i] = (1.f - fa[j][i]) * fx[j][i];
+            }
             A[j] = fa[j][0];
             H[j] = fx[j][0];
 #pragma unroll
@@ -402,6 +442,8 @@ plain_forward_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
         off = noff;
         v = nv;
     }
+#undef FMS_GOFF
+#undef FMS_TOFF
 }
 
 // ---------------------------------------------------------------- backward / reverse reduce -
@@ -409,17 +451,26 @@ plain_forward_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
 // grad_tokens_t = delta_t; grad_gates_t = delta_t * h_{t-1}; grad_h0 = c_0.
 // WRITE = false produces only S_rev = c_0 (from carry_in = 0) and P = prod a.
 // Same persistence rule as the forward kernel.
-template <typename S, bool GENERIC, int U, bool WRITE, int K, bool SEG>
+//
+// FM = true (needs WRITE): unit (b,m,d) additionally reads token row (b,d); instead of storing two
+// full rows it ACCUMULATES into fp32 buffers
+//     acc_gates [b,m,t] += (h_{t-1} - x_t) * delta_t     (sum over d; fm/scan/fm_scan.cuh:188-207
+//                                                          followed by fm/scan/fm_scan.py:76)
+//     acc_tokens[b,d,t] += (1 - g_t) * delta_t           (sum over m; fm_scan.cuh:184-185, fm_scan.py:78)
+// with vector reductions, so the reference's two (B,M,D,L) temporaries never exist.
+template <typename S, bool GENERIC, int U, bool WRITE, int K, bool SEG, bool FM>
 __global__ void __launch_bounds__(Coop<K>::kThreads)
 plain_backward_kernel(const S *__restrict__ gates, const S *__restrict__ states,
                       const S *__restrict__ grad_states, const float *__restrict__ h0,
                       const float *__restrict__ carry_in, S *__restrict__ grad_gates,
                       S *__restrict__ grad_tokens, float *__restrict__ grad_h0,
                       float *__restrict__ P_out, int64_t R, int64_t T, int64_t nseg,
-                      int64_t seg_len) {
+                      int64_t seg_len, const S *__restrict__ tokens_fm, float *__restrict__ acc_gates,
+                      float *__restrict__ acc_tokens, int64_t M, int64_t D) {
+    static_assert(!(FM && SEG) && !(FM && !WRITE), "FM mode: whole rows, full backward only");
     constexpr int E = Store<S>::E;
     constexpr int TILE = 32 * E;
-    constexpr bool PERSIST = !GENERIC && !SEG;
+    constexpr bool PERSIST = !GENERIC && !SEG && !FM;
     constexpr int64_t SUPER = static_cast<int64_t>(TILE) * U * K;
     __shared__ float2 agg[2][K > 1 ? K : 1];
     const int lane = threadIdx.x & 31;
@@ -431,11 +482,19 @@ plain_backward_kernel(const S *__restrict__ gates, const S *__restrict__ states,
     const Unit q = unit_of<SEG>(unit, T, nseg, seg_len);
     const int64_t L = q.len;
     int64_t off = q.offset;
-    const int64_t vbase = row_phase<S, GENERIC>(gates + off);
-    const bool ph_g = !GENERIC || same_phase16(gates + off, grad_states + off);
-    const bool ph_h = !GENERIC || !WRITE || same_phase16(gates + off, states + off);
-    const bool ph_ga = !GENERIC || !WRITE || same_phase16(gates + off, grad_gates + off);
-    const bool ph_gx = !GENERIC || !WRITE || same_phase16(gates + off, grad_tokens + off);
+    int64_t goff_fm = 0, toff_fm = 0;
+    if constexpr (FM) {
+        const int64_t bm = unit / D, d = unit - bm * D, b = bm / M;
+        goff_fm = bm * T;
+        toff_fm = (b * D + d) * T;
+    }
+#define FMS_GOFF (FM ? goff_fm : off)
+    const int64_t vbase = row_phase<S, GENERIC>(gates + FMS_GOFF);
+    const bool ph_g = !GENERIC || same_phase16(gates + FMS_GOFF, grad_states + off);
+    const bool ph_h = !GENERIC || !WRITE || same_phase16(gates + FMS_GOFF, states + off);
+    const bool ph_ga = !GENERIC || !WRITE || FM || same_phase16(gates + off, grad_gates + off);
+    const bool ph_gx = !GENERIC || !WRITE || FM || same_phase16(gates + off, grad_tokens + off);
+    const bool ph_x = !GENERIC || !FM || same_phase16(gates + FMS_GOFF, tokens_fm + toff_fm);
     const int64_t ngroups = (L - vbase + SUPER - 1) / SUPER;
     // this lane's first vector in the LAST group of a unit (the first one the reverse walk visits)
     const int64_t v_last = vbase + (ngroups - 1) * SUPER + static_cast<int64_t>(w) * (TILE * U) + lane * E;
@@ -464,16 +523,17 @@ plain_backward_kernel(const S *__restrict__ gates, const S *__restrict__ states,
 
     int64_t v = v_last;
     int64_t g = ngroups - 1;
-    uint4 ra[U], rg[U], rh[U];
+    uint4 ra[U], rg[U], rh[U], rx[FM ? U : 1];
     float halo[U];
 #pragma unroll
     for (int j = 0; j < U; ++j) {
-        ra[j] = load_vec<S, GENERIC>(gates + off, v + j * TILE, L, true, Store<S>::kOne);
+        ra[j] = load_vec<S, GENERIC>(gates + FMS_GOFF, v + j * TILE, L, true, Store<S>::kOne);
         rg[j] = load_vec<S, GENERIC>(grad_states + off, v + j * TILE, L, ph_g, 0u);
         if constexpr (WRITE) {
             rh[j] = load_vec<S, GENERIC>(states + off, v + j * TILE, L, ph_h, 0u);
             halo[j] = load_halo(off, v + j * TILE);
         }
+        if constexpr (FM) rx[j] = load_vec<S, GENERIC>(tokens_fm + toff_fm, v + j * TILE, L, ph_x, 0u);
     }
 
     for (unsigned it = 0;; ++it) {
@@ -488,17 +548,18 @@ plain_backward_kernel(const S *__restrict__ gates, const S *__restrict__ states,
                 more = false;
             }
         }
-        uint4 na[U], ng[U], nh[U];
+        uint4 na[U], ng[U], nh[U], nx[FM ? U : 1];
         float nhalo[U];
 #pragma unroll
         for (int j = 0; j < U; ++j) {
             const int64_t vv = more ? nv + j * TILE : L;  // L = "outside" for every path
-            na[j] = load_vec<S, GENERIC>(gates + noff, vv, L, true, Store<S>::kOne);
+            na[j] = load_vec<S, GENERIC>(gates + (FM ? goff_fm : noff), vv, L, true, Store<S>::kOne);
             ng[j] = load_vec<S, GENERIC>(grad_states + noff, vv, L, ph_g, 0u);
             if constexpr (WRITE) {
                 nh[j] = load_vec<S, GENERIC>(states + noff, vv, L, ph_h, 0u);
                 nhalo[j] = more ? load_halo(noff, vv) : 0.f;
             }
+            if constexpr (FM) nx[j] = load_vec<S, GENERIC>(tokens_fm + toff_fm, vv, L, ph_x, 0u);
         }
 
         float fa[U][E], fg[U][E], A[U], C[U];
@@ -567,6 +628,8 @@ plain_backward_kernel(const S *__restrict__ gates, const S *__restrict__ states,
                 if (lane == 0) hprev0 = (v + j * TILE - 1 >= 0) ? halo[j] : h_before;
                 float c = fmaf(eA, carry, eC);  // c just after this lane's elements
                 float dx[E], da[E];
+                float fxm[FM ? E : 1];
+                if constexpr (FM) Store<S>::unpack(rx[j], fxm);
 #pragma unroll
                 for (int i = E - 1; i >= 0; --i) {
                     const float delta = fg[j][i] + c;
@@ -575,11 +638,21 @@ plain_backward_kernel(const S *__restrict__ gates, const S *__restrict__ states,
                     if constexpr (GENERIC) {
                         if (v + j * TILE + i == 0) hp = h_before;  // unit start inside a vector
                     }
-                    dx[i] = delta;
-                    da[i] = delta * hp;
+                    if constexpr (FM) {
+                        dx[i] = (1.f - fa[j][i]) * delta;
+                        da[i] = delta * (hp - fxm[i]);
+                    } else {
+                        dx[i] = delta;
+                        da[i] = delta * hp;
+                    }
                 }
-                store_vec<S, GENERIC>(grad_tokens + off, v + j * TILE, L, ph_gx, Store<S>::pack(dx));
-                store_vec<S, GENERIC>(grad_gates + off, v + j * TILE, L, ph_ga, Store<S>::pack(da));
+                if constexpr (FM) {
+                    red_vec<E, GENERIC>(acc_tokens + toff_fm, v + j * TILE, L, dx);
+                    red_vec<E, GENERIC>(acc_gates + goff_fm, v + j * TILE, L, da);
+                } else {
+                    store_vec<S, GENERIC>(grad_tokens + off, v + j * TILE, L, ph_gx, Store<S>::pack(dx));
+                    store_vec<S, GENERIC>(grad_gates + off, v + j * TILE, L, ph_ga, Store<S>::pack(da));
+                }
             } else if constexpr (K == 1) {
                 prod *= tA;
             }
@@ -609,9 +682,22 @@ plain_backward_kernel(const S *__restrict__ gates, const S *__restrict__ states,
                 rh[j] = nh[j];
                 halo[j] = nhalo[j];
             }
+            if constexpr (FM) rx[j] = nx[j];
         }
         off = noff;
         v = nv;
+    }
+#undef FMS_GOFF
+}
+
+// fp32 accumulators -> storage type (FM-mode gradients with 16-bit storage).
+template <typename S>
+__global__ void cast_from_f32_kernel(const float *__restrict__ src, S *__restrict__ dst, int64_t n) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n) {
+        if constexpr (sizeof(S) == 4) dst[i] = src[i];
+        else if constexpr (Store<S>::kOne == 0x3f803f80u) dst[i] = __float2bfloat16(src[i]);
+        else dst[i] = __float2half(src[i]);
     }
 }
 

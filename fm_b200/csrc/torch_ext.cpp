@@ -10,7 +10,9 @@
 // installs a device guard, launches on the current stream of the tensors' device, and checks
 // the launch.
 //
-// Layout: all big tensors are (B, D, T) -- one independent scan per (b, d) row.
+// Layout: all big tensors are (B, D, T) -- one independent scan per (b, d) row -- or, when the
+// output has one more axis than the gates, the reference's own FM layout
+// gates (B,M,L) x tokens (B,D,L) -> states (B,M,D,L) with the 1 - gate token weight.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
@@ -66,10 +68,35 @@ int64_t rows_of_shape(const at::Tensor &t) {
 
 // Forward.  gates, tokens, out: (..., T) of one dtype; initial_state: (...), None or empty (= zeros,
 // which is what fm/scan/fm_scan.py:48 passes by default).  Returns `out`.
+// FM mode (the reference's own shapes): gates (B,M,L), tokens (B,D,L), initial_state (B,M,D) or
+// empty, out (B,M,D,L).  Selected when `out` has one more axis than `gates`.
+static at::Tensor fm_mode_forward(const at::Tensor &gates, const at::Tensor &tokens,
+                                  const c10::optional<at::Tensor> &initial_state, const at::Tensor &out) {
+    TORCH_CHECK(gates.dim() == 3 && tokens.dim() == 3 && out.dim() == 4,
+                "FM mode expects gates (B,M,L), tokens (B,D,L), out (B,M,D,L)");
+    const int64_t B = gates.size(0), M = gates.size(1), L = gates.size(2), D = tokens.size(1);
+    TORCH_CHECK(tokens.size(0) == B && tokens.size(2) == L, "tokens must be (B,D,L) with the B and L of gates");
+    TORCH_CHECK(out.size(0) == B && out.size(1) == M && out.size(2) == D && out.size(3) == L,
+                "out must be (B,M,D,L)");
+    for (const at::Tensor *t : {&tokens, &out}) {
+        TORCH_CHECK(t->is_cuda() && t->is_contiguous() && t->scalar_type() == gates.scalar_type() &&
+                        t->device() == gates.device(),
+                    "tokens and out must be contiguous CUDA tensors with the dtype and device of gates");
+    }
+    const int dtype = dtype_tag(gates);
+    const c10::cuda::CUDAGuard guard(gates.device());
+    at::Tensor h0 = carry_f32(initial_state, B * M * D, gates, "initial_state");
+    check_status(fms_fm_forward(gates.data_ptr(), tokens.data_ptr(), fptr(h0), out.data_ptr(), B, M, D, L, dtype,
+                                at::cuda::getCurrentCUDAStream().stream()),
+                 "fm_scan_forward");
+    return out;
+}
+
 at::Tensor fm_scan_forward(const at::Tensor &gates, const at::Tensor &tokens,
                            const c10::optional<at::Tensor> &initial_state, const at::Tensor &out) {
     TORCH_CHECK(gates.is_cuda(), "gates must be a CUDA tensor");
     TORCH_CHECK(gates.is_contiguous(), "gates must be contiguous");
+    if (out.dim() == gates.dim() + 1) return fm_mode_forward(gates, tokens, initial_state, out);
     check_big(tokens, gates, "tokens");
     check_big(out, gates, "out");
     const int dtype = dtype_tag(gates);
@@ -140,6 +167,46 @@ void fm_scan_backward_ex(const at::Tensor &gates, const at::Tensor &outGrad,
                  "fm_scan_backward");
 }
 
+// FM-mode backward with fused reductions: tokenGradOut (B,D,L), gateGradOut (B,M,L) -- the shapes
+// the reference's Python reaches only after materialising two (B,M,D,L) tensors and summing them
+// (fm/scan/fm_scan.py:70-78).  initial_state is the forward h0; grad_initial_state (B,M,D) fp32.
+void fm_scan_backward_fm(const at::Tensor &gates, const at::Tensor &outGrad, const at::Tensor &tokenGradOut,
+                         const at::Tensor &cached_output, const at::Tensor &input_tokens,
+                         const at::Tensor &gateGradOut, const c10::optional<at::Tensor> &initial_state,
+                         const c10::optional<at::Tensor> &grad_initial_state_opt) {
+    TORCH_CHECK(gates.is_cuda() && gates.is_contiguous() && gates.dim() == 3, "gates must be a contiguous CUDA (B,M,L) tensor");
+    TORCH_CHECK(input_tokens.dim() == 3 && cached_output.dim() == 4, "expected tokens (B,D,L) and states (B,M,D,L)");
+    const int64_t B = gates.size(0), M = gates.size(1), L = gates.size(2), D = input_tokens.size(1);
+    auto same = [&](const at::Tensor &t, at::IntArrayRef shape, const char *name) {
+        TORCH_CHECK(t.is_cuda() && t.is_contiguous() && t.scalar_type() == gates.scalar_type() &&
+                        t.device() == gates.device() && t.sizes() == shape,
+                    name, " must be a contiguous CUDA tensor of shape ", shape, " with the dtype of gates");
+    };
+    same(input_tokens, {B, D, L}, "input_tokens");
+    same(cached_output, {B, M, D, L}, "cached_output");
+    same(outGrad, {B, M, D, L}, "outGrad");
+    same(tokenGradOut, {B, D, L}, "tokenGradOut (fused reduction over M)");
+    same(gateGradOut, {B, M, L}, "gateGradOut (fused reduction over D)");
+    const int dtype = dtype_tag(gates);
+    const c10::cuda::CUDAGuard guard(gates.device());
+    at::Tensor h0 = carry_f32(initial_state, B * M * D, gates, "initial_state");
+    float *gh0 = nullptr;
+    if (grad_initial_state_opt.has_value() && grad_initial_state_opt->defined() && grad_initial_state_opt->numel() > 0) {
+        const at::Tensor &g = *grad_initial_state_opt;
+        TORCH_CHECK(g.is_cuda() && g.is_contiguous() && g.scalar_type() == at::kFloat && g.numel() == B * M * D,
+                    "grad_initial_state must be a contiguous fp32 CUDA tensor of B*M*D elements");
+        gh0 = g.data_ptr<float>();
+    }
+    const size_t scratch = fms_fm_backward_workspace_bytes(B, M, D, L, dtype);
+    at::Tensor ws;
+    if (scratch > 0) ws = at::empty({static_cast<int64_t>(scratch)}, gates.options().dtype(at::kByte));
+    check_status(fms_fm_backward(gates.data_ptr(), input_tokens.data_ptr(), cached_output.data_ptr(),
+                                 outGrad.data_ptr(), fptr(h0), gateGradOut.data_ptr(), tokenGradOut.data_ptr(),
+                                 gh0, B, M, D, L, dtype, scratch ? ws.data_ptr() : nullptr, scratch,
+                                 at::cuda::getCurrentCUDAStream().stream()),
+                 "fm_scan_backward");
+}
+
 // Backward with the reference's seven arguments.  firstPropGrad seeds the reverse scan
 // (fm/scan/fm_scan.cuh:120-122); the reference passes zeros (fm/scan/fm_scan.py:65).
 // input_tokens is accepted for signature compatibility and not read: with the token weight
@@ -150,7 +217,12 @@ void fm_scan_backward(const at::Tensor &gates, const at::Tensor &outGrad,
                       const c10::optional<at::Tensor> &firstPropGrad, const at::Tensor &tokenGradOut,
                       const at::Tensor &cached_output, const c10::optional<at::Tensor> &input_tokens,
                       const at::Tensor &gateGradOut) {
-    (void)input_tokens;
+    if (cached_output.dim() == gates.dim() + 1) {  // FM mode: outputs already reduced, h_{-1} = 0
+        TORCH_CHECK(input_tokens.has_value() && input_tokens->defined(), "FM mode needs input_tokens");
+        fm_scan_backward_fm(gates, outGrad, tokenGradOut, cached_output, *input_tokens, gateGradOut,
+                            c10::nullopt, c10::nullopt);
+        return;
+    }
     fm_scan_backward_ex(gates, outGrad, firstPropGrad, tokenGradOut, cached_output, gateGradOut,
                         c10::nullopt, c10::nullopt);
 }
@@ -160,5 +232,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("fm_scan_forward", &fm_scan_forward, "scan forward (writes and returns out)");
     m.def("fm_scan_backward", &fm_scan_backward, "scan backward, reference signature");
     m.def("fm_scan_backward_ex", &fm_scan_backward_ex, "scan backward with h0 / carry_in / grad_h0");
+    m.def("fm_scan_backward_fm", &fm_scan_backward_fm, "FM-mode backward with fused reductions");
     m.def("abi_version", []() { return fms_version(); });
 }

@@ -1,0 +1,34 @@
+"""The Factorization-Memory layer around the scan, mirroring ``fm_memory`` of the reference
+(fm/scan/fm_scan.py:102-133): same arguments, same returns.
+
+Everything except the scan is stock torch, as in the reference; the scan is this package's
+FM-mode op (one fused backward kernel instead of two (B,M,D,L) temporaries and two sums).
+"""
+from __future__ import annotations
+
+import torch
+
+from .fm_scan import fm_scan
+
+
+def fm_memory(alpha, update_scale, output_scale, inputs, initial_state=None, mem_norm=True, norm_eps=1e-6):
+    """
+    alpha: (B, L, M)   update_scale: (B, L, 1)   output_scale: (B, L, 1)   inputs: (B, L, D)
+    initial_state: (B, M, D)   mem_norm: bool   norm_eps: float
+
+    return: output (B, L, D), memory_states (B, M, D, L)
+    """
+    update_weight = alpha * update_scale                                 # fm_scan.py:117
+    tokens = inputs.transpose(1, 2).contiguous()                         # (B, D, L)  fm_scan.py:118
+    update_weight = update_weight.transpose(1, 2).contiguous()           # (B, M, L)  fm_scan.py:119
+    decay_weight = 1.0 - update_weight                                   # fm_scan.py:120
+
+    memory_states = fm_scan(decay_weight, tokens, initial_state, mode="fm")  # (B, M, D, L)  fm_scan.py:122
+
+    if mem_norm:                                                         # RMS norm over D, fm_scan.py:125-127
+        memory_rms = torch.rsqrt(torch.mean(memory_states ** 2, dim=2, keepdim=True) + norm_eps)
+        memory_states = memory_states * memory_rms
+
+    output_weight = alpha * output_scale                                 # fm_scan.py:130
+    output = torch.einsum('blm,bmdl->bld', output_weight, memory_states).contiguous()  # fm_scan.py:131
+    return output, memory_states

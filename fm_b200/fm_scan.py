@@ -53,6 +53,52 @@ def fm_scan_backward_ex(gates, outGrad, carry_in, tokenGradOut, cached_output, g
                                            gateGradOut, initial_state, grad_initial_state)
 
 
+def fm_scan_backward_fm(gates, outGrad, tokenGradOut, cached_output, input_tokens, gateGradOut,
+                        initial_state=None, grad_initial_state=None):
+    """FM-mode backward with the reductions over D and M fused into the kernel."""
+    return _load_ext().fm_scan_backward_fm(gates, outGrad, tokenGradOut, cached_output, input_tokens,
+                                           gateGradOut, initial_state, grad_initial_state)
+
+
+class FM_Scan_Outer(torch.autograd.Function):
+    """The reference's operator in its own layout (fm/scan/fm_scan.py:37-81):
+    gates (B,M,L), tokens (B,D,L), initial_state (B,M,D) -> states (B,M,D,L) with
+    ``h = g*h + (1-g)*x``.  Backward returns ``d_gates (B,M,L)``, ``d_tokens (B,D,L)`` and
+    ``d_initial_state`` straight from one kernel: the two (B,M,D,L) temporaries and the two sums
+    of the reference's backward (fm/scan/fm_scan.py:70-78) are fused away."""
+
+    @staticmethod
+    def forward(ctx, gates, tokens, initial_state=None):
+        B1, M, L1 = gates.shape
+        B, D, L = tokens.shape
+        assert L1 == L
+        assert B == B1
+        assert gates.is_contiguous()
+        assert tokens.is_contiguous()
+        if initial_state is not None:
+            assert initial_state.shape == (B, M, D)
+            assert initial_state.is_contiguous()
+        output = torch.empty([B, M, D, L], device=gates.device, dtype=gates.dtype)
+        states = fm_scan_forward(gates, tokens, initial_state, output)
+        ctx.save_for_backward(tokens, gates, states, initial_state)
+        ctx.h0_needs_grad = initial_state is not None and ctx.needs_input_grad[2]
+        return states
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        tokens, gates, states, initial_state = ctx.saved_tensors
+        grad_output = grad_output.contiguous()
+        d_gates = torch.empty_like(gates)
+        d_tokens = torch.empty_like(tokens)
+        d_h0 = None
+        if ctx.h0_needs_grad:
+            d_h0 = torch.empty(initial_state.shape, device=gates.device, dtype=torch.float32)
+        fm_scan_backward_fm(gates, grad_output, d_tokens, states, tokens, d_gates, initial_state, d_h0)
+        if d_h0 is not None:
+            d_h0 = d_h0.to(initial_state.dtype)
+        return d_gates, d_tokens, d_h0
+
+
 class FM_Scan(torch.autograd.Function):
     @staticmethod
     def forward(ctx, gates, tokens, initial_state=None):
@@ -84,16 +130,24 @@ class FM_Scan(torch.autograd.Function):
         return d_gates, d_tokens, d_h0
 
 
-def fm_scan(gates, tokens, initial_state=None):
-    """Solve the first-order recurrence ``h_t = a_t * h_{t-1} + x_t`` along the last axis.
+def fm_scan(gates, tokens, initial_state=None, mode="plain"):
+    """Solve the first-order recurrence along the last axis.
 
-    Arguments:
+    ``mode="plain"`` (default): ``h_t = a_t * h_{t-1} + x_t`` on independent rows.
         gates (torch.Tensor): a, shape (B, D, T), contiguous CUDA tensor, fp32 / fp16 / bf16.
             Any T >= 1 (the reference required a power of two in [32, 131072]).
         tokens (torch.Tensor): x, same shape, dtype and device.
         initial_state (torch.Tensor, optional): h_{-1}, shape (B, D); zeros when omitted.
+        Returns states h, shape (B, D, T), dtype of ``gates``.
 
-    Returns:
-        torch.Tensor: states h, shape (B, D, T), dtype of ``gates``.  Arithmetic is fp32.
+    ``mode="fm"``: the reference's operator in its own layout (fm/scan/fm_scan.py:84-99),
+        ``h[b,m,d,t] = g[b,m,t] * h[b,m,d,t-1] + (1 - g[b,m,t]) * x[b,d,t]``
+        gates (B, M, L), tokens (B, D, L), initial_state (B, M, D) -> states (B, M, D, L).
+
+    Arithmetic is fp32 in both modes.
     """
+    if mode == "fm":
+        return FM_Scan_Outer.apply(gates, tokens, initial_state)
+    if mode != "plain":
+        raise ValueError("mode must be 'plain' or 'fm'")
     return FM_Scan.apply(gates, tokens, initial_state)

@@ -126,6 +126,37 @@ int fms_combine_carries(const float *P, const float *S, const float *carry0, flo
                         float *total, int64_t nchunks, int64_t rows, int reverse,
                         fms_stream_t stream);
 
+/* ------------------------------------------------------------------ FM mode, one GPU ------- */
+
+/*
+ * The reference's literal operator (fm/scan/fm_pytorch.py:19-42, fm/scan/fm_scan.cuh:42-218):
+ *   gates g (B,M,L), tokens x (B,D,L), h0 (B,M,D) fp32 or NULL, states h (B,M,D,L)
+ *   h[b,m,d,t] = g[b,m,t] * h[b,m,d,t-1] + (1 - g[b,m,t]) * x[b,d,t]
+ * Replaces the launch inside fm_scan_forward (fm/scan/fm_scan.cuh:344-358) for that layout; the
+ * token weight is applied in fp32 as the token is unpacked (fm/scan/fm_scan.cuh:116).
+ */
+int fms_fm_forward(const void *gates, const void *tokens, const float *h0, void *states, int64_t B,
+                   int64_t M, int64_t D, int64_t L, int dtype, fms_stream_t stream);
+
+/*
+ * FM backward with the gradient reductions fused: replaces fm_scan_backward
+ * (fm/scan/fm_scan.cuh:361-381) AND the two full-size temporaries plus sums of
+ * fm/scan/fm_scan.py:70-78.
+ *   grad_gates  (B,M,L) = sum_d (h[b,m,d,t-1] - x[b,d,t]) * delta[b,m,d,t]
+ *   grad_tokens (B,D,L) = sum_m (1 - g[b,m,t]) * delta[b,m,d,t]
+ *   grad_h0     (B,M,D) fp32, nullable = g_0 * delta_0
+ * h0 is the forward initial state (h[.,-1]); the reference used zeros there
+ * (fm/scan/fm_scan.cuh:195-196 with fm/scan/fm_scan.py:65).
+ * The sums are accumulated in fp32 with atomic vector reductions (their order, hence the last
+ * bits, can differ from run to run).  fp32 outputs are accumulated in place; fp16/bf16 outputs
+ * need fms_fm_backward_workspace_bytes() of caller scratch (fp32 accumulators, cast at the end).
+ */
+size_t fms_fm_backward_workspace_bytes(int64_t B, int64_t M, int64_t D, int64_t L, int dtype);
+int fms_fm_backward(const void *gates, const void *tokens, const void *states, const void *grad_states,
+                    const float *h0, void *grad_gates, void *grad_tokens, float *grad_h0, int64_t B,
+                    int64_t M, int64_t D, int64_t L, int dtype, void *workspace, size_t workspace_bytes,
+                    fms_stream_t stream);
+
 /* ------------------------------------------------- few, long rows: split inside one GPU ---- */
 
 /*

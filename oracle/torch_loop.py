@@ -59,3 +59,19 @@ def plain_fwd_bwd(gates, tokens, grad_states, initial_state=None):
     h = plain_scan_loop(a, x, initial_state)
     (h * grad_states).sum().backward()
     return h.detach(), a.grad, x.grad
+
+
+def fm_memory_loop(alpha, update_scale, output_scale, inputs, initial_state=None, mem_norm=True, norm_eps=1e-6):
+    """The layer around the scan (fm/scan/fm_scan.py:102-133) on top of ``fm_scan_loop``; same
+    arguments and returns as the reference's ``fm_memory``."""
+    update_weight = alpha * update_scale
+    tokens = inputs.transpose(1, 2).contiguous()
+    update_weight = update_weight.transpose(1, 2).contiguous()
+    decay_weight = 1.0 - update_weight
+    memory_states = fm_scan_loop(decay_weight, tokens, initial_state)
+    if mem_norm:
+        memory_rms = torch.rsqrt(torch.mean(memory_states ** 2, dim=2, keepdim=True) + norm_eps)
+        memory_states = memory_states * memory_rms
+    output_weight = alpha * output_scale
+    output = torch.einsum('blm,bmdl->bld', output_weight, memory_states).contiguous()
+    return output, memory_states

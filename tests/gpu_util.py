@@ -105,3 +105,27 @@ def backward_split(a, h, G, h0=None, carry_in=None, want_gh0=False):
               capi.ptr(carry_in), capi.ptr(ga), capi.ptr(gx), capi.ptr(gh0), rows, T,
               capi.dtype_tag(a.dtype), ws.data_ptr(), nbytes, stream_ptr())
     return (ga, gx, gh0) if want_gh0 else (ga, gx)
+
+
+def fm_forward(g, x, h0=None):
+    """g (B,M,L), x (B,D,L) device tensors; h0 (B,M,D) fp32 or None -> h (B,M,D,L)."""
+    B, M, L = g.shape
+    D = x.shape[1]
+    h = torch.empty((B, M, D, L), device=g.device, dtype=g.dtype)
+    capi.call("fms_fm_forward", capi.ptr(g), capi.ptr(x), capi.ptr(h0), capi.ptr(h), B, M, D, L,
+              capi.dtype_tag(g.dtype), stream_ptr())
+    return h
+
+
+def fm_backward(g, x, h, G, h0=None, want_gh0=False):
+    B, M, L = g.shape
+    D = x.shape[1]
+    dg, dx = torch.empty_like(g), torch.empty_like(x)
+    gh0 = torch.empty((B, M, D), device=g.device, dtype=torch.float32) if want_gh0 else None
+    tag = capi.dtype_tag(g.dtype)
+    nbytes = int(capi.lib().fms_fm_backward_workspace_bytes(B, M, D, L, tag))
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=g.device)
+    capi.call("fms_fm_backward", capi.ptr(g), capi.ptr(x), capi.ptr(h), capi.ptr(G), capi.ptr(h0),
+              capi.ptr(dg), capi.ptr(dx), capi.ptr(gh0), B, M, D, L, tag, ws.data_ptr() if nbytes else None,
+              nbytes, stream_ptr())
+    return (dg, dx, gh0) if want_gh0 else (dg, dx)

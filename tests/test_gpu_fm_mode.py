@@ -1,0 +1,119 @@
+"""FM mode -- the reference's literal operator (B,M,L) x (B,D,L) -> (B,M,D,L) -- on the GPU."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import c_oracle as oc
+from tests import gpu_util as G
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("name", H.golden_names("fm"))
+def test_fm_goldens_from_the_reference(name):
+    g = H.load_golden(name)
+    gd, xd, Gd = G.dev(g["g"]), G.dev(g["x"]), G.dev(g["G"])
+    h0d = G.dev(g["h0"]) if "h0" in g else None
+    h = G.fm_forward(gd, xd, h0d)
+    dg, dx, dh0 = G.fm_backward(gd, xd, h, Gd, h0d, want_gh0=True)
+    torch.cuda.synchronize()
+    H.assert_close(G.host(h), g["ref32_h"], 1e-5, 1e-6, name + " states")
+    H.assert_close(G.host(h), g["ref64_h"], 1e-5, 1e-6, name + " states vs double")
+    scale_x = float(np.abs(g["ref64_d_tokens"]).max())
+    scale_g = float(np.abs(g["ref64_d_gates"]).max())
+    H.assert_close(G.host(dx), g["ref64_d_tokens"], 1e-5, 1e-6 * max(1, scale_x), name + " d_tokens")
+    H.assert_close(G.host(dg), g["ref64_d_gates"], 1e-5, 1e-6 * max(1, scale_g), name + " d_gates")
+    if "ref64_d_h0" in g:
+        H.assert_close(G.host(dh0), g["ref64_d_h0"], 1e-5, 1e-6, name + " d_h0")
+
+
+@pytest.mark.parametrize("storage,B,M,D,L", [
+    ("f32", 2, 3, 5, 257), ("bf16", 1, 4, 16, 2048), ("f16", 2, 2, 7, 1000), ("f16", 1, 3, 4, 31),
+    ("bf16", 1, 32, 64, 8192),   # the notebook's usage shape with D cut from 2048 to 64
+    ("f32", 1, 1, 5, 32),        # the notebook's correctness cell
+])
+def test_fm_against_oracle(storage, B, M, D, L):
+    rng = np.random.Generator(np.random.PCG64(B * 1000 + M * 100 + D * 10 + L))
+    g = H.round_storage((0.5 + 0.5 * rng.random((B, M, L), dtype=np.float32)), storage)
+    x = H.round_storage(rng.standard_normal((B, D, L), dtype=np.float32), storage)
+    Gr = H.round_storage(rng.standard_normal((B, M, D, L), dtype=np.float32), storage)
+    h0 = H.round_storage(rng.standard_normal((B, M, D), dtype=np.float32), storage)
+    gd, xd, Gd, h0d = G.dev(g, storage), G.dev(x, storage), G.dev(Gr, storage), G.dev(h0)
+    h = G.fm_forward(gd, xd, h0d)
+    dg, dx, dh0 = G.fm_backward(gd, xd, h, Gd, h0d, want_gh0=True)
+    torch.cuda.synchronize()
+    f64 = np.float64
+    h_ref = oc.fm_forward(g.astype(f64), x.astype(f64), h0.astype(f64), dtype=f64)
+    hs = G.host(h)
+    dg_ref, dx_ref, dh0_ref = oc.fm_backward(g.astype(f64), x.astype(f64), hs.astype(f64), Gr.astype(f64),
+                                             h0.astype(f64), dtype=f64)
+    if storage == "f32":
+        tol = lambda ref: (H.FP32_RTOL, H.FP32_ATOL * max(1.0, float(np.abs(ref).max())))
+    else:
+        tol = lambda ref: (H.LOWP_RTOL, H.lowp_atol(ref))
+    H.assert_close(hs, h_ref, *tol(h_ref), "fm states")
+    H.assert_close(G.host(dx), dx_ref, *tol(dx_ref), "fm d_tokens")
+    H.assert_close(G.host(dg), dg_ref, *tol(dg_ref), "fm d_gates")
+    H.assert_close(G.host(dh0), dh0_ref, 1e-4, 1e-4 * max(1.0, float(np.abs(dh0_ref).max())), "fm d_h0")
+
+
+def test_fm_mode_through_the_torch_op():
+    from fm_b200 import fm_scan
+    g = H.load_golden("fm_2x3x5x64_h0")
+    gd = G.dev(g["g"]).requires_grad_(True)
+    xd = G.dev(g["x"]).requires_grad_(True)
+    h0d = G.dev(g["h0"]).requires_grad_(True)
+    h = fm_scan(gd, xd, h0d, mode="fm")
+    assert h.shape == (2, 3, 5, 64)
+    h.backward(G.dev(g["G"]))
+    torch.cuda.synchronize()
+    H.assert_close(G.host(h), g["ref32_h"], 1e-5, 1e-6, "op states")
+    H.assert_close(G.host(gd.grad), g["ref32_d_gates"], 1e-5, 1e-5, "op d_gates")
+    H.assert_close(G.host(xd.grad), g["ref32_d_tokens"], 1e-5, 1e-5, "op d_tokens")
+    H.assert_close(G.host(h0d.grad), g["ref32_d_h0"], 1e-5, 1e-5, "op d_h0")
+    with pytest.raises(ValueError):
+        fm_scan(gd, xd, mode="outer")
+
+
+def test_fm_equals_plain_on_broadcast_rows():
+    """FM(g, x) is the plain scan of (g, (1-g) x) on the B*M*D broadcast rows -- bit for bit."""
+    rng = np.random.Generator(np.random.PCG64(5))
+    B, M, D, L = 2, 3, 4, 512
+    g = rng.random((B, M, L), dtype=np.float32)
+    x = rng.standard_normal((B, D, L), dtype=np.float32)
+    gd, xd = G.dev(g), G.dev(x)
+    h_fm = G.fm_forward(gd, xd)
+    a_rows = gd[:, :, None, :].expand(B, M, D, L).contiguous()
+    x_rows = ((1.0 - gd)[:, :, None, :] * xd[:, None, :, :]).contiguous()
+    h_plain = G.forward(a_rows.view(-1, L), x_rows.view(-1, L)).view(B, M, D, L)
+    torch.cuda.synchronize()
+    assert torch.equal(h_fm, h_plain)
+
+
+@pytest.mark.parametrize("mem_norm", [True, False])
+def test_fm_memory_layer_matches_loop_restatement(mem_norm):
+    """The layer around the scan, forward and gradients, against the torch-loop restatement."""
+    from fm_b200 import fm_memory
+    from oracle.torch_loop import fm_memory_loop
+    gen = torch.Generator().manual_seed(11)
+    B, L, M, D = 2, 96, 3, 8
+    alpha = torch.softmax(torch.randn(B, L, M, generator=gen), dim=-1)
+    upd = torch.sigmoid(torch.randn(B, L, 1, generator=gen))
+    outs = torch.sigmoid(torch.randn(B, L, 1, generator=gen))
+    inp = torch.randn(B, L, D, generator=gen)
+    h0 = torch.randn(B, M, D, generator=gen)
+    W = torch.randn(B, L, D, generator=gen)
+
+    def run(fn, dev, dtype):
+        args = [t.to(dev, dtype).requires_grad_(True) for t in (alpha, upd, outs, inp, h0)]
+        out, mem = fn(args[0], args[1], args[2], args[3], args[4], mem_norm=mem_norm)
+        (out * W.to(dev, dtype)).sum().backward()
+        return [out.detach().cpu().double(), mem.detach().cpu().double()] + [a.grad.cpu().double() for a in args]
+
+    got = run(fm_memory, "cuda", torch.float32)
+    ref = run(fm_memory_loop, "cpu", torch.float64)
+    names = ["output", "memory_states", "d_alpha", "d_update_scale", "d_output_scale", "d_inputs", "d_h0"]
+    for n, a, b in zip(names, got, ref):
+        scale = max(1.0, float(b.abs().max()))
+        H.assert_close(a.numpy(), b.numpy(), 1e-4, 2e-5 * scale, n)

@@ -43,6 +43,10 @@ UNIT = "elements/s"
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 CPU_SAMPLE_ROWS = 4096
+# DRAM traffic of the backward kernel per algorithmic byte, from the ncu capture summarised in
+# profiles/plain_fwd_bwd_bf16_rows4096_T8192.md (small case; traffic is proportional to rows):
+# reads 201.38 MB against 201.33 MB algorithmic, writes algorithmic.
+NCU_BWD_READ_RATIO = 201.38 / 201.33
 
 
 def measured_peak():
@@ -285,7 +289,9 @@ def run_ours(args):
             "fwd_elements_per_s": global_rows * T / (fwd_ms * 1e-3),
             "roofline": {"bound": "hbm", "kernel": "plain_backward_kernel", "achieved": bwd_gbs,
                          "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": bwd_gbs / peak,
-                         "frac_of_nominal_8TBs": bwd_gbs / NOMINAL_HBM_GBS, "traffic": None,
+                         "frac_of_nominal_8TBs": bwd_gbs / NOMINAL_HBM_GBS,
+                         "traffic": int((3 * NCU_BWD_READ_RATIO + 2) * s * n_local),
+                         "traffic_source": "ncu dram__bytes_read.sum+write.sum on a 4096-row case, scaled by rows",
                          "algorithmic_bytes_per_launch": 5 * s * n_local},
             "roofline_forward": {"kernel": "plain_forward_kernel", "achieved": fwd_gbs,
                                  "frac": fwd_gbs / peak, "frac_of_nominal_8TBs": fwd_gbs / NOMINAL_HBM_GBS,

@@ -408,7 +408,7 @@ def run_e2e(args, a3, x3, G3, device, barrier):
         hb.copy_(t)
     host_out = [torch.empty(a3.shape, dtype=a3.dtype, pin_memory=True) for _ in range(3)]
     rows = a3.numel() // a3.shape[-1]
-    pipe = HostPipeline(max(1, rows // 8), a3.shape[-1], a3.dtype, device)
+    pipe = HostPipeline(max(1, rows // 32), a3.shape[-1], a3.dtype, device)
     torch.cuda.synchronize()
 
     def step():
@@ -424,7 +424,7 @@ def run_e2e(args, a3, x3, G3, device, barrier):
     barrier()
     pipe.close()
     nbytes = a3.numel() * a3.element_size()
-    blocks = 8 if rows >= 8 else 1
+    blocks = 32 if rows >= 2048 else (8 if rows >= 8 else 1)
     return {"ms": start.elapsed_time(end) / steps, "h2d": 3 * nbytes, "d2h": 3 * nbytes,
             "steps": steps, "launches_per_step": 2 * blocks,
             "path": "fms_plain_forward_backward_host: pinned host -> H2D | kernels | D2H overlapped in "

@@ -1,0 +1,170 @@
+// FM-mode backward with the gradient reductions blocked inside a CTA.
+//
+// FM mode is the reference's own operator (fm/scan/fm_pytorch.py:19-42):
+//     h[b,m,d,t] = g[b,m,t] * h[b,m,d,t-1] + (1 - g[b,m,t]) * x[b,d,t]
+// Its backward needs, besides one reverse scan per output row (b,m,d),
+//     d_gates [b,m,t] = sum_d (h[b,m,d,t-1] - x[b,d,t]) * delta[b,m,d,t]
+//     d_tokens[b,d,t] = sum_m (1 - g[b,m,t])            * delta[b,m,d,t]
+// which the reference obtains from two (B,M,D,L) temporaries and two torch sums
+// (fm/scan/fm_scan.cuh:184-207, fm/scan/fm_scan.py:70-78).
+//
+// Here a CTA owns MC gate rows x DC token rows of one batch element (MC*DC output rows) and
+// walks time backwards one tile (32 lanes x 16 bytes) per step.  Warp w owns gate row m0+w:
+//   * the gate tile is loaded and unpacked once per step and the gate half of the pair scan
+//     (the five levels of prefix products) is computed once, then reused for all DC rows;
+//   * the DC token tiles of the step are staged in shared memory once for all warps;
+//   * the sum over d is accumulated in registers (same warp), the sum over m in a
+//     shared-memory tile with shared atomics (different warps);
+//   * per step each warp issues ONE vector reduction row for d_gates and the CTA DC rows for
+//     d_tokens: global atomics drop by DC and MC against one-row-per-CTA.
+// Only the big streams h and G (grad of the states) come from HBM; they are prefetched PD rows
+// ahead into registers.
+#pragma once
+
+#include "scan_kernels.cuh"
+
+namespace fms {
+
+template <typename S, int MC, int DC, int PD>
+__global__ void __launch_bounds__(MC * 32, 2)
+fm_backward_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
+                           const S *__restrict__ states, const S *__restrict__ grad_states,
+                           const float *__restrict__ h0, float *__restrict__ acc_gates,
+                           float *__restrict__ acc_tokens, float *__restrict__ grad_h0, int64_t M,
+                           int64_t D, int64_t L, int64_t m_blocks, int64_t d_blocks) {
+    static_assert(DC % PD == 0 && PD <= DC, "DC must be a multiple of the prefetch distance");
+    constexpr int E = Store<S>::E;
+    constexpr int W = 32 * E;  // positions per tile
+    __shared__ uint4 xs[DC][32];      // token tiles of this step, raw storage
+    __shared__ float accx[DC][W];     // sum over the CTA's gate rows of (1-g)*delta; index i*32+lane
+    const int lane = threadIdx.x & 31;
+    const int w = threadIdx.x >> 5;
+
+    // block -> (b, m block, d block); d blocks vary fastest so neighbours share the gate rows in L2
+    const int64_t blk = blockIdx.x;
+    const int64_t db = blk % d_blocks, mb = (blk / d_blocks) % m_blocks, b = blk / (d_blocks * m_blocks);
+    const int64_t m = mb * MC + w, d0 = db * DC;
+    const bool have_m = m < M;
+    const int64_t ntiles = (L + W - 1) / W;
+
+    const S *grow = gates + (b * M + (have_m ? m : 0)) * L;
+    const int64_t row0 = ((b * M + (have_m ? m : 0)) * D + d0);  // first output row of this warp
+    float carry[DC], dh_before[DC];
+#pragma unroll
+    for (int d = 0; d < DC; ++d) {
+        carry[d] = 0.f;
+        dh_before[d] = (h0 && have_m && d0 + d < D) ? h0[row0 + d] : 0.f;
+    }
+#pragma unroll
+    for (int d = w; d < DC; d += MC)
+#pragma unroll
+        for (int i = 0; i < E; ++i) accx[d][i * 32 + lane] = 0.f;
+
+    // register ring of the big streams: slot = d % PD
+    uint4 rG[PD], rH[PD];
+    float rhalo[PD];
+    auto fetch = [&](int slot, int64_t tile, int d) {
+        const int64_t t = tile * W + lane * E;
+        const bool ok = have_m && tile >= 0 && d0 + d < D && t < L;
+        const int64_t base = (row0 + d) * L;
+        rG[slot] = ok ? ldg_stream(grad_states + base + t) : make_uint4(0u, 0u, 0u, 0u);
+        rH[slot] = ok ? ldg_stream(states + base + t) : make_uint4(0u, 0u, 0u, 0u);
+        rhalo[slot] = (ok && lane == 0 && t > 0) ? Store<S>::to_float(states[base + t - 1]) : 0.f;
+    };
+#pragma unroll
+    for (int p = 0; p < PD; ++p) fetch(p, ntiles - 1, p);
+
+    for (int64_t tile = ntiles - 1; tile >= 0; --tile) {
+        const int64_t t = tile * W + lane * E;  // this lane's first position
+        const bool in = t < L;
+        __syncthreads();  // previous step's flush is complete: xs and accx may be reused
+        // stage the DC token tiles
+#pragma unroll
+        for (int d = w; d < DC; d += MC)
+            xs[d][lane] = (in && d0 + d < D) ? ldg_stream(tokens + (b * D + d0 + d) * L + t)
+                                             : make_uint4(0u, 0u, 0u, 0u);
+        // gate tile: unpack once, prefix products once
+        float fa[E], om[E];
+        {
+            const uint4 q = (in && have_m) ? ldg_stream(grow + t)
+                                           : make_uint4(Store<S>::kOne, Store<S>::kOne, Store<S>::kOne, Store<S>::kOne);
+            Store<S>::unpack(q, fa);
+        }
+        float A = fa[E - 1];
+#pragma unroll
+        for (int i = E - 2; i >= 0; --i) A *= fa[i];
+#pragma unroll
+        for (int i = 0; i < E; ++i) om[i] = 1.f - fa[i];
+        float Alvl[5];
+#pragma unroll
+        for (int k = 0; k < 5; ++k) {
+            Alvl[k] = A;
+            const float pA = __shfl_down_sync(kFullMask, A, 1 << k);
+            if (lane + (1 << k) < 32) A *= pA;
+        }
+        float eA = __shfl_down_sync(kFullMask, A, 1);
+        if (lane == 31) eA = 1.f;
+        const float tA = __shfl_sync(kFullMask, A, 0);
+        float dg[E];
+#pragma unroll
+        for (int i = 0; i < E; ++i) dg[i] = 0.f;
+        __syncthreads();  // token tiles are staged
+
+#pragma unroll
+        for (int d = 0; d < DC; ++d) {
+            const int slot = d % PD;
+            float fg[E], fh[E], fx[E];
+            Store<S>::unpack(rG[slot], fg);
+            Store<S>::unpack(rH[slot], fh);
+            const float halo = rhalo[slot];
+            // refill the slot: PD rows ahead, wrapping into the next (earlier) tile
+            if (d + PD < DC) fetch(slot, tile, d + PD);
+            else fetch(slot, tile - 1, d + PD - DC);
+            Store<S>::unpack(xs[d][lane], fx);
+
+            float C = fa[E - 1] * fg[E - 1];
+#pragma unroll
+            for (int i = E - 2; i >= 0; --i) C = fa[i] * (fg[i] + C);
+#pragma unroll
+            for (int k = 0; k < 5; ++k) {
+                const float pC = __shfl_down_sync(kFullMask, C, 1 << k);
+                if (lane + (1 << k) < 32) C = fmaf(Alvl[k], pC, C);
+            }
+            float eC = __shfl_down_sync(kFullMask, C, 1);
+            if (lane == 31) eC = 0.f;
+            const float tC = __shfl_sync(kFullMask, C, 0);
+            float hprev0 = __shfl_up_sync(kFullMask, fh[E - 1], 1);
+            if (lane == 0) hprev0 = (t > 0) ? halo : dh_before[d];
+            float c = fmaf(eA, carry[d], eC);
+            carry[d] = fmaf(tA, carry[d], tC);
+            const bool row_ok = in && have_m && d0 + d < D;
+#pragma unroll
+            for (int i = E - 1; i >= 0; --i) {
+                const float delta = fg[i] + c;
+                c = fa[i] * delta;
+                const float hp = (i > 0) ? fh[i > 0 ? i - 1 : 0] : hprev0;
+                dg[i] = fmaf(delta, hp - fx[i], dg[i]);
+                if (row_ok) atomicAdd(&accx[d][i * 32 + lane], om[i] * delta);
+            }
+        }
+        if (in && have_m) red_vec<E, false>(acc_gates + (b * M + m) * L, t, L, dg);
+        __syncthreads();  // every warp has added its share to accx
+#pragma unroll
+        for (int d = w; d < DC; d += MC) {
+            float v[E];
+#pragma unroll
+            for (int i = 0; i < E; ++i) {
+                v[i] = accx[d][i * 32 + lane];
+                accx[d][i * 32 + lane] = 0.f;
+            }
+            if (in && d0 + d < D) red_vec<E, false>(acc_tokens + (b * D + d0 + d) * L, t, L, v);
+        }
+    }
+    if (grad_h0 && have_m && lane == 0) {
+#pragma unroll
+        for (int d = 0; d < DC; ++d)
+            if (d0 + d < D) grad_h0[row0 + d] = carry[d];
+    }
+}
+
+}  // namespace fms

@@ -6,6 +6,7 @@
 #include <cstdlib>
 #include <mutex>
 
+#include "fm_kernels.cuh"
 #include "scan_kernels.cuh"
 
 #define FMS_EXPORT extern "C" __attribute__((visibility("default")))
@@ -422,6 +423,28 @@ int launch_fm_backward(const FmShape &sh, bool aligned, const void *gates, const
     return check_launch();
 }
 
+// Blocked backward (fm_kernels.cuh): 8 gate rows x 8 token rows per CTA, aligned tensors only.
+template <typename S>
+int launch_fm_backward_blocked(const FmShape &sh, const void *gates, const void *tokens, const void *states,
+                               const void *grad_states, const float *h0, float *acc_gates, float *acc_tokens,
+                               float *grad_h0, cudaStream_t st) {
+    constexpr int MC = 8, DC = 8;
+    const int64_t m_blocks = (sh.M + MC - 1) / MC, d_blocks = (sh.D + DC - 1) / DC;
+    if (sh.B > 0x7fffffffLL / m_blocks || sh.B * m_blocks > 0x7fffffffLL / d_blocks) return FMS_ERR_BAD_SHAPE;
+    const unsigned grid = static_cast<unsigned>(sh.B * m_blocks * d_blocks);
+    const int pd = tune_value("FMS_TUNE_FM_PD", 4);
+#define FMS_LAUNCH_FM_BLOCKED(PDV)                                                                  \
+    fms::fm_backward_blocked_kernel<S, MC, DC, PDV><<<grid, MC * 32, 0, st>>>(                      \
+        static_cast<const S *>(gates), static_cast<const S *>(tokens), static_cast<const S *>(states), \
+        static_cast<const S *>(grad_states), h0, acc_gates, acc_tokens, grad_h0, sh.M, sh.D, sh.L,   \
+        m_blocks, d_blocks)
+    if (pd == 2) FMS_LAUNCH_FM_BLOCKED(2);
+    else if (pd == 8) FMS_LAUNCH_FM_BLOCKED(8);
+    else FMS_LAUNCH_FM_BLOCKED(4);
+#undef FMS_LAUNCH_FM_BLOCKED
+    return check_launch();
+}
+
 template <typename S>
 int launch_cast(const float *src, void *dst, int64_t n, cudaStream_t st) {
     if (n == 0) return FMS_OK;
@@ -505,7 +528,14 @@ FMS_EXPORT int fms_fm_backward(const void *gates, const void *tokens, const void
     aligned = aligned && (static_cast<uint64_t>(L) * sizeof(float)) % 16 == 0 && aligned_to(acc_g, 16) &&
               aligned_to(acc_x, 16);
     {
+        // rows that share a gate or a token row are reduced inside a CTA before any global
+        // atomic when everything is 16-byte aligned; the row-per-CTA kernel covers the rest
+        const bool blocked = aligned && tune_value("FMS_TUNE_FM_BLOCKED", 1) != 0;
         auto pass = [&]() -> int {
+            if (blocked) {
+                FMS_DISPATCH_DTYPE(dtype, (launch_fm_backward_blocked<S>(sh, gates, tokens, states, grad_states,
+                                                                         h0, acc_g, acc_x, grad_h0, st)));
+            }
             FMS_DISPATCH_DTYPE(dtype, (launch_fm_backward<S>(sh, aligned, gates, tokens, states, grad_states, h0,
                                                              acc_g, acc_x, grad_h0, st)));
         };

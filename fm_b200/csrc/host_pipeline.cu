@@ -93,9 +93,11 @@ FMS_EXPORT int fms_plain_forward_backward_host(fms_pipeline *p, const void *gate
     int64_t block_rows = static_cast<int64_t>((p->workspace_bytes / 12 / kAlign * kAlign) / row_bytes);
     if (block_rows < 1) return FMS_ERR_WORKSPACE;
     block_rows = std::min(block_rows, rows);
-    // A few blocks more than the minimum keep both copy directions busy while the first block
-    // is still on its way in.
-    if (rows >= 8 && block_rows > rows / 8) block_rows = (rows + 7) / 8;
+    // Many blocks keep the fill (first block on its way in) and the drain (last block on its way
+    // out) short against the steady state in which both copy directions run at once.
+    constexpr int64_t kBlocks = 32, kMinBlockRows = 64;
+    if (rows >= kBlocks * kMinBlockRows && block_rows > rows / kBlocks) block_rows = (rows + kBlocks - 1) / kBlocks;
+    else if (rows >= 8 && block_rows > rows / 8) block_rows = (rows + 7) / 8;
     const size_t slot = round_up(static_cast<size_t>(block_rows) * row_bytes, kAlign);
     char *in_buf[2][3], *out_buf[2][3];
     for (int s = 0; s < 2; ++s)

@@ -223,7 +223,7 @@ int fms_plain_forward_split_static(const void *gates, const void *tokens, const 
 /*
  * Forward + backward with inputs and outputs in HOST memory, for callers whose tensors live
  * on the host (the reference's CPU path fm/scan/fm_pytorch.py:3-42 is such a caller's
- * alternative).  Rows are cut into blocks; host->device copies, the two kernels and
+ * alternative).  Rows are cut into blocks (up to 32); host->device copies, the two kernels and
  * device->host copies of consecutive blocks overlap on three internal streams (both PCIe
  * directions busy at once).  The reference has no counterpart: its extension only accepts
  * CUDA tensors (fm/scan/fm_scan.cuh:346-348).

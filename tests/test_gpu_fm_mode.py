@@ -32,8 +32,12 @@ def test_fm_goldens_from_the_reference(name):
     ("f32", 2, 3, 5, 257), ("bf16", 1, 4, 16, 2048), ("f16", 2, 2, 7, 1000), ("f16", 1, 3, 4, 31),
     ("bf16", 1, 32, 64, 8192),   # the notebook's usage shape with D cut from 2048 to 64
     ("f32", 1, 1, 5, 32),        # the notebook's correctness cell
+    ("bf16", 2, 9, 17, 520),     # M, D not multiples of the CTA block, ragged last tile
 ])
-def test_fm_against_oracle(storage, B, M, D, L):
+@pytest.mark.parametrize("blocked", [1, 0])
+def test_fm_against_oracle(monkeypatch, blocked, storage, B, M, D, L):
+    # blocked = 1: CTA-blocked reductions (aligned shapes); 0: one output row per CTA
+    monkeypatch.setenv("FMS_TUNE_FM_BLOCKED", str(blocked))
     rng = np.random.Generator(np.random.PCG64(B * 1000 + M * 100 + D * 10 + L))
     g = H.round_storage((0.5 + 0.5 * rng.random((B, M, L), dtype=np.float32)), storage)
     x = H.round_storage(rng.standard_normal((B, D, L), dtype=np.float32), storage)

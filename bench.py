@@ -391,6 +391,71 @@ def run_time_split(args):
         dist.destroy_process_group()
 
 
+def run_fm_mode(args):
+    """Secondary workload: the reference's own operator and demo shape, gates (1,32,8192),
+    tokens (1,D,8192) -> states (1,32,D,8192), bf16 (fm_test.ipynb:29-33 uses D = 2048).
+
+    One GPU.  Prints its own JSON line: forward writes the states once (the gate and token rows are
+    re-read from L2); backward reads states and their gradient once and reduces over D and M
+    inside the kernel.  `--rows` sets D (a small D is the profiler case).
+    """
+    import torch
+
+    from fm_b200 import fm_scan_backward_fm, fm_scan_forward
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    B, M, D, L = 1, 32, args.rows or 2048, 8192
+    gen = torch.Generator(device=dev).manual_seed(1070)
+    g = (0.9 + 0.1 * torch.rand(B, M, L, device=dev, generator=gen)).to(torch.bfloat16)
+    x = torch.randn(B, D, L, device=dev, generator=gen).to(torch.bfloat16)
+    G = torch.randn(B, M, D, L, device=dev, generator=gen).to(torch.bfloat16)
+    h = torch.empty(B, M, D, L, device=dev, dtype=torch.bfloat16)
+    dg, dx = torch.empty_like(g), torch.empty_like(x)
+
+    def fwd():
+        fm_scan_forward(g, x, None, h)
+
+    def bwd():
+        fm_scan_backward_fm(g, G, dx, h, x, dg, None, None)
+
+    for _ in range(max(3, args.warmup)):
+        fwd()
+        bwd()
+    torch.cuda.synchronize()
+    K = args.steps
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+    with ClockSampler(physical_gpu_index(0)) as clocks:
+        for k in range(K):
+            ev[k][0].record()
+            fwd()
+            ev[k][1].record()
+            bwd()
+            ev[k][2].record()
+        torch.cuda.synchronize()
+    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+    bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+    n = B * M * D * L
+    peak, kind = measured_peak()
+    line = {"metric": "FM-mode scan fwd+bwd output elements/s", "value": n / ((fwd_ms + bwd_ms) * 1e-3),
+            "unit": UNIT, "n_gpus": 1, "steps": K, "warmup": max(3, args.warmup),
+            "ms_per_step": fwd_ms + bwd_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "FM mode (B,M,D,L)=(%d,%d,%d,%d) bf16 storage / fp32 accumulate" % (B, M, D, L)},
+            "gpu_launches": K * 5, "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
+            "roofline_forward": {"algorithmic_bytes_per_launch": 2 * n + 2 * (M + D) * B * L,
+                                 "achieved": (2 * n + 2 * (M + D) * B * L) / (fwd_ms * 1e-3) / 1e9,
+                                 "peak": peak, "peak_kind": kind, "unit": "GB/s"},
+            "roofline": {"bound": "hbm", "kernel": "fm_backward_blocked_kernel",
+                         "algorithmic_bytes_per_launch": 4 * n + 4 * (M + D) * B * L,
+                         "achieved": (4 * n + 4 * (M + D) * B * L) / (bwd_ms * 1e-3) / 1e9,
+                         "peak": peak, "peak_kind": kind, "unit": "GB/s"},
+            "clocks": clocks.summary()}
+    line["roofline"]["frac"] = line["roofline"]["achieved"] / peak
+    line["roofline_forward"]["frac"] = line["roofline_forward"]["achieved"] / peak
+    print(json.dumps(line), flush=True)
+
+
 def run_e2e(args, a3, x3, G3, device, barrier):
     """Same step with pinned HOST inputs and outputs through the host-buffer entry of the C ABI.
 
@@ -438,8 +503,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
-    ap.add_argument("--workload", choices=["c3", "c4"], default="c3",
-                    help="c3: the headline row-sharded workload; c4: the long sequence split along T")
+    ap.add_argument("--workload", choices=["c3", "c4", "fm"], default="c3",
+                    help="c3: the headline row-sharded workload; c4: the long sequence split along T; "
+                         "fm: the reference's (B,M,L)x(B,D,L)->(B,M,D,L) operator at its demo shape")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling aid)")
@@ -450,6 +516,8 @@ def main():
         run_reference_arm(args)
     elif args.workload == "c4":
         run_time_split(args)
+    elif args.workload == "fm":
+        run_fm_mode(args)
     else:
         run_ours(args)
 

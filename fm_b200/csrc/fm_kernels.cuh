@@ -13,8 +13,9 @@
 //   * the gate tile is loaded and unpacked once per step and the gate half of the pair scan
 //     (the five levels of prefix products) is computed once, then reused for all DC rows;
 //   * the DC token tiles of the step are staged in shared memory once for all warps;
-//   * the sum over d is accumulated in registers (same warp), the sum over m in a
-//     shared-memory tile with shared atomics (different warps);
+//   * the sum over d is accumulated in registers (same warp); for the sum over m every warp
+//     publishes its tile to shared memory and, after a barrier, warp d adds the MC tiles of
+//     token row d (plain 128-bit shared accesses, no shared atomics, fixed summation order);
 //   * per step each warp issues ONE vector reduction row for d_gates and the CTA DC rows for
 //     d_tokens: global atomics drop by DC and MC against one-row-per-CTA.
 // Only the big streams h and G (grad of the states) come from HBM; they are prefetched PD rows
@@ -35,8 +36,14 @@ fm_backward_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ to
     static_assert(DC % PD == 0 && PD <= DC, "DC must be a multiple of the prefetch distance");
     constexpr int E = Store<S>::E;
     constexpr int W = 32 * E;  // positions per tile
-    __shared__ uint4 xs[DC][32];      // token tiles of this step, raw storage
-    __shared__ float accx[DC][W];     // sum over the CTA's gate rows of (1-g)*delta; index i*32+lane
+    // dynamic shared memory (more than the 48 KB static limit): token tiles, then the partial tiles
+    extern __shared__ __align__(16) unsigned char fm_smem[];
+    uint4(*xs)[DC][32] = reinterpret_cast<uint4(*)[DC][32]>(fm_smem);  // [2][DC][32] token tiles, raw
+    // every warp's (1-g)*delta tile of every token row; summed over warps after the step.
+    // [warp][row][E/4][lane] float4: a lane's two vectors sit in different halves, so both the
+    // stores and the loads are conflict-free 128-bit accesses
+    float4(*part)[DC][E / 4][32] =
+        reinterpret_cast<float4(*)[DC][E / 4][32]>(fm_smem + sizeof(uint4) * 2 * DC * 32);  // [MC][DC][E/4][32]
     const int lane = threadIdx.x & 31;
     const int w = threadIdx.x >> 5;
 
@@ -55,11 +62,6 @@ fm_backward_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ to
         carry[d] = 0.f;
         dh_before[d] = (h0 && have_m && d0 + d < D) ? h0[row0 + d] : 0.f;
     }
-#pragma unroll
-    for (int d = w; d < DC; d += MC)
-#pragma unroll
-        for (int i = 0; i < E; ++i) accx[d][i * 32 + lane] = 0.f;
-
     // register ring of the big streams: slot = d % PD
     uint4 rG[PD], rH[PD];
     float rhalo[PD];
@@ -74,22 +76,37 @@ fm_backward_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ to
 #pragma unroll
     for (int p = 0; p < PD; ++p) fetch(p, ntiles - 1, p);
 
-    for (int64_t tile = ntiles - 1; tile >= 0; --tile) {
+    // Token tiles and the gate tile of a step are fetched one step ahead into registers; the token
+    // tiles then go to the shared buffer the NEXT step reads (two buffers, so a step needs only
+    // two barriers).
+    auto load_x = [&](int64_t tile, int d) -> uint4 {
+        const int64_t tt = tile * W + lane * E;
+        return (tile >= 0 && tt < L && d < DC && d0 + d < D) ? ldg_stream(tokens + (b * D + d0 + d) * L + tt)
+                                                   : make_uint4(0u, 0u, 0u, 0u);
+    };
+    auto load_g = [&](int64_t tile) -> uint4 {
+        const int64_t tt = tile * W + lane * E;
+        return (tile >= 0 && tt < L && have_m)
+                   ? ldg_stream(grow + tt)
+                   : make_uint4(Store<S>::kOne, Store<S>::kOne, Store<S>::kOne, Store<S>::kOne);
+    };
+    constexpr int XPW = (DC + MC - 1) / MC;  // token rows staged per warp
+    uint4 gq = load_g(ntiles - 1), xq[XPW];
+#pragma unroll
+    for (int k = 0; k < XPW; ++k)
+        if (w + k * MC < DC) xs[0][w + k * MC][lane] = load_x(ntiles - 1, w + k * MC);
+
+    unsigned step = 0;
+    for (int64_t tile = ntiles - 1; tile >= 0; --tile, ++step) {
         const int64_t t = tile * W + lane * E;  // this lane's first position
         const bool in = t < L;
-        __syncthreads();  // previous step's flush is complete: xs and accx may be reused
-        // stage the DC token tiles
-#pragma unroll
-        for (int d = w; d < DC; d += MC)
-            xs[d][lane] = (in && d0 + d < D) ? ldg_stream(tokens + (b * D + d0 + d) * L + t)
-                                             : make_uint4(0u, 0u, 0u, 0u);
-        // gate tile: unpack once, prefix products once
+        const unsigned buf = step & 1u;
+        __syncthreads();  // previous step's flush is complete and xs[buf] is staged
         float fa[E], om[E];
-        {
-            const uint4 q = (in && have_m) ? ldg_stream(grow + t)
-                                           : make_uint4(Store<S>::kOne, Store<S>::kOne, Store<S>::kOne, Store<S>::kOne);
-            Store<S>::unpack(q, fa);
-        }
+        Store<S>::unpack(gq, fa);
+        gq = load_g(tile - 1);
+#pragma unroll
+        for (int k = 0; k < XPW; ++k) xq[k] = load_x(tile - 1, w + k * MC);
         float A = fa[E - 1];
 #pragma unroll
         for (int i = E - 2; i >= 0; --i) A *= fa[i];
@@ -108,7 +125,6 @@ fm_backward_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ to
         float dg[E];
 #pragma unroll
         for (int i = 0; i < E; ++i) dg[i] = 0.f;
-        __syncthreads();  // token tiles are staged
 
 #pragma unroll
         for (int d = 0; d < DC; ++d) {
@@ -120,7 +136,7 @@ fm_backward_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ to
             // refill the slot: PD rows ahead, wrapping into the next (earlier) tile
             if (d + PD < DC) fetch(slot, tile, d + PD);
             else fetch(slot, tile - 1, d + PD - DC);
-            Store<S>::unpack(xs[d][lane], fx);
+            Store<S>::unpack(xs[buf][d][lane], fx);
 
             float C = fa[E - 1] * fg[E - 1];
 #pragma unroll
@@ -137,26 +153,39 @@ fm_backward_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ to
             if (lane == 0) hprev0 = (t > 0) ? halo : dh_before[d];
             float c = fmaf(eA, carry[d], eC);
             carry[d] = fmaf(tA, carry[d], tC);
-            const bool row_ok = in && have_m && d0 + d < D;
+            float dxv[E];  // zero for masked rows and lanes (G = 0, carry = 0 there)
 #pragma unroll
             for (int i = E - 1; i >= 0; --i) {
                 const float delta = fg[i] + c;
                 c = fa[i] * delta;
                 const float hp = (i > 0) ? fh[i > 0 ? i - 1 : 0] : hprev0;
                 dg[i] = fmaf(delta, hp - fx[i], dg[i]);
-                if (row_ok) atomicAdd(&accx[d][i * 32 + lane], om[i] * delta);
+                dxv[i] = om[i] * delta;
             }
+#pragma unroll
+            for (int k = 0; k < E / 4; ++k)
+                part[w][d][k][lane] = make_float4(dxv[4 * k], dxv[4 * k + 1], dxv[4 * k + 2], dxv[4 * k + 3]);
         }
         if (in && have_m) red_vec<E, false>(acc_gates + (b * M + m) * L, t, L, dg);
-        __syncthreads();  // every warp has added its share to accx
+#pragma unroll
+        for (int k = 0; k < XPW; ++k)
+            if (w + k * MC < DC) xs[buf ^ 1u][w + k * MC][lane] = xq[k];
+        __syncthreads();  // every warp has published its tiles (and staged the next token tiles)
 #pragma unroll
         for (int d = w; d < DC; d += MC) {
             float v[E];
 #pragma unroll
-            for (int i = 0; i < E; ++i) {
-                v[i] = accx[d][i * 32 + lane];
-                accx[d][i * 32 + lane] = 0.f;
-            }
+            for (int i = 0; i < E; ++i) v[i] = 0.f;
+#pragma unroll
+            for (int ww = 0; ww < MC; ++ww)
+#pragma unroll
+                for (int k = 0; k < E / 4; ++k) {
+                    const float4 p = part[ww][d][k][lane];
+                    v[4 * k] += p.x;
+                    v[4 * k + 1] += p.y;
+                    v[4 * k + 2] += p.z;
+                    v[4 * k + 3] += p.w;
+                }
             if (in && d0 + d < D) red_vec<E, false>(acc_tokens + (b * D + d0 + d) * L, t, L, v);
         }
     }
@@ -165,6 +194,12 @@ fm_backward_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ to
         for (int d = 0; d < DC; ++d)
             if (d0 + d < D) grad_h0[row0 + d] = carry[d];
     }
+}
+
+// Dynamic shared memory the kernel above needs.
+template <typename S, int MC, int DC>
+constexpr size_t fm_backward_blocked_smem() {
+    return sizeof(uint4) * 2 * DC * 32 + sizeof(float4) * MC * DC * (Store<S>::E / 4) * 32;
 }
 
 }  // namespace fms

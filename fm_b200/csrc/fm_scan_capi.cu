@@ -433,11 +433,18 @@ int launch_fm_backward_blocked(const FmShape &sh, const void *gates, const void 
     if (sh.B > 0x7fffffffLL / m_blocks || sh.B * m_blocks > 0x7fffffffLL / d_blocks) return FMS_ERR_BAD_SHAPE;
     const unsigned grid = static_cast<unsigned>(sh.B * m_blocks * d_blocks);
     const int pd = tune_value("FMS_TUNE_FM_PD", 4);
+    constexpr size_t smem = fms::fm_backward_blocked_smem<S, MC, DC>();
 #define FMS_LAUNCH_FM_BLOCKED(PDV)                                                                  \
-    fms::fm_backward_blocked_kernel<S, MC, DC, PDV><<<grid, MC * 32, 0, st>>>(                      \
-        static_cast<const S *>(gates), static_cast<const S *>(tokens), static_cast<const S *>(states), \
-        static_cast<const S *>(grad_states), h0, acc_gates, acc_tokens, grad_h0, sh.M, sh.D, sh.L,   \
-        m_blocks, d_blocks)
+    do {                                                                                            \
+        auto kern = fms::fm_backward_blocked_kernel<S, MC, DC, PDV>;                                \
+        static const cudaError_t attr = cudaFuncSetAttribute(                                       \
+            kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));             \
+        if (int rc = record(attr)) return rc;                                                       \
+        kern<<<grid, MC * 32, smem, st>>>(                                                          \
+            static_cast<const S *>(gates), static_cast<const S *>(tokens),                          \
+            static_cast<const S *>(states), static_cast<const S *>(grad_states), h0, acc_gates,     \
+            acc_tokens, grad_h0, sh.M, sh.D, sh.L, m_blocks, d_blocks);                             \
+    } while (0)
     if (pd == 2) FMS_LAUNCH_FM_BLOCKED(2);
     else if (pd == 8) FMS_LAUNCH_FM_BLOCKED(8);
     else FMS_LAUNCH_FM_BLOCKED(4);

@@ -1,4 +1,4 @@
-// FM-mode backward with the gradient reductions blocked inside a CTA.
+// FM-mode kernels blocked over rows that share a gate row or a token row.
 //
 // FM mode is the reference's own operator (fm/scan/fm_pytorch.py:19-42):
 //     h[b,m,d,t] = g[b,m,t] * h[b,m,d,t-1] + (1 - g[b,m,t]) * x[b,d,t]
@@ -196,7 +196,111 @@ fm_backward_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ to
     }
 }
 
-// Dynamic shared memory the kernel above needs.
+// FM-mode forward with the same blocking: warp w owns gate row m0+w and produces the DC state
+// rows (m0+w, d0..d0+DC-1).  The gate tile is unpacked and its prefix products are taken once per
+// step; the DC token tiles are staged in shared memory one step ahead (two buffers, one barrier
+// per step); each state row costs one 5-shuffle scan of its token half and one 16-byte store per
+// lane.  Nothing but the states goes to HBM; gates and tokens are read once per CTA block.
+template <typename S, int MC, int DC>
+__global__ void __launch_bounds__(MC * 32)
+fm_forward_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
+                          const float *__restrict__ h0, S *__restrict__ states, int64_t M, int64_t D,
+                          int64_t L, int64_t m_blocks, int64_t d_blocks) {
+    constexpr int E = Store<S>::E;
+    constexpr int W = 32 * E;
+    __shared__ uint4 xs[2][DC][32];
+    const int lane = threadIdx.x & 31;
+    const int w = threadIdx.x >> 5;
+    const int64_t blk = blockIdx.x;
+    const int64_t db = blk % d_blocks, mb = (blk / d_blocks) % m_blocks, b = blk / (d_blocks * m_blocks);
+    const int64_t m = mb * MC + w, d0 = db * DC;
+    const bool have_m = m < M;
+    const int64_t ntiles = (L + W - 1) / W;
+    const S *grow = gates + (b * M + (have_m ? m : 0)) * L;
+    const int64_t row0 = ((b * M + (have_m ? m : 0)) * D + d0);
+
+    float carry[DC];
+#pragma unroll
+    for (int d = 0; d < DC; ++d) carry[d] = (h0 && have_m && d0 + d < D) ? h0[row0 + d] : 0.f;
+
+    auto load_x = [&](int64_t tile, int d) -> uint4 {
+        const int64_t tt = tile * W + lane * E;
+        return (tile < ntiles && tt < L && d < DC && d0 + d < D)
+                   ? ldg_stream(tokens + (b * D + d0 + d) * L + tt)
+                   : make_uint4(0u, 0u, 0u, 0u);
+    };
+    auto load_g = [&](int64_t tile) -> uint4 {
+        const int64_t tt = tile * W + lane * E;
+        return (tile < ntiles && tt < L && have_m)
+                   ? ldg_stream(grow + tt)
+                   : make_uint4(Store<S>::kOne, Store<S>::kOne, Store<S>::kOne, Store<S>::kOne);
+    };
+    constexpr int XPW = (DC + MC - 1) / MC;
+    uint4 gq = load_g(0), xq[XPW];
+#pragma unroll
+    for (int k = 0; k < XPW; ++k)
+        if (w + k * MC < DC) xs[0][w + k * MC][lane] = load_x(0, w + k * MC);
+
+    for (int64_t tile = 0; tile < ntiles; ++tile) {
+        const int64_t t = tile * W + lane * E;
+        const bool in = t < L;
+        const unsigned buf = static_cast<unsigned>(tile) & 1u;
+        __syncthreads();  // xs[buf] is staged; xs[buf^1] is no longer read
+        float fa[E], om[E];
+        Store<S>::unpack(gq, fa);
+        gq = load_g(tile + 1);
+#pragma unroll
+        for (int k = 0; k < XPW; ++k) xq[k] = load_x(tile + 1, w + k * MC);
+        float A = fa[0];
+#pragma unroll
+        for (int i = 1; i < E; ++i) A *= fa[i];
+#pragma unroll
+        for (int i = 0; i < E; ++i) om[i] = 1.f - fa[i];
+        float Alvl[5];
+#pragma unroll
+        for (int k = 0; k < 5; ++k) {
+            Alvl[k] = A;
+            const float pA = __shfl_up_sync(kFullMask, A, 1 << k);
+            if (lane >= (1 << k)) A *= pA;
+        }
+        float eA = __shfl_up_sync(kFullMask, A, 1);
+        if (lane == 0) eA = 1.f;
+        const float tA = __shfl_sync(kFullMask, A, 31);
+
+#pragma unroll
+        for (int d = 0; d < DC; ++d) {
+            float fx[E];
+            Store<S>::unpack(xs[buf][d][lane], fx);
+#pragma unroll
+            for (int i = 0; i < E; ++i) fx[i] *= om[i];
+            float H = fx[0];
+#pragma unroll
+            for (int i = 1; i < E; ++i) H = fmaf(fa[i], H, fx[i]);
+#pragma unroll
+            for (int k = 0; k < 5; ++k) {
+                const float pH = __shfl_up_sync(kFullMask, H, 1 << k);
+                if (lane >= (1 << k)) H = fmaf(Alvl[k], pH, H);
+            }
+            float eH = __shfl_up_sync(kFullMask, H, 1);
+            if (lane == 0) eH = 0.f;
+            const float tH = __shfl_sync(kFullMask, H, 31);
+            float s_ = fmaf(eA, carry[d], eH);
+            carry[d] = fmaf(tA, carry[d], tH);
+            float out[E];
+#pragma unroll
+            for (int i = 0; i < E; ++i) {
+                s_ = fmaf(fa[i], s_, fx[i]);
+                out[i] = s_;
+            }
+            if (in && have_m && d0 + d < D) stg_stream(states + (row0 + d) * L + t, Store<S>::pack(out));
+        }
+#pragma unroll
+        for (int k = 0; k < XPW; ++k)
+            if (w + k * MC < DC) xs[buf ^ 1u][w + k * MC][lane] = xq[k];
+    }
+}
+
+// Dynamic shared memory fm_backward_blocked_kernel needs.
 template <typename S, int MC, int DC>
 constexpr size_t fm_backward_blocked_smem() {
     return sizeof(uint4) * 2 * DC * 32 + sizeof(float4) * MC * DC * (Store<S>::E / 4) * 32;

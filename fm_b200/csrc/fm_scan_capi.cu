@@ -423,6 +423,20 @@ int launch_fm_backward(const FmShape &sh, bool aligned, const void *gates, const
     return check_launch();
 }
 
+// Blocked forward (fm_kernels.cuh): 8 gate rows x 8 token rows per CTA, aligned tensors only.
+template <typename S>
+int launch_fm_forward_blocked(const FmShape &sh, const void *gates, const void *tokens, const float *h0,
+                              void *states, cudaStream_t st) {
+    constexpr int MC = 8, DC = 8;
+    const int64_t m_blocks = (sh.M + MC - 1) / MC, d_blocks = (sh.D + DC - 1) / DC;
+    if (sh.B > 0x7fffffffLL / m_blocks || sh.B * m_blocks > 0x7fffffffLL / d_blocks) return FMS_ERR_BAD_SHAPE;
+    const unsigned grid = static_cast<unsigned>(sh.B * m_blocks * d_blocks);
+    fms::fm_forward_blocked_kernel<S, MC, DC><<<grid, MC * 32, 0, st>>>(
+        static_cast<const S *>(gates), static_cast<const S *>(tokens), h0, static_cast<S *>(states), sh.M, sh.D,
+        sh.L, m_blocks, d_blocks);
+    return check_launch();
+}
+
 // Blocked backward (fm_kernels.cuh): 8 gate rows x 8 token rows per CTA, aligned tensors only.
 template <typename S>
 int launch_fm_backward_blocked(const FmShape &sh, const void *gates, const void *tokens, const void *states,
@@ -489,6 +503,9 @@ FMS_EXPORT int fms_fm_forward(const void *gates, const void *tokens, const float
     bool aligned = false;
     if (int rc = fm_alignment(aligned, L, dtype, gates, tokens, static_cast<const void *>(states))) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (aligned && tune_value("FMS_TUNE_FM_BLOCKED", 1) != 0) {
+        FMS_DISPATCH_DTYPE(dtype, (launch_fm_forward_blocked<S>(sh, gates, tokens, h0, states, st)));
+    }
     FMS_DISPATCH_DTYPE(dtype, (launch_fm_forward<S>(sh, aligned, gates, tokens, h0, states, st)));
 }
 

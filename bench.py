@@ -43,9 +43,9 @@ UNIT = "elements/s"
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 CPU_SAMPLE_ROWS = 4096
-# DRAM traffic of the backward kernel per algorithmic byte, from the ncu capture summarised in
-# profiles/plain_fwd_bwd_bf16_rows4096_T8192.md (small case; traffic is proportional to rows):
-# reads 201.38 MB against 201.33 MB algorithmic, writes algorithmic.
+# DRAM traffic of the backward kernel per algorithmic byte, from an ncu capture of the same kernel
+# on 4096 rows x T=8192 bf16 (traffic is proportional to rows): reads 201.38 MB against 201.33 MB
+# algorithmic, writes algorithmic.
 NCU_BWD_READ_RATIO = 201.38 / 201.33
 
 

@@ -30,7 +30,9 @@ import numpy as np
 import torch
 
 HERE = Path(__file__).resolve().parent
-REF = os.environ.get("FM_REFERENCE", "/root/reference")
+REF = os.environ.get("FM_REFERENCE")
+if not REF:
+    raise SystemExit("set FM_REFERENCE to a checkout of lexionbear/fm")
 sys.path.insert(0, REF)
 from fm.scan.fm_pytorch import fm_scan_pytorch  # noqa: E402  (the reference itself)
 

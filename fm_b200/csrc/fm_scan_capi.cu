@@ -577,7 +577,8 @@ FMS_EXPORT int fms_fm_backward(const void *gates, const void *tokens, const void
 namespace {
 
 constexpr int64_t kSplitTargetUnits = 148 * 32;  // enough one-warp units to fill the GPU
-constexpr int64_t kSplitMinSegment = 4096;       // positions; shorter segments only add carries
+constexpr int64_t kSplitMinLength = 8192;        // rows shorter than this are never split
+constexpr int64_t kSplitMinSegment = 2048;       // positions; shorter segments only add carries
 constexpr int64_t kSplitQuantum = 1024;          // segment lengths are multiples of this, so
                                                  // segments of aligned rows stay 16-byte aligned
 
@@ -588,7 +589,7 @@ struct SplitPlan {
 
 SplitPlan plan_split(int64_t rows, int64_t T) {
     SplitPlan p{1, T, rows, 0};
-    if (rows <= 0 || T < 2 * kSplitMinSegment || rows >= kSplitTargetUnits / 2) return p;
+    if (rows <= 0 || T < kSplitMinLength || rows >= kSplitTargetUnits / 2) return p;
     int64_t want = (kSplitTargetUnits + rows - 1) / rows;
     want = std::min<int64_t>(want, T / kSplitMinSegment);
     if (want < 2) return p;

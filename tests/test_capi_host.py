@@ -81,3 +81,39 @@ def test_ops_refuse_cpu_tensors():
     from fm_b200.ops import CudaScanOps
     with pytest.raises(RuntimeError, match="CUDA"):
         CudaScanOps.forward(torch.zeros(2, 8), torch.zeros(2, 8))
+
+
+def test_fm_mode_argument_checks_need_no_device():
+    L = capi.lib()
+    buf = (ctypes.c_char * 256)()
+    p = (ctypes.addressof(buf) + 15) // 16 * 16
+    fwd = lambda *a: capi.call("fms_fm_forward", *a, check=False)
+    assert fwd(p, p, None, p, 1, 2, 3, 8, 42, None) == capi.FMS_ERR_BAD_DTYPE
+    assert fwd(p, p, None, p, 1, -2, 3, 8, capi.FMS_F32, None) == capi.FMS_ERR_BAD_SHAPE
+    assert fwd(p, p, None, p, 2 ** 31, 2 ** 31, 2 ** 31, 8, capi.FMS_F32, None) == capi.FMS_ERR_BAD_SHAPE
+    assert fwd(p, None, None, p, 1, 2, 3, 8, capi.FMS_F32, None) == capi.FMS_ERR_NULL_POINTER
+    assert fwd(p + 2, p, None, p, 1, 2, 3, 8, capi.FMS_F32, None) == capi.FMS_ERR_MISALIGNED
+    assert fwd(None, None, None, None, 0, 2, 3, 8, capi.FMS_F32, None) == capi.FMS_OK  # empty batch
+    # fp32 gradients accumulate in place; 16-bit ones need fp32 accumulators for both outputs
+    assert L.fms_fm_backward_workspace_bytes(1, 32, 2048, 8192, capi.FMS_F32) == 0
+    assert L.fms_fm_backward_workspace_bytes(1, 32, 2048, 8192, capi.FMS_BF16) == (32 + 2048) * 8192 * 4
+    assert L.fms_fm_backward_workspace_bytes(1, 32, 2048, 8192, 9) == 0
+    rc = capi.call("fms_fm_backward", p, p, p, p, None, p, p, None, 1, 2, 3, 8, capi.FMS_BF16, None, 0, None,
+                   check=False)
+    assert rc == capi.FMS_ERR_WORKSPACE
+
+
+def test_split_plan_is_pure_arithmetic():
+    L = capi.lib()
+    assert L.fms_plain_split_segments(32768, 8192, capi.FMS_BF16) == 1      # plenty of rows
+    assert L.fms_plain_split_segments(4, 8191, capi.FMS_F32) == 1           # too short to split
+    nseg = L.fms_plain_split_segments(4, 1 << 20, capi.FMS_F32)
+    assert nseg > 1 and 4 * nseg >= 148 * 8 and (1 << 20) // nseg >= 2048
+    assert L.fms_plain_split_workspace_bytes(4, 1 << 20, capi.FMS_F32) >= 4 * nseg * 12
+    assert L.fms_plain_split_workspace_bytes(32768, 8192, capi.FMS_BF16) == 0
+    # the built-in scratch refuses more units than it holds, before touching the device
+    buf = (ctypes.c_char * 64)()
+    p = (ctypes.addressof(buf) + 15) // 16 * 16
+    rc = capi.call("fms_plain_forward_split_static", p, p, None, p, None, 2000, 16384, capi.FMS_F32, None,
+                   check=False)
+    assert rc == capi.FMS_ERR_TOO_LARGE

@@ -1,18 +1,22 @@
-// Device code of the B200 scan: PLAIN-mode forward, backward and carry-only (reduce) kernels.
+// Device code of the B200 scan: forward, backward and carry-only (reduce) kernels.
 //
 // Work decomposition
-//   One warp owns one row and walks it along time in groups of U tiles.  A tile is 32 lanes x
-//   one 16-byte vector (E = 4 fp32 or 8 fp16/bf16 elements per lane), i.e. 512 contiguous bytes
-//   per tensor per warp instruction, so every global access is a fully coalesced 128-bit
-//   access.  The loads of group g+1 are issued into registers before group g is computed, which
-//   keeps U x (number of input tensors) x 512 B in flight per warp across the serial carry.
+//   K warps own one scan unit (a row, or a segment of a row) and walk it along time in
+//   super-tiles of K*U tiles.  A tile is 32 lanes x one 16-byte vector (E = 4 fp32 or 8 fp16/bf16
+//   elements per lane), i.e. 512 contiguous bytes per tensor per warp instruction, so every
+//   global access is a fully coalesced 128-bit access and a CTA reads K*U*512 contiguous bytes
+//   per tensor per step.  The loads of step g+1 are issued into registers before step g is
+//   computed, which keeps U x (number of input tensors) x 512 B in flight per warp across the
+//   serial carry.  K == 1 packs four independent units into a CTA and uses no block barrier;
+//   K > 1 exchanges the warps' aggregates through double-buffered shared memory with one
+//   __syncthreads per super-tile.
 //
 //   Inside a tile: each lane scans its E elements sequentially to an aggregate pair
 //   (A, H) = (prod a, state from a zero start); the 32 pairs are combined with a 5-step
 //   warp-shuffle scan under the associative operator
 //        (A2, H2) o (A1, H1) = (A2*A1, A2*H1 + H2)          ("1" earlier in time than "2");
-//   the lane's carry-in follows from the exclusive prefix and the running row carry, and the
-//   lane re-runs its E elements sequentially from that carry-in to produce the outputs.  Only
+//   the lane's carry-in follows from the exclusive prefix and the running carry, and the lane
+//   re-runs its E elements sequentially from that carry-in to produce the outputs.  Only
 //   multiply-add pairs are used, so gates that are exactly 0 or 1 need no special case.
 //
 //   Backward uses the substitution c_t = a_t * delta_t (delta_t = G_t + c_{t+1}), which turns the
@@ -24,6 +28,10 @@
 // GENERIC instantiation: tiles are laid on the 16-byte grid of the gates row, vectors that
 // straddle a row end or belong to a tensor with a different phase are read/written element by
 // element under a mask, and masked positions carry the identity (a = 1, x = 0).
+//
+// Other template flags: WRITE (false = carries only), SEG (units are segments of rows: the split
+// path for few long rows), FM (the reference's (B,M,L) x (B,D,L) -> (B,M,D,L) operator with the
+// 1 - gate token weight; its blocked variants live in fm_kernels.cuh).
 #pragma once
 
 #include <cuda_bf16.h>

@@ -83,7 +83,22 @@ class _TimeSplitScan(torch.autograd.Function):
         return grad_gates, grad_tokens, d_h0, None, None
 
 
-def fm_scan_time_split(gates, tokens, initial_state=None, group=None, ops=None):
+def _validate_layout(gates, group):
+    """Every rank must hold the same rows (B, D) in the same dtype; a mismatch would otherwise
+    surface as a hang or as garbage carries.  One small all-gather of a descriptor."""
+    rows = 1
+    for s in gates.shape[:-1]:
+        rows *= s
+    code = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2, torch.float64: 3}.get(gates.dtype, -1)
+    mine = torch.tensor([rows, gates.dim(), code], device=gates.device, dtype=torch.int64)
+    everyone = _gather(mine, group)
+    if not bool((everyone == mine).all()):
+        raise RuntimeError(
+            "fm_scan_time_split: ranks disagree on (rows, rank of tensor, dtype): "
+            f"{everyone.tolist()} -- every rank must hold the same (B, D) rows of one dtype")
+
+
+def fm_scan_time_split(gates, tokens, initial_state=None, group=None, ops=None, validate=False):
     """Differentiable scan of this rank's time block; ranks are ordered along T by group rank.
 
     Arguments:
@@ -91,6 +106,8 @@ def fm_scan_time_split(gates, tokens, initial_state=None, group=None, ops=None):
         initial_state: (B, D) state before the first block; only rank 0's values are used.
         group: process group spanning the time blocks (default: the world group).
         ops: local scan passes (default ``CudaScanOps``).
+        validate: exchange a shape/dtype descriptor first and raise on every rank if the ranks
+            disagree (one extra small all-gather; off by default).
     Returns:
         states of this rank's block, (B, D, T_k).
     """
@@ -98,4 +115,6 @@ def fm_scan_time_split(gates, tokens, initial_state=None, group=None, ops=None):
         raise RuntimeError("fm_scan_time_split needs an initialised torch.distributed process group")
     if gates.shape != tokens.shape:
         raise RuntimeError("gates and tokens must have the same shape")
+    if validate:
+        _validate_layout(gates, group)
     return _TimeSplitScan.apply(gates, tokens, initial_state, group, ops or CudaScanOps)

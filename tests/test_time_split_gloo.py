@@ -83,3 +83,27 @@ def test_shard_rows_returns_contiguous_views():
     parts = [sharding.shard_rows(t, r, 4) for r in range(4)]
     assert torch.equal(torch.cat(parts), t.view(12, 5))
     assert all(p.is_contiguous() for p in parts)
+
+
+def _mismatch_worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from fm_b200.time_split import fm_scan_time_split
+        from tests.cpu_ops import OracleScanOps
+        rows = 6 if rank == 0 else 5          # rank 1 holds a different number of rows
+        a = torch.rand(1, rows, 16, dtype=torch.float64)
+        try:
+            fm_scan_time_split(a, a.clone(), ops=OracleScanOps, validate=True)
+            outcome = "no error"
+        except RuntimeError as e:
+            outcome = "raised" if "disagree" in str(e) else f"other: {e}"
+        with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:
+            f.write(outcome)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_time_split_reports_mismatched_rows_on_every_rank(tmp_path):
+    mp.spawn(_mismatch_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    assert [(tmp_path / f"rank{r}.txt").read_text() for r in range(2)] == ["raised", "raised"]

@@ -437,12 +437,38 @@ def run_fm_mode(args):
     bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
     n = B * M * D * L
     peak, kind = measured_peak()
+
+    # the layer around the scan (inference): with the states materialised, and read out directly
+    from fm_b200 import fm_memory
+    del G, h
+    alpha = torch.softmax(torch.randn(B, L, M, device=dev, generator=gen), dim=-1).to(torch.bfloat16)
+    upd = torch.sigmoid(torch.randn(B, L, 1, device=dev, generator=gen)).to(torch.bfloat16)
+    outs = torch.sigmoid(torch.randn(B, L, 1, device=dev, generator=gen)).to(torch.bfloat16)
+    inp = torch.randn(B, L, D, device=dev, generator=gen).to(torch.bfloat16)
+
+    def layer_ms(need_states):
+        with torch.no_grad():
+            for _ in range(3):
+                fm_memory(alpha, upd, outs, inp, need_states=need_states)
+            torch.cuda.synchronize()
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record()
+            for _ in range(max(1, K // 2)):
+                fm_memory(alpha, upd, outs, inp, need_states=need_states)
+            s1.record()
+            torch.cuda.synchronize()
+        return s0.elapsed_time(s1) / max(1, K // 2)
+
+    layer_states_ms = layer_ms(True)
+    layer_fused_ms = layer_ms(False)
     line = {"metric": "FM-mode scan fwd+bwd output elements/s", "value": n / ((fwd_ms + bwd_ms) * 1e-3),
             "unit": UNIT, "n_gpus": 1, "steps": K, "warmup": max(3, args.warmup),
             "ms_per_step": fwd_ms + bwd_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": "FM mode (B,M,D,L)=(%d,%d,%d,%d) bf16 storage / fp32 accumulate" % (B, M, D, L)},
             "gpu_launches": K * 5, "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
+            "layer_forward_ms": {"states_materialised_torch_epilogue": layer_states_ms,
+                                 "read_out_without_states": layer_fused_ms},
             "roofline_forward": {"algorithmic_bytes_per_launch": 2 * n + 2 * (M + D) * B * L,
                                  "achieved": (2 * n + 2 * (M + D) * B * L) / (fwd_ms * 1e-3) / 1e9,
                                  "peak": peak, "peak_kind": kind, "unit": "GB/s"},

@@ -300,7 +300,180 @@ fm_forward_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ tok
     }
 }
 
-// Dynamic shared memory fm_backward_blocked_kernel needs.
+// The layer's read-out without materialising the states (fm/scan/fm_scan.py:122-131 computes
+// states (B,M,D,L), RMS-normalises them over D and contracts them with the output weight over
+// M).  Two launches of this kernel recompute the scan instead of storing it:
+//   MODE 0: sumsq[b,m,t]  += sum over the CTA's token rows of h[b,m,d,t]^2
+//   MODE 1: out32[b,d,t]  += sum over the CTA's gate rows of scale[b,m,t] * h[b,m,d,t]
+// with scale = output_weight * rsqrt(sumsq / D + eps) formed in between (or just the output
+// weight when the norm is off).  Same blocking as fm_forward_blocked_kernel; HBM sees only the
+// gate, token, scale and output rows -- the (B,M,D,L) tensor never exists.
+template <typename S, int MC, int DC, int MODE>
+__global__ void __launch_bounds__(MC * 32)
+fm_readout_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
+                          const float *__restrict__ h0, const float *__restrict__ scale,
+                          float *__restrict__ sumsq, float *__restrict__ out32, int64_t M, int64_t D,
+                          int64_t L, int64_t m_blocks, int64_t d_blocks) {
+    constexpr int E = Store<S>::E;
+    constexpr int W = 32 * E;
+    extern __shared__ __align__(16) unsigned char fm_smem[];
+    uint4(*xs)[DC][32] = reinterpret_cast<uint4(*)[DC][32]>(fm_smem);
+    float4(*part)[DC][E / 4][32] =
+        reinterpret_cast<float4(*)[DC][E / 4][32]>(fm_smem + sizeof(uint4) * 2 * DC * 32);  // MODE 1 only
+    const int lane = threadIdx.x & 31;
+    const int w = threadIdx.x >> 5;
+    const int64_t blk = blockIdx.x;
+    const int64_t db = blk % d_blocks, mb = (blk / d_blocks) % m_blocks, b = blk / (d_blocks * m_blocks);
+    const int64_t m = mb * MC + w, d0 = db * DC;
+    const bool have_m = m < M;
+    const int64_t ntiles = (L + W - 1) / W;
+    const int64_t grow_off = (b * M + (have_m ? m : 0)) * L;
+    const S *grow = gates + grow_off;
+    const int64_t row0 = ((b * M + (have_m ? m : 0)) * D + d0);
+
+    float carry[DC];
+#pragma unroll
+    for (int d = 0; d < DC; ++d) carry[d] = (h0 && have_m && d0 + d < D) ? h0[row0 + d] : 0.f;
+
+    auto load_x = [&](int64_t tile, int d) -> uint4 {
+        const int64_t tt = tile * W + lane * E;
+        return (tile < ntiles && tt < L && d < DC && d0 + d < D)
+                   ? ldg_stream(tokens + (b * D + d0 + d) * L + tt)
+                   : make_uint4(0u, 0u, 0u, 0u);
+    };
+    auto load_g = [&](int64_t tile) -> uint4 {
+        const int64_t tt = tile * W + lane * E;
+        return (tile < ntiles && tt < L && have_m)
+                   ? ldg_stream(grow + tt)
+                   : make_uint4(Store<S>::kOne, Store<S>::kOne, Store<S>::kOne, Store<S>::kOne);
+    };
+    constexpr int XPW = (DC + MC - 1) / MC;
+    uint4 gq = load_g(0), xq[XPW];
+#pragma unroll
+    for (int k = 0; k < XPW; ++k)
+        if (w + k * MC < DC) xs[0][w + k * MC][lane] = load_x(0, w + k * MC);
+
+    for (int64_t tile = 0; tile < ntiles; ++tile) {
+        const int64_t t = tile * W + lane * E;
+        const bool in = t < L;
+        const unsigned buf = static_cast<unsigned>(tile) & 1u;
+        __syncthreads();  // xs[buf] staged; previous flush done
+        float fa[E], om[E], sc[E], ss[E];
+        Store<S>::unpack(gq, fa);
+        gq = load_g(tile + 1);
+#pragma unroll
+        for (int k = 0; k < XPW; ++k) xq[k] = load_x(tile + 1, w + k * MC);
+#pragma unroll
+        for (int i = 0; i < E; ++i) {
+            sc[i] = 0.f;
+            ss[i] = 0.f;
+        }
+        if constexpr (MODE == 1) {
+            if (in && have_m) {
+#pragma unroll
+                for (int k = 0; k < E / 4; ++k) {
+                    const float4 q4 = *reinterpret_cast<const float4 *>(scale + grow_off + t + 4 * k);
+                    sc[4 * k] = q4.x;
+                    sc[4 * k + 1] = q4.y;
+                    sc[4 * k + 2] = q4.z;
+                    sc[4 * k + 3] = q4.w;
+                }
+            }
+        }
+        float A = fa[0];
+#pragma unroll
+        for (int i = 1; i < E; ++i) A *= fa[i];
+#pragma unroll
+        for (int i = 0; i < E; ++i) om[i] = 1.f - fa[i];
+        float Alvl[5];
+#pragma unroll
+        for (int k = 0; k < 5; ++k) {
+            Alvl[k] = A;
+            const float pA = __shfl_up_sync(kFullMask, A, 1 << k);
+            if (lane >= (1 << k)) A *= pA;
+        }
+        float eA = __shfl_up_sync(kFullMask, A, 1);
+        if (lane == 0) eA = 1.f;
+        const float tA = __shfl_sync(kFullMask, A, 31);
+
+#pragma unroll
+        for (int d = 0; d < DC; ++d) {
+            float fx[E];
+            Store<S>::unpack(xs[buf][d][lane], fx);
+#pragma unroll
+            for (int i = 0; i < E; ++i) fx[i] *= om[i];
+            float H = fx[0];
+#pragma unroll
+            for (int i = 1; i < E; ++i) H = fmaf(fa[i], H, fx[i]);
+#pragma unroll
+            for (int k = 0; k < 5; ++k) {
+                const float pH = __shfl_up_sync(kFullMask, H, 1 << k);
+                if (lane >= (1 << k)) H = fmaf(Alvl[k], pH, H);
+            }
+            float eH = __shfl_up_sync(kFullMask, H, 1);
+            if (lane == 0) eH = 0.f;
+            const float tH = __shfl_sync(kFullMask, H, 31);
+            float s_ = fmaf(eA, carry[d], eH);
+            carry[d] = fmaf(tA, carry[d], tH);
+            const bool row_ok = have_m && d0 + d < D;
+            float contrib[E];
+#pragma unroll
+            for (int i = 0; i < E; ++i) {
+                s_ = fmaf(fa[i], s_, fx[i]);
+                if constexpr (MODE == 0) {
+                    if (row_ok) ss[i] = fmaf(s_, s_, ss[i]);
+                } else {
+                    contrib[i] = sc[i] * s_;  // sc is zero for lanes and gate rows outside the problem
+                }
+            }
+            if constexpr (MODE == 1) {
+#pragma unroll
+                for (int k = 0; k < E / 4; ++k)
+                    part[w][d][k][lane] =
+                        make_float4(contrib[4 * k], contrib[4 * k + 1], contrib[4 * k + 2], contrib[4 * k + 3]);
+            }
+        }
+        if constexpr (MODE == 0) {
+            if (in && have_m) red_vec<E, false>(sumsq + grow_off, t, L, ss);
+        }
+#pragma unroll
+        for (int k = 0; k < XPW; ++k)
+            if (w + k * MC < DC) xs[buf ^ 1u][w + k * MC][lane] = xq[k];
+        if constexpr (MODE == 1) {
+            __syncthreads();  // every warp has published its tiles
+#pragma unroll
+            for (int d = w; d < DC; d += MC) {
+                float v[E];
+#pragma unroll
+                for (int i = 0; i < E; ++i) v[i] = 0.f;
+#pragma unroll
+                for (int ww = 0; ww < MC; ++ww)
+#pragma unroll
+                    for (int k = 0; k < E / 4; ++k) {
+                        const float4 p = part[ww][d][k][lane];
+                        v[4 * k] += p.x;
+                        v[4 * k + 1] += p.y;
+                        v[4 * k + 2] += p.z;
+                        v[4 * k + 3] += p.w;
+                    }
+                if (in && d0 + d < D) red_vec<E, false>(out32 + (b * D + d0 + d) * L, t, L, v);
+            }
+        }
+    }
+}
+
+// scale[b,m,t] = weight[b,m,t] * rsqrt(sumsq[b,m,t] / D + eps)   (in place over sumsq)
+template <typename S>
+__global__ void fm_readout_scale_kernel(float *__restrict__ sumsq_to_scale, const S *__restrict__ weight,
+                                        int64_t n, float inv_d, float eps, int use_norm) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n) {
+        const float wgt = Store<S>::to_float(weight[i]);
+        sumsq_to_scale[i] = use_norm ? wgt * rsqrtf(sumsq_to_scale[i] * inv_d + eps) : wgt;
+    }
+}
+
+// Dynamic shared memory fm_backward_blocked_kernel and fm_readout_blocked_kernel need.
 template <typename S, int MC, int DC>
 constexpr size_t fm_backward_blocked_smem() {
     return sizeof(uint4) * 2 * DC * 32 + sizeof(float4) * MC * DC * (Store<S>::E / 4) * 32;

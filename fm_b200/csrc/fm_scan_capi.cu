@@ -573,6 +573,76 @@ FMS_EXPORT int fms_fm_backward(const void *gates, const void *tokens, const void
     FMS_DISPATCH_DTYPE(dtype, (launch_cast<S>(acc_x, grad_tokens, n_x, st)));
 }
 
+// ------------------------------------------------------------------ FM layer read-out -------
+namespace {
+
+template <typename S>
+int launch_fm_readout(const FmShape &sh, const void *gates, const void *tokens, const void *weight,
+                      const float *h0, float *scale, float *out32, void *out, int mem_norm, float eps,
+                      cudaStream_t st) {
+    constexpr int MC = 8, DC = 8;
+    const int64_t m_blocks = (sh.M + MC - 1) / MC, d_blocks = (sh.D + DC - 1) / DC;
+    if (sh.B > 0x7fffffffLL / m_blocks || sh.B * m_blocks > 0x7fffffffLL / d_blocks) return FMS_ERR_BAD_SHAPE;
+    const unsigned grid = static_cast<unsigned>(sh.B * m_blocks * d_blocks);
+    constexpr size_t smem = fms::fm_backward_blocked_smem<S, MC, DC>();
+    const int64_t n_g = sh.B * sh.M * sh.L, n_x = sh.B * sh.D * sh.L;
+    auto k0 = fms::fm_readout_blocked_kernel<S, MC, DC, 0>;
+    auto k1 = fms::fm_readout_blocked_kernel<S, MC, DC, 1>;
+    static const cudaError_t a0 =
+        cudaFuncSetAttribute(k0, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    static const cudaError_t a1 =
+        cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (int rc = record(a0)) return rc;
+    if (int rc = record(a1)) return rc;
+    if (int rc = record(cudaMemsetAsync(scale, 0, static_cast<size_t>(n_g + n_x) * sizeof(float), st))) return rc;
+    if (mem_norm) {
+        k0<<<grid, MC * 32, smem, st>>>(static_cast<const S *>(gates), static_cast<const S *>(tokens), h0, nullptr,
+                                        scale, nullptr, sh.M, sh.D, sh.L, m_blocks, d_blocks);
+        if (int rc = check_launch()) return rc;
+    }
+    const int64_t blocks = (n_g + 255) / 256;
+    if (blocks > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;
+    fms::fm_readout_scale_kernel<S><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+        scale, static_cast<const S *>(weight), n_g, 1.f / static_cast<float>(sh.D), eps, mem_norm ? 1 : 0);
+    if (int rc = check_launch()) return rc;
+    k1<<<grid, MC * 32, smem, st>>>(static_cast<const S *>(gates), static_cast<const S *>(tokens), h0, scale, nullptr,
+                                    out32, sh.M, sh.D, sh.L, m_blocks, d_blocks);
+    if (int rc = check_launch()) return rc;
+    return launch_cast<S>(out32, out, n_x, st);
+}
+
+}  // namespace
+
+FMS_EXPORT size_t fms_fm_readout_workspace_bytes(int64_t B, int64_t M, int64_t D, int64_t L, int dtype) {
+    FmShape sh;
+    if (make_fm_shape(sh, B, M, D, L, dtype) != FMS_OK || sh.rows == 0 || L == 0) return 0;
+    return (fm_acc_elems(sh) * sizeof(float) + 255) / 256 * 256;
+}
+
+FMS_EXPORT int fms_fm_readout(const void *gates, const void *tokens, const void *out_weight, const float *h0,
+                              void *out, int64_t B, int64_t M, int64_t D, int64_t L, int dtype, int mem_norm,
+                              float eps, void *workspace, size_t workspace_bytes, fms_stream_t stream) {
+    FmShape sh;
+    if (int rc = make_fm_shape(sh, B, M, D, L, dtype)) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (B == 0 || D == 0 || L == 0) return FMS_OK;
+    if (M == 0) {
+        if (!out) return FMS_ERR_NULL_POINTER;
+        return record(cudaMemsetAsync(out, 0, static_cast<size_t>(B) * D * L * elem_size(dtype), st));
+    }
+    bool aligned = false;
+    if (int rc = fm_alignment(aligned, L, dtype, gates, tokens, out_weight, static_cast<const void *>(out)))
+        return rc;
+    if (!aligned || (static_cast<uint64_t>(L) * sizeof(float)) % 16 != 0) return FMS_ERR_MISALIGNED;
+    const size_t need = fms_fm_readout_workspace_bytes(B, M, D, L, dtype);
+    if (!workspace || !aligned_to(workspace, 16) || workspace_bytes < need) return FMS_ERR_WORKSPACE;
+    float *scale = static_cast<float *>(workspace);
+    float *out32 = scale + static_cast<size_t>(B) * M * L;
+    if (!aligned_to(out32, 16)) return FMS_ERR_WORKSPACE;
+    FMS_DISPATCH_DTYPE(dtype, (launch_fm_readout<S>(sh, gates, tokens, out_weight, h0, scale, out32, out, mem_norm,
+                                                    eps, st)));
+}
+
 // ------------------------------------------------------------------ split inside one GPU ----
 namespace {
 

@@ -207,6 +207,33 @@ void fm_scan_backward_fm(const at::Tensor &gates, const at::Tensor &outGrad, con
                  "fm_scan_backward");
 }
 
+// Layer read-out without the states (inference): out (B,D,L) = sum_m weight * [rms-norm] * states.
+// gates, weight (B,M,L); tokens, out (B,D,L); initial_state (B,M,D) or None.
+void fm_memory_readout(const at::Tensor &gates, const at::Tensor &tokens, const at::Tensor &weight,
+                       const c10::optional<at::Tensor> &initial_state, const at::Tensor &out, bool mem_norm,
+                       double eps) {
+    TORCH_CHECK(gates.is_cuda() && gates.is_contiguous() && gates.dim() == 3, "gates must be a contiguous CUDA (B,M,L) tensor");
+    TORCH_CHECK(tokens.dim() == 3, "tokens must be (B,D,L)");
+    const int64_t B = gates.size(0), M = gates.size(1), L = gates.size(2), D = tokens.size(1);
+    auto same = [&](const at::Tensor &t, at::IntArrayRef shape, const char *name) {
+        TORCH_CHECK(t.is_cuda() && t.is_contiguous() && t.scalar_type() == gates.scalar_type() &&
+                        t.device() == gates.device() && t.sizes() == shape,
+                    name, " must be a contiguous CUDA tensor of shape ", shape, " with the dtype of gates");
+    };
+    same(tokens, {B, D, L}, "tokens");
+    same(weight, {B, M, L}, "weight");
+    same(out, {B, D, L}, "out");
+    const int dtype = dtype_tag(gates);
+    const c10::cuda::CUDAGuard guard(gates.device());
+    at::Tensor h0 = carry_f32(initial_state, B * M * D, gates, "initial_state");
+    const size_t scratch = fms_fm_readout_workspace_bytes(B, M, D, L, dtype);
+    at::Tensor ws = at::empty({static_cast<int64_t>(std::max<size_t>(scratch, 16))}, gates.options().dtype(at::kByte));
+    check_status(fms_fm_readout(gates.data_ptr(), tokens.data_ptr(), weight.data_ptr(), fptr(h0), out.data_ptr(), B,
+                                M, D, L, dtype, mem_norm ? 1 : 0, static_cast<float>(eps), ws.data_ptr(), scratch,
+                                at::cuda::getCurrentCUDAStream().stream()),
+                 "fm_memory_readout");
+}
+
 // Backward with the reference's seven arguments.  firstPropGrad seeds the reverse scan
 // (fm/scan/fm_scan.cuh:120-122); the reference passes zeros (fm/scan/fm_scan.py:65).
 // input_tokens is accepted for signature compatibility and not read: with the token weight
@@ -233,5 +260,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("fm_scan_backward", &fm_scan_backward, "scan backward, reference signature");
     m.def("fm_scan_backward_ex", &fm_scan_backward_ex, "scan backward with h0 / carry_in / grad_h0");
     m.def("fm_scan_backward_fm", &fm_scan_backward_fm, "FM-mode backward with fused reductions");
+    m.def("fm_memory_readout", &fm_memory_readout, "layer read-out without materialising the states");
     m.def("abi_version", []() { return fms_version(); });
 }

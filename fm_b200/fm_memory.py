@@ -8,20 +8,44 @@ from __future__ import annotations
 
 import torch
 
-from .fm_scan import fm_scan
+from .fm_scan import _load_ext, fm_scan
 
 
-def fm_memory(alpha, update_scale, output_scale, inputs, initial_state=None, mem_norm=True, norm_eps=1e-6):
+def _fused_readout_applies(need_states, tensors, L):
+    """The no-states path: nothing needs a gradient, the caller does not want the states, and rows
+    are 16-byte aligned."""
+    if need_states:
+        return False
+    if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors):
+        return False
+    return (L * tensors[0].element_size()) % 16 == 0 and (L * 4) % 16 == 0
+
+
+def fm_memory(alpha, update_scale, output_scale, inputs, initial_state=None, mem_norm=True, norm_eps=1e-6,
+              need_states=True):
     """
     alpha: (B, L, M)   update_scale: (B, L, 1)   output_scale: (B, L, 1)   inputs: (B, L, D)
     initial_state: (B, M, D)   mem_norm: bool   norm_eps: float
 
     return: output (B, L, D), memory_states (B, M, D, L)
+
+    ``need_states=False`` (inference): when no argument requires a gradient the layer output is
+    computed by recomputing the scan inside two read-out kernels and the (B, M, D, L) states are
+    never written; ``memory_states`` is then returned as None.  The norm is evaluated in fp32
+    there, where the reference evaluates it in the storage dtype.
     """
     update_weight = alpha * update_scale                                 # fm_scan.py:117
     tokens = inputs.transpose(1, 2).contiguous()                         # (B, D, L)  fm_scan.py:118
     update_weight = update_weight.transpose(1, 2).contiguous()           # (B, M, L)  fm_scan.py:119
     decay_weight = 1.0 - update_weight                                   # fm_scan.py:120
+
+    if _fused_readout_applies(need_states, (alpha, update_scale, output_scale, inputs, initial_state),
+                              tokens.shape[-1]):
+        out_weight = (alpha * output_scale).transpose(1, 2).contiguous()  # (B, M, L)
+        out = torch.empty_like(tokens)                                    # (B, D, L)
+        _load_ext().fm_memory_readout(decay_weight, tokens, out_weight, initial_state, out, bool(mem_norm),
+                                      float(norm_eps))
+        return out.transpose(1, 2).contiguous(), None
 
     memory_states = fm_scan(decay_weight, tokens, initial_state, mode="fm")  # (B, M, D, L)  fm_scan.py:122
 

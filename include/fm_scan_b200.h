@@ -157,6 +157,24 @@ int fms_fm_backward(const void *gates, const void *tokens, const void *states, c
                     int64_t M, int64_t D, int64_t L, int dtype, void *workspace, size_t workspace_bytes,
                     fms_stream_t stream);
 
+/*
+ * Read-out of the layer around the scan WITHOUT materialising the states: what
+ * fm/scan/fm_scan.py:122-131 computes as states (B,M,D,L) -> RMS norm over D -> contraction with
+ * the output weight over M, for callers that need only the layer output (inference).
+ *   out[b,d,t] = sum_m w[b,m,t] * rsqrt(mean_d h[b,m,d,t]^2 + eps) * h[b,m,d,t]     (mem_norm != 0)
+ *   out[b,d,t] = sum_m w[b,m,t] * h[b,m,d,t]                                        (mem_norm == 0)
+ * with h the FM-mode states of (gates, tokens, h0).  gates and out_weight are (B,M,L), tokens and
+ * out are (B,D,L), all of the storage dtype.  The scan is recomputed in two passes (sum of
+ * squares, then read-out); HBM traffic is the four small tensors plus fp32 scratch of
+ * fms_fm_readout_workspace_bytes().  Arithmetic is fp32 throughout, including the norm, which the
+ * reference evaluates in the storage dtype.  Requires 16-byte aligned rows (L * element size
+ * % 16 == 0, aligned bases); otherwise FMS_ERR_MISALIGNED is returned and nothing is launched.
+ */
+size_t fms_fm_readout_workspace_bytes(int64_t B, int64_t M, int64_t D, int64_t L, int dtype);
+int fms_fm_readout(const void *gates, const void *tokens, const void *out_weight, const float *h0, void *out,
+                   int64_t B, int64_t M, int64_t D, int64_t L, int dtype, int mem_norm, float eps,
+                   void *workspace, size_t workspace_bytes, fms_stream_t stream);
+
 /* ------------------------------------------------- few, long rows: split inside one GPU ---- */
 
 /*

@@ -124,3 +124,35 @@ def test_fm_memory_layer_matches_loop_restatement(mem_norm):
     for n, a, b in zip(names, got, ref):
         scale = max(1.0, float(b.abs().max()))
         H.assert_close(a.numpy(), b.numpy(), 1e-4, 2e-5 * scale, n)
+
+
+@pytest.mark.parametrize("mem_norm", [True, False])
+@pytest.mark.parametrize("dtype,B,L,M,D", [(torch.float32, 2, 96, 3, 8), (torch.bfloat16, 1, 1024, 12, 37),
+                                            (torch.float32, 1, 520, 9, 17)])
+def test_fm_memory_readout_without_states(mem_norm, dtype, B, L, M, D):
+    """need_states=False: the layer output from the two read-out kernels (states never written)
+    against the torch-loop restatement of the layer in double precision."""
+    from fm_b200 import fm_memory
+    from oracle.torch_loop import fm_memory_loop
+    gen = torch.Generator().manual_seed(21)
+    alpha = torch.softmax(torch.randn(B, L, M, generator=gen), dim=-1)
+    upd = torch.sigmoid(torch.randn(B, L, 1, generator=gen))
+    outs = torch.sigmoid(torch.randn(B, L, 1, generator=gen))
+    inp = torch.randn(B, L, D, generator=gen)
+    h0 = torch.randn(B, M, D, generator=gen)
+    args = [t.to(dtype) for t in (alpha, upd, outs, inp, h0)]
+    with torch.no_grad():
+        out, mem = fm_memory(*(a.cuda() for a in args), mem_norm=mem_norm, need_states=False)
+        out_full, mem_full = fm_memory(*(a.cuda() for a in args), mem_norm=mem_norm)
+    assert mem is None and mem_full is not None and out.shape == (B, L, D)
+    ref, _ = fm_memory_loop(*(a.double() for a in args), mem_norm=mem_norm)
+    scale = max(1.0, float(ref.abs().max()))
+    if dtype == torch.float32:
+        H.assert_close(out.cpu().double().numpy(), ref.numpy(), 1e-4, 2e-5 * scale, "fused read-out")
+    else:
+        H.assert_close(out.float().cpu().numpy(), ref.numpy(), 2e-2, 2e-2 * scale, "fused read-out bf16")
+        H.assert_close(out_full.float().cpu().numpy(), ref.numpy(), 3e-2, 5e-2 * scale, "unfused bf16")
+    # with a gradient requested the layer must keep the differentiable path
+    a0 = args[0].cuda().requires_grad_(True)
+    out2, mem2 = fm_memory(a0, *(a.cuda() for a in args[1:]), mem_norm=mem_norm, need_states=False)
+    assert mem2 is not None and out2.requires_grad

@@ -446,21 +446,46 @@ def run_fm_mode(args):
     outs = torch.sigmoid(torch.randn(B, L, 1, device=dev, generator=gen)).to(torch.bfloat16)
     inp = torch.randn(B, L, D, device=dev, generator=gen).to(torch.bfloat16)
 
-    def layer_ms(need_states):
+    def layer_ms(need_states, fused):
         with torch.no_grad():
             for _ in range(3):
-                fm_memory(alpha, upd, outs, inp, need_states=need_states)
+                fm_memory(alpha, upd, outs, inp, need_states=need_states, fused=fused)
             torch.cuda.synchronize()
             s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             s0.record()
             for _ in range(max(1, K // 2)):
-                fm_memory(alpha, upd, outs, inp, need_states=need_states)
+                fm_memory(alpha, upd, outs, inp, need_states=need_states, fused=fused)
             s1.record()
             torch.cuda.synchronize()
         return s0.elapsed_time(s1) / max(1, K // 2)
 
-    layer_states_ms = layer_ms(True)
-    layer_fused_ms = layer_ms(False)
+    layer_states_ms = layer_ms(True, False)
+    layer_fused_states_ms = layer_ms(True, True)
+    layer_fused_ms = layer_ms(False, True)
+
+    def train_ms(fused):
+        args = [t.clone().requires_grad_(True) for t in (alpha, upd, outs, inp)]
+        Wt = torch.randn(B, L, D, device=dev, generator=gen).to(torch.bfloat16)
+
+        def one():
+            out, _ = fm_memory(*args, fused=fused)
+            torch.autograd.grad((out * Wt).sum(), args)
+
+        for _ in range(2):
+            one()
+        torch.cuda.synchronize()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = max(1, K // 4)
+        s0.record()
+        for _ in range(reps):
+            one()
+        s1.record()
+        torch.cuda.synchronize()
+        return s0.elapsed_time(s1) / reps
+
+    train_fused_ms = train_ms(True)
+    torch.cuda.empty_cache()
+    train_composed_ms = train_ms(False)
     line = {"metric": "FM-mode scan fwd+bwd output elements/s", "value": n / ((fwd_ms + bwd_ms) * 1e-3),
             "unit": UNIT, "n_gpus": 1, "steps": K, "warmup": max(3, args.warmup),
             "ms_per_step": fwd_ms + bwd_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -468,7 +493,10 @@ def run_fm_mode(args):
             "config": {"workload": "FM mode (B,M,D,L)=(%d,%d,%d,%d) bf16 storage / fp32 accumulate" % (B, M, D, L)},
             "gpu_launches": K * 5, "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
             "layer_forward_ms": {"states_materialised_torch_epilogue": layer_states_ms,
+                                 "fused_with_normalised_states": layer_fused_states_ms,
                                  "read_out_without_states": layer_fused_ms},
+            "layer_train_step_ms": {"fused_op": train_fused_ms,
+                                    "fm_scan_plus_torch_norm_and_einsum": train_composed_ms},
             "roofline_forward": {"algorithmic_bytes_per_launch": 2 * n + 2 * (M + D) * B * L,
                                  "achieved": (2 * n + 2 * (M + D) * B * L) / (fwd_ms * 1e-3) / 1e9,
                                  "peak": peak, "peak_kind": kind, "unit": "GB/s"},

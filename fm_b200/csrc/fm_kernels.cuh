@@ -305,6 +305,8 @@ fm_forward_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ tok
 // M).  Two launches of this kernel recompute the scan instead of storing it:
 //   MODE 0: sumsq[b,m,t]  += sum over the CTA's token rows of h[b,m,d,t]^2
 //   MODE 1: out32[b,d,t]  += sum over the CTA's gate rows of scale[b,m,t] * h[b,m,d,t]
+//   MODE 2: MODE 1 and the normalised states h * rnorm are written (the training forward of the
+//           layer, which hands the normalised states back to the caller)
 // with scale = output_weight * rsqrt(sumsq / D + eps) formed in between (or just the output
 // weight when the norm is off).  Same blocking as fm_forward_blocked_kernel; HBM sees only the
 // gate, token, scale and output rows -- the (B,M,D,L) tensor never exists.
@@ -312,8 +314,11 @@ template <typename S, int MC, int DC, int MODE>
 __global__ void __launch_bounds__(MC * 32)
 fm_readout_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
                           const float *__restrict__ h0, const float *__restrict__ scale,
-                          float *__restrict__ sumsq, float *__restrict__ out32, int64_t M, int64_t D,
-                          int64_t L, int64_t m_blocks, int64_t d_blocks) {
+                          float *__restrict__ sumsq, float *__restrict__ out32,
+                          const float *__restrict__ rnorm, S *__restrict__ states_out, int64_t M,
+                          int64_t D, int64_t L, int64_t m_blocks, int64_t d_blocks) {
+    constexpr bool READOUT = MODE >= 1;
+    constexpr bool STORE = MODE == 2;
     constexpr int E = Store<S>::E;
     constexpr int W = 32 * E;
     extern __shared__ __align__(16) unsigned char fm_smem[];
@@ -368,7 +373,8 @@ fm_readout_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ tok
             sc[i] = 0.f;
             ss[i] = 0.f;
         }
-        if constexpr (MODE == 1) {
+        float rn[STORE ? E : 1];
+        if constexpr (READOUT) {
             if (in && have_m) {
 #pragma unroll
                 for (int k = 0; k < E / 4; ++k) {
@@ -377,6 +383,20 @@ fm_readout_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ tok
                     sc[4 * k + 1] = q4.y;
                     sc[4 * k + 2] = q4.z;
                     sc[4 * k + 3] = q4.w;
+                }
+            }
+        }
+        if constexpr (STORE) {
+#pragma unroll
+            for (int i = 0; i < E; ++i) rn[i] = 1.f;
+            if (rnorm && in && have_m) {
+#pragma unroll
+                for (int k = 0; k < E / 4; ++k) {
+                    const float4 q4 = *reinterpret_cast<const float4 *>(rnorm + grow_off + t + 4 * k);
+                    rn[4 * k] = q4.x;
+                    rn[4 * k + 1] = q4.y;
+                    rn[4 * k + 2] = q4.z;
+                    rn[4 * k + 3] = q4.w;
                 }
             }
         }
@@ -416,7 +436,7 @@ fm_readout_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ tok
             float s_ = fmaf(eA, carry[d], eH);
             carry[d] = fmaf(tA, carry[d], tH);
             const bool row_ok = have_m && d0 + d < D;
-            float contrib[E];
+            float contrib[E], hn[STORE ? E : 1];
 #pragma unroll
             for (int i = 0; i < E; ++i) {
                 s_ = fmaf(fa[i], s_, fx[i]);
@@ -425,8 +445,12 @@ fm_readout_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ tok
                 } else {
                     contrib[i] = sc[i] * s_;  // sc is zero for lanes and gate rows outside the problem
                 }
+                if constexpr (STORE) hn[i] = s_ * rn[i];
             }
-            if constexpr (MODE == 1) {
+            if constexpr (STORE) {
+                if (in && row_ok) stg_stream(states_out + (row0 + d) * L + t, Store<S>::pack(hn));
+            }
+            if constexpr (READOUT) {
 #pragma unroll
                 for (int k = 0; k < E / 4; ++k)
                     part[w][d][k][lane] =
@@ -439,7 +463,7 @@ fm_readout_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ tok
 #pragma unroll
         for (int k = 0; k < XPW; ++k)
             if (w + k * MC < DC) xs[buf ^ 1u][w + k * MC][lane] = xq[k];
-        if constexpr (MODE == 1) {
+        if constexpr (READOUT) {
             __syncthreads();  // every warp has published its tiles
 #pragma unroll
             for (int d = w; d < DC; d += MC) {
@@ -463,13 +487,17 @@ fm_readout_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ tok
 }
 
 // scale[b,m,t] = weight[b,m,t] * rsqrt(sumsq[b,m,t] / D + eps)   (in place over sumsq)
+// rnorm_out (nullable) receives the norm factor itself (kept for the layer's backward).
 template <typename S>
 __global__ void fm_readout_scale_kernel(float *__restrict__ sumsq_to_scale, const S *__restrict__ weight,
-                                        int64_t n, float inv_d, float eps, int use_norm) {
+                                        float *__restrict__ rnorm_out, int64_t n, float inv_d, float eps,
+                                        int use_norm) {
     const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i < n) {
         const float wgt = Store<S>::to_float(weight[i]);
-        sumsq_to_scale[i] = use_norm ? wgt * rsqrtf(sumsq_to_scale[i] * inv_d + eps) : wgt;
+        const float r = use_norm ? rsqrtf(sumsq_to_scale[i] * inv_d + eps) : 1.f;
+        sumsq_to_scale[i] = wgt * r;
+        if (rnorm_out) rnorm_out[i] = r;
     }
 }
 
@@ -477,6 +505,298 @@ __global__ void fm_readout_scale_kernel(float *__restrict__ sumsq_to_scale, cons
 template <typename S, int MC, int DC>
 constexpr size_t fm_backward_blocked_smem() {
     return sizeof(uint4) * 2 * DC * 32 + sizeof(float4) * MC * DC * (Store<S>::E / 4) * 32;
+}
+
+// ---------------------------------------------------------------- layer backward ------------
+// Training backward of the layer (scan -> RMS norm over D -> read-out over M), given
+//   hn   (B,M,D,L)  the normalised states the forward returned, hn = h * r,  r = rsqrt(mean_d h^2 + eps)
+//   dout (B,D,L)    gradient of the layer output,  ext (B,M,D,L) optional gradient of the returned states
+//   w    (B,M,L)    output weight
+// With Ghn = ext + w * dout the gradient that reaches the raw states is
+//   G = r * (Ghn - hn * c),   c[b,m,t] = (1/D) sum_d Ghn * hn          (c = 0 without the norm)
+// and the weight gradient is dw[b,m,t] = sum_d dout * hn.
+//
+// Pass 1 (this kernel): the two sums over d, accumulated in registers over the CTA's DC token
+// rows and reduced into fp32 (B,M,L) buffers.  No recurrence here: pure streaming of hn.
+template <typename S, int MC, int DC, bool EXT>
+__global__ void __launch_bounds__(MC * 32)
+fm_layer_dots_kernel(const S *__restrict__ hn, const S *__restrict__ dout, const S *__restrict__ ext,
+                     const S *__restrict__ weight, float *__restrict__ dotc, float *__restrict__ dw,
+                     int64_t M, int64_t D, int64_t L, int64_t m_blocks, int64_t d_blocks) {
+    constexpr int E = Store<S>::E;
+    constexpr int W = 32 * E;
+    __shared__ uint4 ds[DC][32];
+    const int lane = threadIdx.x & 31;
+    const int w = threadIdx.x >> 5;
+    const int64_t blk = blockIdx.x;
+    const int64_t db = blk % d_blocks, mb = (blk / d_blocks) % m_blocks, b = blk / (d_blocks * m_blocks);
+    const int64_t m = mb * MC + w, d0 = db * DC;
+    const bool have_m = m < M;
+    const int64_t ntiles = (L + W - 1) / W;
+    const int64_t grow_off = (b * M + (have_m ? m : 0)) * L;
+    const int64_t row0 = ((b * M + (have_m ? m : 0)) * D + d0);
+    for (int64_t tile = 0; tile < ntiles; ++tile) {
+        const int64_t t = tile * W + lane * E;
+        const bool in = t < L;
+        __syncthreads();
+        for (int d = w; d < DC; d += MC)
+            ds[d][lane] = (in && d0 + d < D) ? ldg_stream(dout + (b * D + d0 + d) * L + t) : make_uint4(0u, 0u, 0u, 0u);
+        float fw[E], a1[E], a2[E];
+        {
+            const uint4 q = (in && have_m) ? ldg_stream(weight + grow_off + t) : make_uint4(0u, 0u, 0u, 0u);
+            Store<S>::unpack(q, fw);
+        }
+#pragma unroll
+        for (int i = 0; i < E; ++i) a1[i] = a2[i] = 0.f;
+        __syncthreads();
+#pragma unroll
+        for (int d = 0; d < DC; ++d) {
+            const bool ok = in && have_m && d0 + d < D;
+            float fh[E], fd[E], fe[E];
+            Store<S>::unpack(ok ? ldg_stream(hn + (row0 + d) * L + t) : make_uint4(0u, 0u, 0u, 0u), fh);
+            Store<S>::unpack(ds[d][lane], fd);
+            if constexpr (EXT)
+                Store<S>::unpack(ok ? ldg_stream(ext + (row0 + d) * L + t) : make_uint4(0u, 0u, 0u, 0u), fe);
+#pragma unroll
+            for (int i = 0; i < E; ++i) {
+                float ghn = fw[i] * fd[i];
+                if constexpr (EXT) ghn += fe[i];
+                a1[i] = fmaf(ghn, fh[i], a1[i]);
+                a2[i] = fmaf(fd[i], fh[i], a2[i]);
+            }
+        }
+        if (in && have_m) {
+            red_vec<E, false>(dotc + grow_off, t, L, a1);
+            red_vec<E, false>(dw + grow_off, t, L, a2);
+        }
+    }
+}
+
+// Small per-(b,m,t) factors for pass 2, in place:  p1 = r*w,  p2 = r*c = r*dotc/D,  rinv = 1/r.
+// Without the norm r = 1 and c = 0.
+template <typename S>
+__global__ void fm_layer_factors_kernel(const float *__restrict__ rnorm, const S *__restrict__ weight,
+                                        float *__restrict__ dotc_to_p2, float *__restrict__ p1,
+                                        float *__restrict__ rinv, int64_t n, float inv_d) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n) {
+        const float r = rnorm ? rnorm[i] : 1.f;
+        p1[i] = r * Store<S>::to_float(weight[i]);
+        dotc_to_p2[i] = rnorm ? r * dotc_to_p2[i] * inv_d : 0.f;
+        rinv[i] = 1.f / r;
+    }
+}
+
+// Pass 2: fm_backward_blocked_kernel with the gradient of the raw states GENERATED per tile
+//   G = p1 * dout - hn * p2 (+ r * ext)     and the raw states recovered as h = hn * rinv,
+// so the only (B,M,D,L) stream read is hn (and ext when the caller used the returned states).
+template <typename S, int MC, int DC, int PD, bool EXT>
+__global__ void __launch_bounds__(MC * 32, 2)
+fm_layer_backward_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
+                                 const S *__restrict__ hn, const S *__restrict__ dout,
+                                 const S *__restrict__ ext, const float *__restrict__ p1,
+                                 const float *__restrict__ p2, const float *__restrict__ rinv,
+                                 const float *__restrict__ rnorm, const float *__restrict__ h0,
+                                 float *__restrict__ acc_gates, float *__restrict__ acc_tokens,
+                                 float *__restrict__ grad_h0, int64_t M, int64_t D, int64_t L,
+                                 int64_t m_blocks, int64_t d_blocks) {
+    static_assert(DC % PD == 0 && PD <= DC, "DC must be a multiple of the prefetch distance");
+    constexpr int E = Store<S>::E;
+    constexpr int W = 32 * E;
+    extern __shared__ __align__(16) unsigned char fm_smem[];
+    uint4(*xs)[DC][32] = reinterpret_cast<uint4(*)[DC][32]>(fm_smem);                        // [2] tokens
+    uint4(*ds)[DC][32] = reinterpret_cast<uint4(*)[DC][32]>(fm_smem + sizeof(uint4) * 2 * DC * 32);  // [2] dout
+    float4(*part)[DC][E / 4][32] =
+        reinterpret_cast<float4(*)[DC][E / 4][32]>(fm_smem + sizeof(uint4) * 4 * DC * 32);
+    const int lane = threadIdx.x & 31;
+    const int w = threadIdx.x >> 5;
+    const int64_t blk = blockIdx.x;
+    const int64_t db = blk % d_blocks, mb = (blk / d_blocks) % m_blocks, b = blk / (d_blocks * m_blocks);
+    const int64_t m = mb * MC + w, d0 = db * DC;
+    const bool have_m = m < M;
+    const int64_t ntiles = (L + W - 1) / W;
+    const int64_t grow_off = (b * M + (have_m ? m : 0)) * L;
+    const S *grow = gates + grow_off;
+    const int64_t row0 = ((b * M + (have_m ? m : 0)) * D + d0);
+    float carry[DC], dh_before[DC];
+#pragma unroll
+    for (int d = 0; d < DC; ++d) {
+        carry[d] = 0.f;
+        dh_before[d] = (h0 && have_m && d0 + d < D) ? h0[row0 + d] : 0.f;
+    }
+    uint4 rH[PD], rE[EXT ? PD : 1];
+    float rhalo[PD];
+    auto fetch = [&](int slot, int64_t tile, int d) {
+        const int64_t t = tile * W + lane * E;
+        const bool ok = have_m && tile >= 0 && d0 + d < D && t < L;
+        const int64_t base = (row0 + d) * L;
+        rH[slot] = ok ? ldg_stream(hn + base + t) : make_uint4(0u, 0u, 0u, 0u);
+        if constexpr (EXT) rE[slot] = ok ? ldg_stream(ext + base + t) : make_uint4(0u, 0u, 0u, 0u);
+        // raw state just before the tile: hn[t-1] * rinv[t-1]
+        rhalo[slot] = (ok && lane == 0 && t > 0) ? Store<S>::to_float(hn[base + t - 1]) * rinv[grow_off + t - 1] : 0.f;
+    };
+#pragma unroll
+    for (int p = 0; p < PD; ++p) fetch(p, ntiles - 1, p);
+
+    auto load_row = [&](const S *base_ptr, int64_t tile, int d) -> uint4 {
+        const int64_t tt = tile * W + lane * E;
+        return (tile >= 0 && tt < L && d < DC && d0 + d < D) ? ldg_stream(base_ptr + (b * D + d0 + d) * L + tt)
+                                                             : make_uint4(0u, 0u, 0u, 0u);
+    };
+    auto load_g = [&](int64_t tile) -> uint4 {
+        const int64_t tt = tile * W + lane * E;
+        return (tile >= 0 && tt < L && have_m)
+                   ? ldg_stream(grow + tt)
+                   : make_uint4(Store<S>::kOne, Store<S>::kOne, Store<S>::kOne, Store<S>::kOne);
+    };
+    constexpr int XPW = (DC + MC - 1) / MC;
+    uint4 gq = load_g(ntiles - 1), xq[XPW], dq[XPW];
+#pragma unroll
+    for (int k = 0; k < XPW; ++k)
+        if (w + k * MC < DC) {
+            xs[0][w + k * MC][lane] = load_row(tokens, ntiles - 1, w + k * MC);
+            ds[0][w + k * MC][lane] = load_row(dout, ntiles - 1, w + k * MC);
+        }
+
+    auto load_f32 = [&](const float *src, int64_t t, bool ok, float fill, float (&f)[E]) {
+#pragma unroll
+        for (int k = 0; k < E / 4; ++k) {
+            const float4 q4 = ok ? *reinterpret_cast<const float4 *>(src + grow_off + t + 4 * k)
+                                 : make_float4(fill, fill, fill, fill);
+            f[4 * k] = q4.x;
+            f[4 * k + 1] = q4.y;
+            f[4 * k + 2] = q4.z;
+            f[4 * k + 3] = q4.w;
+        }
+    };
+
+    unsigned step = 0;
+    for (int64_t tile = ntiles - 1; tile >= 0; --tile, ++step) {
+        const int64_t t = tile * W + lane * E;
+        const bool in = t < L;
+        const unsigned buf = step & 1u;
+        __syncthreads();  // previous flush complete; xs[buf], ds[buf] staged
+        float fa[E], om[E], f1[E], f2[E], fri[E];
+        Store<S>::unpack(gq, fa);
+        gq = load_g(tile - 1);
+#pragma unroll
+        for (int k = 0; k < XPW; ++k) {
+            xq[k] = load_row(tokens, tile - 1, w + k * MC);
+            dq[k] = load_row(dout, tile - 1, w + k * MC);
+        }
+        load_f32(p1, t, in && have_m, 0.f, f1);
+        load_f32(p2, t, in && have_m, 0.f, f2);
+        load_f32(rinv, t, in && have_m, 1.f, fri);
+        float frn[EXT ? E : 1];
+        if constexpr (EXT) {
+            if (rnorm) load_f32(rnorm, t, in && have_m, 1.f, frn);
+            else {
+#pragma unroll
+                for (int i = 0; i < E; ++i) frn[i] = 1.f;
+            }
+        }
+        float A = fa[E - 1];
+#pragma unroll
+        for (int i = E - 2; i >= 0; --i) A *= fa[i];
+#pragma unroll
+        for (int i = 0; i < E; ++i) om[i] = 1.f - fa[i];
+        float Alvl[5];
+#pragma unroll
+        for (int k = 0; k < 5; ++k) {
+            Alvl[k] = A;
+            const float pA = __shfl_down_sync(kFullMask, A, 1 << k);
+            if (lane + (1 << k) < 32) A *= pA;
+        }
+        float eA = __shfl_down_sync(kFullMask, A, 1);
+        if (lane == 31) eA = 1.f;
+        const float tA = __shfl_sync(kFullMask, A, 0);
+        float dg[E];
+#pragma unroll
+        for (int i = 0; i < E; ++i) dg[i] = 0.f;
+
+#pragma unroll
+        for (int d = 0; d < DC; ++d) {
+            const int slot = d % PD;
+            float fg[E], fh[E], fx[E], fd[E];
+            Store<S>::unpack(rH[slot], fh);  // normalised states
+            float fe[EXT ? E : 1];
+            if constexpr (EXT) Store<S>::unpack(rE[slot], fe);
+            const float halo = rhalo[slot];
+            if (d + PD < DC) fetch(slot, tile, d + PD);
+            else fetch(slot, tile - 1, d + PD - DC);
+            Store<S>::unpack(xs[buf][d][lane], fx);
+            Store<S>::unpack(ds[buf][d][lane], fd);
+#pragma unroll
+            for (int i = 0; i < E; ++i) {
+                float gi = fmaf(f1[i], fd[i], -fh[i] * f2[i]);  // r*w*dout - hn*r*c
+                if constexpr (EXT) gi = fmaf(frn[i], fe[i], gi);
+                fg[i] = gi;
+                fh[i] *= fri[i];  // raw state
+            }
+            float C = fa[E - 1] * fg[E - 1];
+#pragma unroll
+            for (int i = E - 2; i >= 0; --i) C = fa[i] * (fg[i] + C);
+#pragma unroll
+            for (int k = 0; k < 5; ++k) {
+                const float pC = __shfl_down_sync(kFullMask, C, 1 << k);
+                if (lane + (1 << k) < 32) C = fmaf(Alvl[k], pC, C);
+            }
+            float eC = __shfl_down_sync(kFullMask, C, 1);
+            if (lane == 31) eC = 0.f;
+            const float tC = __shfl_sync(kFullMask, C, 0);
+            float hprev0 = __shfl_up_sync(kFullMask, fh[E - 1], 1);
+            if (lane == 0) hprev0 = (t > 0) ? halo : dh_before[d];
+            float c = fmaf(eA, carry[d], eC);
+            carry[d] = fmaf(tA, carry[d], tC);
+            float dxv[E];
+#pragma unroll
+            for (int i = E - 1; i >= 0; --i) {
+                const float delta = fg[i] + c;
+                c = fa[i] * delta;
+                const float hp = (i > 0) ? fh[i > 0 ? i - 1 : 0] : hprev0;
+                dg[i] = fmaf(delta, hp - fx[i], dg[i]);
+                dxv[i] = om[i] * delta;
+            }
+#pragma unroll
+            for (int k = 0; k < E / 4; ++k)
+                part[w][d][k][lane] = make_float4(dxv[4 * k], dxv[4 * k + 1], dxv[4 * k + 2], dxv[4 * k + 3]);
+        }
+        if (in && have_m) red_vec<E, false>(acc_gates + grow_off, t, L, dg);
+#pragma unroll
+        for (int k = 0; k < XPW; ++k)
+            if (w + k * MC < DC) {
+                xs[buf ^ 1u][w + k * MC][lane] = xq[k];
+                ds[buf ^ 1u][w + k * MC][lane] = dq[k];
+            }
+        __syncthreads();
+#pragma unroll
+        for (int d = w; d < DC; d += MC) {
+            float v[E];
+#pragma unroll
+            for (int i = 0; i < E; ++i) v[i] = 0.f;
+#pragma unroll
+            for (int ww = 0; ww < MC; ++ww)
+#pragma unroll
+                for (int k = 0; k < E / 4; ++k) {
+                    const float4 p = part[ww][d][k][lane];
+                    v[4 * k] += p.x;
+                    v[4 * k + 1] += p.y;
+                    v[4 * k + 2] += p.z;
+                    v[4 * k + 3] += p.w;
+                }
+            if (in && d0 + d < D) red_vec<E, false>(acc_tokens + (b * D + d0 + d) * L, t, L, v);
+        }
+    }
+    if (grad_h0 && have_m && lane == 0) {
+#pragma unroll
+        for (int d = 0; d < DC; ++d)
+            if (d0 + d < D) grad_h0[row0 + d] = carry[d];
+    }
+}
+
+template <typename S, int MC, int DC>
+constexpr size_t fm_layer_backward_smem() {
+    return sizeof(uint4) * 4 * DC * 32 + sizeof(float4) * MC * DC * (Store<S>::E / 4) * 32;
 }
 
 }  // namespace fms

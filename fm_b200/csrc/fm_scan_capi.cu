@@ -576,10 +576,12 @@ FMS_EXPORT int fms_fm_backward(const void *gates, const void *tokens, const void
 // ------------------------------------------------------------------ FM layer read-out -------
 namespace {
 
+// states_out / rnorm_out non-null: the training forward (normalised states and the norm factor are
+// kept for the backward); null: inference read-out, nothing of size (B,M,D,L) is written.
 template <typename S>
 int launch_fm_readout(const FmShape &sh, const void *gates, const void *tokens, const void *weight,
                       const float *h0, float *scale, float *out32, void *out, int mem_norm, float eps,
-                      cudaStream_t st) {
+                      void *states_out, float *rnorm_out, cudaStream_t st) {
     constexpr int MC = 8, DC = 8;
     const int64_t m_blocks = (sh.M + MC - 1) / MC, d_blocks = (sh.D + DC - 1) / DC;
     if (sh.B > 0x7fffffffLL / m_blocks || sh.B * m_blocks > 0x7fffffffLL / d_blocks) return FMS_ERR_BAD_SHAPE;
@@ -588,6 +590,10 @@ int launch_fm_readout(const FmShape &sh, const void *gates, const void *tokens, 
     const int64_t n_g = sh.B * sh.M * sh.L, n_x = sh.B * sh.D * sh.L;
     auto k0 = fms::fm_readout_blocked_kernel<S, MC, DC, 0>;
     auto k1 = fms::fm_readout_blocked_kernel<S, MC, DC, 1>;
+    auto k2 = fms::fm_readout_blocked_kernel<S, MC, DC, 2>;
+    static const cudaError_t a2 =
+        cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (int rc = record(a2)) return rc;
     static const cudaError_t a0 =
         cudaFuncSetAttribute(k0, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     static const cudaError_t a1 =
@@ -597,16 +603,22 @@ int launch_fm_readout(const FmShape &sh, const void *gates, const void *tokens, 
     if (int rc = record(cudaMemsetAsync(scale, 0, static_cast<size_t>(n_g + n_x) * sizeof(float), st))) return rc;
     if (mem_norm) {
         k0<<<grid, MC * 32, smem, st>>>(static_cast<const S *>(gates), static_cast<const S *>(tokens), h0, nullptr,
-                                        scale, nullptr, sh.M, sh.D, sh.L, m_blocks, d_blocks);
+                                        scale, nullptr, nullptr, nullptr, sh.M, sh.D, sh.L, m_blocks, d_blocks);
         if (int rc = check_launch()) return rc;
     }
     const int64_t blocks = (n_g + 255) / 256;
     if (blocks > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;
     fms::fm_readout_scale_kernel<S><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
-        scale, static_cast<const S *>(weight), n_g, 1.f / static_cast<float>(sh.D), eps, mem_norm ? 1 : 0);
+        scale, static_cast<const S *>(weight), mem_norm ? rnorm_out : nullptr, n_g,
+        1.f / static_cast<float>(sh.D), eps, mem_norm ? 1 : 0);
     if (int rc = check_launch()) return rc;
-    k1<<<grid, MC * 32, smem, st>>>(static_cast<const S *>(gates), static_cast<const S *>(tokens), h0, scale, nullptr,
-                                    out32, sh.M, sh.D, sh.L, m_blocks, d_blocks);
+    if (states_out)
+        k2<<<grid, MC * 32, smem, st>>>(static_cast<const S *>(gates), static_cast<const S *>(tokens), h0, scale,
+                                        nullptr, out32, mem_norm ? rnorm_out : nullptr,
+                                        static_cast<S *>(states_out), sh.M, sh.D, sh.L, m_blocks, d_blocks);
+    else
+        k1<<<grid, MC * 32, smem, st>>>(static_cast<const S *>(gates), static_cast<const S *>(tokens), h0, scale,
+                                        nullptr, out32, nullptr, nullptr, sh.M, sh.D, sh.L, m_blocks, d_blocks);
     if (int rc = check_launch()) return rc;
     return launch_cast<S>(out32, out, n_x, st);
 }
@@ -640,7 +652,114 @@ FMS_EXPORT int fms_fm_readout(const void *gates, const void *tokens, const void 
     float *out32 = scale + static_cast<size_t>(B) * M * L;
     if (!aligned_to(out32, 16)) return FMS_ERR_WORKSPACE;
     FMS_DISPATCH_DTYPE(dtype, (launch_fm_readout<S>(sh, gates, tokens, out_weight, h0, scale, out32, out, mem_norm,
-                                                    eps, st)));
+                                                    eps, nullptr, nullptr, st)));
+}
+
+// ------------------------------------------------------------------ FM layer, training -----
+namespace {
+
+template <typename S>
+int launch_fm_layer_backward(const FmShape &sh, const void *gates, const void *tokens, const void *weight,
+                             const void *hn, const void *dout, const void *ext, const float *rnorm,
+                             const float *h0, float *ws, void *grad_gates, void *grad_tokens, void *grad_weight,
+                             float *grad_h0, cudaStream_t st) {
+    constexpr int MC = 8, DC = 8, PD = 4;
+    const int64_t m_blocks = (sh.M + MC - 1) / MC, d_blocks = (sh.D + DC - 1) / DC;
+    if (sh.B > 0x7fffffffLL / m_blocks || sh.B * m_blocks > 0x7fffffffLL / d_blocks) return FMS_ERR_BAD_SHAPE;
+    const unsigned grid = static_cast<unsigned>(sh.B * m_blocks * d_blocks);
+    const int64_t n_g = sh.B * sh.M * sh.L, n_x = sh.B * sh.D * sh.L;
+    float *dotc = ws, *dw = dotc + n_g, *p1 = dw + n_g, *rinv = p1 + n_g, *acc_g = rinv + n_g, *acc_x = acc_g + n_g;
+    if (int rc = record(cudaMemsetAsync(ws, 0, static_cast<size_t>(5 * n_g + n_x) * sizeof(float), st))) return rc;
+    const S *hn_ = static_cast<const S *>(hn), *dout_ = static_cast<const S *>(dout), *ext_ = static_cast<const S *>(ext);
+    const S *w_ = static_cast<const S *>(weight);
+    if (ext)
+        fms::fm_layer_dots_kernel<S, MC, DC, true><<<grid, MC * 32, 0, st>>>(hn_, dout_, ext_, w_, dotc, dw, sh.M, sh.D,
+                                                                              sh.L, m_blocks, d_blocks);
+    else
+        fms::fm_layer_dots_kernel<S, MC, DC, false><<<grid, MC * 32, 0, st>>>(hn_, dout_, nullptr, w_, dotc, dw, sh.M,
+                                                                               sh.D, sh.L, m_blocks, d_blocks);
+    if (int rc = check_launch()) return rc;
+    const int64_t blocks = (n_g + 255) / 256;
+    if (blocks > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;
+    fms::fm_layer_factors_kernel<S><<<static_cast<unsigned>(blocks), 256, 0, st>>>(rnorm, w_, dotc, p1, rinv, n_g,
+                                                                                   1.f / static_cast<float>(sh.D));
+    if (int rc = check_launch()) return rc;
+    constexpr size_t smem = fms::fm_layer_backward_smem<S, MC, DC>();
+#define FMS_LAUNCH_LAYER_BWD(EXTV)                                                                      \
+    do {                                                                                                \
+        auto kern = fms::fm_layer_backward_blocked_kernel<S, MC, DC, PD, EXTV>;                         \
+        static const cudaError_t attr = cudaFuncSetAttribute(                                           \
+            kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));                 \
+        if (int rc = record(attr)) return rc;                                                           \
+        kern<<<grid, MC * 32, smem, st>>>(static_cast<const S *>(gates), static_cast<const S *>(tokens), hn_, dout_, \
+                                          ext_, p1, dotc, rinv, rnorm, h0, acc_g, acc_x, grad_h0, sh.M, sh.D,    \
+                                          sh.L, m_blocks, d_blocks);                                    \
+    } while (0)
+    if (ext) FMS_LAUNCH_LAYER_BWD(true);
+    else FMS_LAUNCH_LAYER_BWD(false);
+#undef FMS_LAUNCH_LAYER_BWD
+    if (int rc = check_launch()) return rc;
+    if (int rc = launch_cast<S>(acc_g, grad_gates, n_g, st)) return rc;
+    if (int rc = launch_cast<S>(dw, grad_weight, n_g, st)) return rc;
+    return launch_cast<S>(acc_x, grad_tokens, n_x, st);
+}
+
+}  // namespace
+
+FMS_EXPORT int fms_fm_layer_forward(const void *gates, const void *tokens, const void *out_weight, const float *h0,
+                                    void *out, void *states_norm, float *rnorm, int64_t B, int64_t M, int64_t D,
+                                    int64_t L, int dtype, int mem_norm, float eps, void *workspace,
+                                    size_t workspace_bytes, fms_stream_t stream) {
+    FmShape sh;
+    if (int rc = make_fm_shape(sh, B, M, D, L, dtype)) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (sh.rows == 0 || L == 0) return FMS_OK;
+    bool aligned = false;
+    if (int rc = fm_alignment(aligned, L, dtype, gates, tokens, out_weight, static_cast<const void *>(out),
+                              static_cast<const void *>(states_norm)))
+        return rc;
+    if (mem_norm && !rnorm) return FMS_ERR_NULL_POINTER;
+    if (!aligned || (static_cast<uint64_t>(L) * sizeof(float)) % 16 != 0 || (rnorm && !aligned_to(rnorm, 16)))
+        return FMS_ERR_MISALIGNED;
+    const size_t need = fms_fm_readout_workspace_bytes(B, M, D, L, dtype);
+    if (!workspace || !aligned_to(workspace, 16) || workspace_bytes < need) return FMS_ERR_WORKSPACE;
+    float *scale = static_cast<float *>(workspace);
+    float *out32 = scale + static_cast<size_t>(B) * M * L;
+    FMS_DISPATCH_DTYPE(dtype, (launch_fm_readout<S>(sh, gates, tokens, out_weight, h0, scale, out32, out, mem_norm,
+                                                    eps, states_norm, rnorm, st)));
+}
+
+FMS_EXPORT size_t fms_fm_layer_backward_workspace_bytes(int64_t B, int64_t M, int64_t D, int64_t L, int dtype) {
+    FmShape sh;
+    if (make_fm_shape(sh, B, M, D, L, dtype) != FMS_OK || sh.rows == 0 || L == 0) return 0;
+    const size_t elems = static_cast<size_t>(B) * static_cast<size_t>(5 * M + D) * static_cast<size_t>(L);
+    return (elems * sizeof(float) + 255) / 256 * 256;
+}
+
+FMS_EXPORT int fms_fm_layer_backward(const void *gates, const void *tokens, const void *out_weight,
+                                     const void *states_norm, const float *rnorm, const void *grad_out,
+                                     const void *grad_states_norm, const float *h0, void *grad_gates,
+                                     void *grad_tokens, void *grad_out_weight, float *grad_h0, int64_t B, int64_t M,
+                                     int64_t D, int64_t L, int dtype, void *workspace, size_t workspace_bytes,
+                                     fms_stream_t stream) {
+    FmShape sh;
+    if (int rc = make_fm_shape(sh, B, M, D, L, dtype)) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (sh.rows == 0 || L == 0) return FMS_OK;
+    bool aligned = false;
+    if (int rc = fm_alignment(aligned, L, dtype, gates, tokens, out_weight, states_norm, grad_out,
+                              static_cast<const void *>(grad_gates), static_cast<const void *>(grad_tokens),
+                              static_cast<const void *>(grad_out_weight)))
+        return rc;
+    if (grad_states_norm && !aligned_to(grad_states_norm, 16)) aligned = false;
+    if (!aligned || (static_cast<uint64_t>(L) * sizeof(float)) % 16 != 0 || (rnorm && !aligned_to(rnorm, 16)))
+        return FMS_ERR_MISALIGNED;
+    const size_t need = fms_fm_layer_backward_workspace_bytes(B, M, D, L, dtype);
+    if (!workspace || !aligned_to(workspace, 16) || workspace_bytes < need) return FMS_ERR_WORKSPACE;
+    FMS_DISPATCH_DTYPE(dtype, (launch_fm_layer_backward<S>(sh, gates, tokens, out_weight, states_norm, grad_out,
+                                                           grad_states_norm, rnorm, h0,
+                                                           static_cast<float *>(workspace), grad_gates, grad_tokens,
+                                                           grad_out_weight, grad_h0, st)));
 }
 
 // ------------------------------------------------------------------ split inside one GPU ----

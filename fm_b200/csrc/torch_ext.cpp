@@ -234,6 +234,89 @@ void fm_memory_readout(const at::Tensor &gates, const at::Tensor &tokens, const 
                  "fm_memory_readout");
 }
 
+// Training forward of the layer: writes out (B,D,L), the normalised states (B,M,D,L) and the norm
+// factor rnorm (B,M,L) fp32 (ignored when mem_norm is false).
+void fm_memory_forward_train(const at::Tensor &gates, const at::Tensor &tokens, const at::Tensor &weight,
+                             const c10::optional<at::Tensor> &initial_state, const at::Tensor &out,
+                             const at::Tensor &states_norm, const at::Tensor &rnorm, bool mem_norm, double eps) {
+    TORCH_CHECK(gates.is_cuda() && gates.is_contiguous() && gates.dim() == 3 && tokens.dim() == 3,
+                "gates must be a contiguous CUDA (B,M,L) tensor and tokens (B,D,L)");
+    const int64_t B = gates.size(0), M = gates.size(1), L = gates.size(2), D = tokens.size(1);
+    auto same = [&](const at::Tensor &t, at::IntArrayRef shape, const char *name) {
+        TORCH_CHECK(t.is_cuda() && t.is_contiguous() && t.scalar_type() == gates.scalar_type() &&
+                        t.device() == gates.device() && t.sizes() == shape,
+                    name, " must be a contiguous CUDA tensor of shape ", shape, " with the dtype of gates");
+    };
+    same(tokens, {B, D, L}, "tokens");
+    same(weight, {B, M, L}, "weight");
+    same(out, {B, D, L}, "out");
+    same(states_norm, {B, M, D, L}, "states_norm");
+    TORCH_CHECK(rnorm.is_cuda() && rnorm.is_contiguous() && rnorm.scalar_type() == at::kFloat &&
+                    rnorm.numel() == B * M * L, "rnorm must be a contiguous fp32 CUDA tensor of B*M*L elements");
+    const int dtype = dtype_tag(gates);
+    const c10::cuda::CUDAGuard guard(gates.device());
+    at::Tensor h0 = carry_f32(initial_state, B * M * D, gates, "initial_state");
+    const size_t scratch = fms_fm_readout_workspace_bytes(B, M, D, L, dtype);
+    at::Tensor ws = at::empty({static_cast<int64_t>(std::max<size_t>(scratch, 16))}, gates.options().dtype(at::kByte));
+    check_status(fms_fm_layer_forward(gates.data_ptr(), tokens.data_ptr(), weight.data_ptr(), fptr(h0), out.data_ptr(),
+                                      states_norm.data_ptr(), rnorm.data_ptr<float>(), B, M, D, L, dtype,
+                                      mem_norm ? 1 : 0, static_cast<float>(eps), ws.data_ptr(), scratch,
+                                      at::cuda::getCurrentCUDAStream().stream()),
+                 "fm_memory_forward");
+}
+
+// Training backward of the layer.  grad_states_norm: None when the returned states were not used.
+void fm_memory_backward(const at::Tensor &gates, const at::Tensor &tokens, const at::Tensor &weight,
+                        const at::Tensor &states_norm, const at::Tensor &rnorm, bool mem_norm,
+                        const at::Tensor &grad_out, const c10::optional<at::Tensor> &grad_states_norm,
+                        const c10::optional<at::Tensor> &initial_state, const at::Tensor &d_gates,
+                        const at::Tensor &d_tokens, const at::Tensor &d_weight,
+                        const c10::optional<at::Tensor> &d_initial_state) {
+    TORCH_CHECK(gates.is_cuda() && gates.is_contiguous() && gates.dim() == 3 && tokens.dim() == 3,
+                "gates must be a contiguous CUDA (B,M,L) tensor and tokens (B,D,L)");
+    const int64_t B = gates.size(0), M = gates.size(1), L = gates.size(2), D = tokens.size(1);
+    auto same = [&](const at::Tensor &t, at::IntArrayRef shape, const char *name) {
+        TORCH_CHECK(t.is_cuda() && t.is_contiguous() && t.scalar_type() == gates.scalar_type() &&
+                        t.device() == gates.device() && t.sizes() == shape,
+                    name, " must be a contiguous CUDA tensor of shape ", shape, " with the dtype of gates");
+    };
+    same(tokens, {B, D, L}, "tokens");
+    same(weight, {B, M, L}, "weight");
+    same(states_norm, {B, M, D, L}, "states_norm");
+    same(grad_out, {B, D, L}, "grad_out");
+    same(d_gates, {B, M, L}, "d_gates");
+    same(d_tokens, {B, D, L}, "d_tokens");
+    same(d_weight, {B, M, L}, "d_weight");
+    const void *ext = nullptr;
+    if (grad_states_norm.has_value() && grad_states_norm->defined()) {
+        same(*grad_states_norm, {B, M, D, L}, "grad_states_norm");
+        ext = grad_states_norm->data_ptr();
+    }
+    const float *rn = nullptr;
+    if (mem_norm) {
+        TORCH_CHECK(rnorm.is_cuda() && rnorm.is_contiguous() && rnorm.scalar_type() == at::kFloat &&
+                        rnorm.numel() == B * M * L, "rnorm must be a contiguous fp32 CUDA tensor of B*M*L elements");
+        rn = rnorm.data_ptr<float>();
+    }
+    float *gh0 = nullptr;
+    if (d_initial_state.has_value() && d_initial_state->defined() && d_initial_state->numel() > 0) {
+        TORCH_CHECK(d_initial_state->is_cuda() && d_initial_state->is_contiguous() &&
+                        d_initial_state->scalar_type() == at::kFloat && d_initial_state->numel() == B * M * D,
+                    "d_initial_state must be a contiguous fp32 CUDA tensor of B*M*D elements");
+        gh0 = d_initial_state->data_ptr<float>();
+    }
+    const int dtype = dtype_tag(gates);
+    const c10::cuda::CUDAGuard guard(gates.device());
+    at::Tensor h0 = carry_f32(initial_state, B * M * D, gates, "initial_state");
+    const size_t scratch = fms_fm_layer_backward_workspace_bytes(B, M, D, L, dtype);
+    at::Tensor ws = at::empty({static_cast<int64_t>(std::max<size_t>(scratch, 16))}, gates.options().dtype(at::kByte));
+    check_status(fms_fm_layer_backward(gates.data_ptr(), tokens.data_ptr(), weight.data_ptr(), states_norm.data_ptr(),
+                                       rn, grad_out.data_ptr(), ext, fptr(h0), d_gates.data_ptr(), d_tokens.data_ptr(),
+                                       d_weight.data_ptr(), gh0, B, M, D, L, dtype, ws.data_ptr(), scratch,
+                                       at::cuda::getCurrentCUDAStream().stream()),
+                 "fm_memory_backward");
+}
+
 // Backward with the reference's seven arguments.  firstPropGrad seeds the reverse scan
 // (fm/scan/fm_scan.cuh:120-122); the reference passes zeros (fm/scan/fm_scan.py:65).
 // input_tokens is accepted for signature compatibility and not read: with the token weight
@@ -260,6 +343,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("fm_scan_backward", &fm_scan_backward, "scan backward, reference signature");
     m.def("fm_scan_backward_ex", &fm_scan_backward_ex, "scan backward with h0 / carry_in / grad_h0");
     m.def("fm_scan_backward_fm", &fm_scan_backward_fm, "FM-mode backward with fused reductions");
+    m.def("fm_memory_forward_train", &fm_memory_forward_train, "layer forward: output + normalised states");
+    m.def("fm_memory_backward", &fm_memory_backward, "layer backward with the state gradient generated in-kernel");
     m.def("fm_memory_readout", &fm_memory_readout, "layer read-out without materialising the states");
     m.def("abi_version", []() { return fms_version(); });
 }

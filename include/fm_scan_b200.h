@@ -175,6 +175,30 @@ int fms_fm_readout(const void *gates, const void *tokens, const void *out_weight
                    int64_t B, int64_t M, int64_t D, int64_t L, int dtype, int mem_norm, float eps,
                    void *workspace, size_t workspace_bytes, fms_stream_t stream);
 
+/*
+ * The same layer for training (fm/scan/fm_scan.py:122-131 followed by autograd).
+ * fms_fm_layer_forward: one recomputing pass for the norm, then one pass that writes the
+ * NORMALISED states (the tensor the reference's layer returns) and the output together.
+ *   states_norm (B,M,D,L) out;  rnorm (B,M,L) fp32 out, the norm factor (NULL allowed iff
+ *   mem_norm == 0);  workspace: fms_fm_readout_workspace_bytes().
+ * fms_fm_layer_backward: gradients of gates (B,M,L), tokens (B,D,L), out_weight (B,M,L) and h0
+ * from grad_out (B,D,L) and, optionally, grad_states_norm (B,M,D,L; NULL when the caller did not
+ * use the returned states).  The gradient of the raw states is generated inside the reverse scan,
+ *   G = r*(Ghn - hn*c),  Ghn = grad_states_norm + w*grad_out,  c = mean_d(Ghn*hn),
+ * so the only (B,M,D,L) tensors read are states_norm (twice) and grad_states_norm if given;
+ * the reference's autograd reads and writes ~10 such tensors.  Pass rnorm == NULL iff the forward
+ * ran with mem_norm == 0.  Same alignment rule as fms_fm_readout.
+ */
+int fms_fm_layer_forward(const void *gates, const void *tokens, const void *out_weight, const float *h0, void *out,
+                         void *states_norm, float *rnorm, int64_t B, int64_t M, int64_t D, int64_t L, int dtype,
+                         int mem_norm, float eps, void *workspace, size_t workspace_bytes, fms_stream_t stream);
+size_t fms_fm_layer_backward_workspace_bytes(int64_t B, int64_t M, int64_t D, int64_t L, int dtype);
+int fms_fm_layer_backward(const void *gates, const void *tokens, const void *out_weight, const void *states_norm,
+                          const float *rnorm, const void *grad_out, const void *grad_states_norm, const float *h0,
+                          void *grad_gates, void *grad_tokens, void *grad_out_weight, float *grad_h0, int64_t B,
+                          int64_t M, int64_t D, int64_t L, int dtype, void *workspace, size_t workspace_bytes,
+                          fms_stream_t stream);
+
 /* ------------------------------------------------- few, long rows: split inside one GPU ---- */
 
 /*

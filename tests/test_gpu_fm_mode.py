@@ -98,9 +98,13 @@ def test_fm_equals_plain_on_broadcast_rows(monkeypatch):
     assert torch.equal(h_fm, h_plain)
 
 
+@pytest.mark.parametrize("fused", [True, False])
+@pytest.mark.parametrize("use_states", [False, True])
 @pytest.mark.parametrize("mem_norm", [True, False])
-def test_fm_memory_layer_matches_loop_restatement(mem_norm):
-    """The layer around the scan, forward and gradients, against the torch-loop restatement."""
+def test_fm_memory_layer_matches_loop_restatement(mem_norm, use_states, fused):
+    """The layer around the scan, forward and gradients, against the torch-loop restatement:
+    the fused op (state gradient generated in-kernel) and the reference's composition; with and
+    without a loss term on the returned states."""
     from fm_b200 import fm_memory
     from oracle.torch_loop import fm_memory_loop
     gen = torch.Generator().manual_seed(11)
@@ -112,10 +116,16 @@ def test_fm_memory_layer_matches_loop_restatement(mem_norm):
     h0 = torch.randn(B, M, D, generator=gen)
     W = torch.randn(B, L, D, generator=gen)
 
+    Wm = torch.randn(B, M, D, L, generator=gen)
+
     def run(fn, dev, dtype):
         args = [t.to(dev, dtype).requires_grad_(True) for t in (alpha, upd, outs, inp, h0)]
-        out, mem = fn(args[0], args[1], args[2], args[3], args[4], mem_norm=mem_norm)
-        (out * W.to(dev, dtype)).sum().backward()
+        kw = {"fused": fused} if fn is fm_memory else {}
+        out, mem = fn(args[0], args[1], args[2], args[3], args[4], mem_norm=mem_norm, **kw)
+        loss = (out * W.to(dev, dtype)).sum()
+        if use_states:
+            loss = loss + (mem * Wm.to(dev, dtype)).sum()
+        loss.backward()
         return [out.detach().cpu().double(), mem.detach().cpu().double()] + [a.grad.cpu().double() for a in args]
 
     got = run(fm_memory, "cuda", torch.float32)
@@ -156,3 +166,32 @@ def test_fm_memory_readout_without_states(mem_norm, dtype, B, L, M, D):
     a0 = args[0].cuda().requires_grad_(True)
     out2, mem2 = fm_memory(a0, *(a.cuda() for a in args[1:]), mem_norm=mem_norm, need_states=False)
     assert mem2 is not None and out2.requires_grad
+
+
+@pytest.mark.parametrize("mem_norm", [True, False])
+def test_fused_layer_bf16_against_double(mem_norm):
+    """The fused op itself on bf16 tensors at a ragged shape (M, D not multiples of the CTA block,
+    several tiles), against a double-precision evaluation of the same rounded inputs."""
+    from fm_b200.fm_memory import _FusedLayer
+    from oracle.torch_loop import fm_scan_loop
+    gen = torch.Generator().manual_seed(31)
+    B, L, M, D = 1, 776, 11, 19
+    decay = (0.7 + 0.3 * torch.rand(B, M, L, generator=gen)).to(torch.bfloat16)
+    tokens = torch.randn(B, D, L, generator=gen).to(torch.bfloat16)
+    weight = torch.rand(B, M, L, generator=gen).to(torch.bfloat16)
+    Wt = torch.randn(B, D, L, generator=gen)
+
+    args = [t.cuda().requires_grad_(True) for t in (decay, tokens, weight)]
+    out, states = _FusedLayer.apply(args[0], args[1], args[2], None, mem_norm, 1e-6)
+    (out.double() * Wt.cuda().double()).sum().backward()
+    got = [out.detach().double().cpu(), states.detach().double().cpu()] + [a.grad.double().cpu() for a in args]
+
+    ref_args = [t.double().requires_grad_(True) for t in (decay, tokens, weight)]
+    h = fm_scan_loop(ref_args[0], ref_args[1])
+    if mem_norm:
+        h = h * torch.rsqrt(torch.mean(h ** 2, dim=2, keepdim=True) + 1e-6)
+    ref_out = torch.einsum('bml,bmdl->bdl', ref_args[2], h)
+    (ref_out * Wt.double()).sum().backward()
+    ref = [ref_out.detach(), h.detach()] + [a.grad for a in ref_args]
+    for n, a, b in zip(["output", "states", "d_decay", "d_tokens", "d_weight"], got, ref):
+        H.assert_close(a.numpy(), b.numpy(), 2e-2, 2e-2 * float(b.abs().pow(2).mean().sqrt()), n)

@@ -125,7 +125,6 @@ def physical_gpu_index(local_index: int) -> int:
 # ------------------------------------------------------------------------- CPU baseline -----
 def cpu_port_throughput(rows: int, T: int, repeats: int, warmup: int = 1):
     """fwd+bwd elements/s of the C port (OpenMP over rows) on `rows` x T of the workload."""
-    import numpy as np
     from oracle import c_oracle as oc
     from tests.helpers import make_inputs
 

@@ -10,7 +10,6 @@ which hold outputs of the unmodified reference function.
 from __future__ import annotations
 
 import ctypes
-import os
 import subprocess
 from pathlib import Path
 

@@ -10,7 +10,6 @@ Collected last (file name) so that a run stopping at the first failure has alrea
 everything else.  It must pass alone in a fresh process and after the other tests: it relies on
 nothing but the library, and the shared array needs no clearing between calls.
 """
-import numpy as np
 import pytest
 import torch
 

@@ -343,8 +343,13 @@ def run_time_split(args):
     x = torch.randn(B, D, Tk, device=device, generator=gen).requires_grad_(True)
     G = torch.randn(B, D, Tk, device=device, generator=gen)
 
+    exchange = None
+    if world > 1 and args.exchange == "peer":
+        from fm_b200.peer_exchange import PeerCarryExchange
+        exchange = PeerCarryExchange(B * D)
+
     def step():
-        h = fm_scan_time_split(a, x) if world > 1 else fm_scan(a, x)
+        h = fm_scan_time_split(a, x, exchange=exchange) if world > 1 else fm_scan(a, x)
         return torch.autograd.grad(h, (a, x), G)
 
     def barrier():
@@ -369,6 +374,8 @@ def run_time_split(args):
         t = torch.tensor([ms], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
+    if exchange is not None:
+        exchange.check()
     if rank == 0:
         n = B * D * T
         peak, kind = measured_peak()
@@ -379,7 +386,9 @@ def run_time_split(args):
                 "data": "synthetic",
                 "config": {"workload": "scan fwd+bwd (B,D,T)=(1,%d,262144) fp32, T split in %d blocks" % (D, world),
                            "gates": "a = sigmoid(N(0,1)+3); x, G ~ N(0,1)",
-                           "exchange": "all-gather of (P,S) fp32 carries, once per direction"},
+                           "exchange": ("peer stores + flags in symmetric memory, fold on arrival"
+                                        if exchange is not None else
+                                        "NCCL all-gather of (P,S) fp32 carries, once per direction")},
                 "gpu_launches": K * (2 if world == 1 else 6),
                 "roofline_fwd_bwd": {"algorithmic_GBs_per_gpu": 8 * 4 * n / world / (ms * 1e-3) / 1e9,
                                      "moved_GBs_per_gpu": passes * 4 * n / world / (ms * 1e-3) / 1e9,
@@ -559,6 +568,8 @@ def main():
     ap.add_argument("--workload", choices=["c3", "c4", "fm"], default="c3",
                     help="c3: the headline row-sharded workload; c4: the long sequence split along T; "
                          "fm: the reference's (B,M,L)x(B,D,L)->(B,M,D,L) operator at its demo shape")
+    ap.add_argument("--exchange", choices=["nccl", "peer"], default="nccl",
+                    help="carry transport of --workload c4")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling aid)")

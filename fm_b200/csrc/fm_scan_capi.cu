@@ -663,7 +663,8 @@ int launch_fm_layer_backward(const FmShape &sh, const void *gates, const void *t
                              const void *hn, const void *dout, const void *ext, const float *rnorm,
                              const float *h0, float *ws, void *grad_gates, void *grad_tokens, void *grad_weight,
                              float *grad_h0, cudaStream_t st) {
-    constexpr int MC = 8, DC = 8, PD = 4;
+    constexpr int MC = 8, DC = 8;
+    const int pd = tune_value("FMS_TUNE_FM_PD", 4);
     const int64_t m_blocks = (sh.M + MC - 1) / MC, d_blocks = (sh.D + DC - 1) / DC;
     if (sh.B > 0x7fffffffLL / m_blocks || sh.B * m_blocks > 0x7fffffffLL / d_blocks) return FMS_ERR_BAD_SHAPE;
     const unsigned grid = static_cast<unsigned>(sh.B * m_blocks * d_blocks);
@@ -685,9 +686,9 @@ int launch_fm_layer_backward(const FmShape &sh, const void *gates, const void *t
                                                                                    1.f / static_cast<float>(sh.D));
     if (int rc = check_launch()) return rc;
     constexpr size_t smem = fms::fm_layer_backward_smem<S, MC, DC>();
-#define FMS_LAUNCH_LAYER_BWD(EXTV)                                                                      \
+#define FMS_LAUNCH_LAYER_BWD(EXTV, PDV)                                                                 \
     do {                                                                                                \
-        auto kern = fms::fm_layer_backward_blocked_kernel<S, MC, DC, PD, EXTV>;                         \
+        auto kern = fms::fm_layer_backward_blocked_kernel<S, MC, DC, PDV, EXTV>;                        \
         static const cudaError_t attr = cudaFuncSetAttribute(                                           \
             kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));                 \
         if (int rc = record(attr)) return rc;                                                           \
@@ -695,8 +696,14 @@ int launch_fm_layer_backward(const FmShape &sh, const void *gates, const void *t
                                           ext_, p1, dotc, rinv, rnorm, h0, acc_g, acc_x, grad_h0, sh.M, sh.D,    \
                                           sh.L, m_blocks, d_blocks);                                    \
     } while (0)
-    if (ext) FMS_LAUNCH_LAYER_BWD(true);
-    else FMS_LAUNCH_LAYER_BWD(false);
+    if (ext) {
+        if (pd == 2) FMS_LAUNCH_LAYER_BWD(true, 2);
+        else FMS_LAUNCH_LAYER_BWD(true, 4);
+    } else {
+        if (pd == 2) FMS_LAUNCH_LAYER_BWD(false, 2);
+        else if (pd == 8) FMS_LAUNCH_LAYER_BWD(false, 8);
+        else FMS_LAUNCH_LAYER_BWD(false, 4);
+    }
 #undef FMS_LAUNCH_LAYER_BWD
     if (int rc = check_launch()) return rc;
     if (int rc = launch_cast<S>(acc_g, grad_gates, n_g, st)) return rc;

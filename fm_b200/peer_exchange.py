@@ -1,0 +1,101 @@
+"""Carry exchange of the split-along-T scan over peer-mapped memory (one box, NVLink/NVSwitch).
+
+``PeerCarryExchange`` owns this rank's exchange buffer, allocated as torch symmetric memory so
+that every rank of the group has it mapped, and drives the two C-ABI calls
+``fms_peer_publish`` (peer stores + flag) and ``fms_peer_wait_fold`` (bounded wait on local flags
++ carry fold).  It replaces the NCCL all-gather, the carry fold kernel and the tensor slicing of
+the default path of ``fm_b200.time_split`` by two small kernels per direction.
+
+All ranks must create the object together and then perform the same sequence of forward and
+backward exchanges (the usual SPMD discipline): exchange numbers are counted per direction.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from . import capi
+
+_P, _I64, _I, _U32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_uint32
+
+
+def _bind():
+    L = capi.lib()
+    if not getattr(L, "_fms_peer_bound", False):
+        L.fms_peer_exchange_bytes.restype = ctypes.c_size_t
+        L.fms_peer_exchange_bytes.argtypes = [_I64, _I]
+        L.fms_peer_exchange_status_offset.restype = ctypes.c_size_t
+        L.fms_peer_exchange_status_offset.argtypes = [_I64, _I]
+        L.fms_peer_publish.restype = _I
+        L.fms_peer_publish.argtypes = [_P, _P, _I64, ctypes.POINTER(_P), _I, _I, _I, _U32, _P]
+        L.fms_peer_wait_fold.restype = _I
+        L.fms_peer_wait_fold.argtypes = [_P, _P, _P, _I64, _I, _I, _I, _U32, ctypes.c_double, _P]
+        L._fms_peer_bound = True
+    return L
+
+
+class PeerExchangeTimeout(RuntimeError):
+    pass
+
+
+class PeerCarryExchange:
+    def __init__(self, rows: int, group=None, device=None, max_wait_seconds: float = 2.0):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self._L = _bind()
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank = dist.get_rank(self.group)
+        self.world = dist.get_world_size(self.group)
+        if self.world > 8:
+            raise ValueError("the peer exchange covers one box: at most 8 ranks")
+        self.rows = int(rows)
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.max_wait_seconds = float(max_wait_seconds)
+        nbytes = int(self._L.fms_peer_exchange_bytes(self.rows, self.world))
+        self.buffer = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+        self.buffer.zero_()
+        self.handle = symm_mem.rendezvous(self.buffer, self.group)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)  # every buffer is zeroed before anyone publishes
+        self._peers = (_P * self.world)(*[int(p) for p in self.handle.buffer_ptrs])
+        off = int(self._L.fms_peer_exchange_status_offset(self.rows, self.world))
+        self.status = self.buffer[off:off + 4].view(torch.int32)
+        self._count = [0, 0]  # exchanges done so far: forward, reverse
+
+    def _stream(self):
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def exchange(self, P: torch.Tensor, S: torch.Tensor, carry0=None, reverse: bool = False) -> torch.Tensor:
+        """Publish this block's (P, S) and return the carry entering this block (fp32, rows)."""
+        for t in (P, S):
+            if not (t.is_cuda and t.dtype == torch.float32 and t.is_contiguous() and t.numel() == self.rows):
+                raise RuntimeError("P and S must be contiguous fp32 CUDA tensors with one element per row")
+        if carry0 is not None and not (carry0.is_cuda and carry0.dtype == torch.float32
+                                       and carry0.is_contiguous() and carry0.numel() == self.rows):
+            raise RuntimeError("carry0 must be a contiguous fp32 CUDA tensor with one element per row")
+        d = 1 if reverse else 0
+        self._count[d] += 1
+        number = self._count[d]
+        out = torch.empty(self.rows, device=self.device, dtype=torch.float32)
+        with torch.cuda.device(self.device):
+            rc = self._L.fms_peer_publish(P.data_ptr(), S.data_ptr(), self.rows, self._peers, self.world, self.rank,
+                                          d, number, self._stream())
+            if rc == capi.FMS_OK:
+                rc = self._L.fms_peer_wait_fold(self.buffer.data_ptr(), capi.ptr(carry0), out.data_ptr(), self.rows,
+                                                self.world, self.rank, d, number, self.max_wait_seconds,
+                                                self._stream())
+        if rc != capi.FMS_OK:
+            raise capi.FmsError("fms_peer_publish/wait_fold", rc, capi.status_string(rc),
+                                int(self._L.fms_last_cuda_error()))
+        return out
+
+    def check(self) -> None:
+        """Synchronise and raise if any wait ran into its bound since the last check."""
+        code = int(self.status.item())
+        if code != 0:
+            self.status.zero_()
+            raise PeerExchangeTimeout(
+                f"rank {self.rank}: a peer did not publish its carries within {self.max_wait_seconds} s "
+                f"({'reverse' if code == 2 else 'forward'} exchange)")

@@ -17,7 +17,9 @@ Backward mirrors it in reverse time order with c_t = a_t * delta_t as the carrie
     4. the ordinary backward of the block with carry_in = c_in,k and h0 = h_in,k      reads a, h, G; writes 2
 Rank 0's dL/dh0 output is the gradient of ``initial_state``.
 
-The collective is whatever the group's backend provides (NCCL over NVLink on GPUs).  The local
+The collective is whatever the group's backend provides (NCCL over NVLink on GPUs); with a
+``PeerCarryExchange`` the all-gather and the fold are replaced by peer stores + flags in
+symmetric memory and a fold-on-arrival kernel.  The local
 passes come from an ops object: ``CudaScanOps`` (the CUDA kernels) by default.  Tests on CPU
 ranks inject another ops object to exercise the exchange logic over gloo; the package itself
 ships no CPU scan.
@@ -41,38 +43,47 @@ def _gather(t: torch.Tensor, group) -> torch.Tensor:
 
 class _TimeSplitScan(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, gates, tokens, initial_state, group, ops):
+    def forward(ctx, gates, tokens, initial_state, group, ops, exchange):
         rank = dist.get_rank(group)
         world = dist.get_world_size(group)
         rows_shape = gates.shape[:-1]
         P, S = ops.reduce(gates, tokens)
-        PS = _gather(torch.stack([P.reshape(-1), S.reshape(-1)]), group)  # (world, 2, rows)
-        P_all = PS[:, 0].contiguous()
-        S_all = PS[:, 1].contiguous()
         carry0 = None
         if initial_state is not None:
             # every rank must fold the same h0: take rank 0's
             carry0 = initial_state.to(torch.float32).reshape(-1).contiguous().clone()
             dist.broadcast(carry0, src=dist.get_global_rank(group, 0) if group is not None else 0,
                            group=group)
-        h_in_all, _ = ops.combine(P_all, S_all, carry0, reverse=False)
-        h_in = h_in_all[rank].reshape(rows_shape).contiguous()
+        if exchange is not None:
+            # peer stores + flags over NVLink, fold on arrival (fm_b200.peer_exchange)
+            P_keep = P.reshape(-1).contiguous()
+            h_in = exchange.exchange(P_keep, S.reshape(-1).contiguous(), carry0, reverse=False)
+            h_in = h_in.reshape(rows_shape)
+        else:
+            PS = _gather(torch.stack([P.reshape(-1), S.reshape(-1)]), group)  # (world, 2, rows)
+            P_keep = PS[:, 0].contiguous()
+            h_in_all, _ = ops.combine(P_keep, PS[:, 1].contiguous(), carry0, reverse=False)
+            h_in = h_in_all[rank].reshape(rows_shape).contiguous()
         states = ops.forward(gates, tokens, h_in)
-        ctx.save_for_backward(gates, states, h_in, P_all)
-        ctx.group, ctx.ops, ctx.rank, ctx.world = group, ops, rank, world
+        ctx.save_for_backward(gates, states, h_in, P_keep)
+        ctx.group, ctx.ops, ctx.rank, ctx.world, ctx.exchange = group, ops, rank, world, exchange
         ctx.h0_dtype = None if initial_state is None else initial_state.dtype
         ctx.h0_needs_grad = initial_state is not None and ctx.needs_input_grad[2]
         return states
 
     @staticmethod
     def backward(ctx, grad_states):
-        gates, states, h_in, P_all = ctx.saved_tensors
+        gates, states, h_in, P_keep = ctx.saved_tensors
         group, ops, rank = ctx.group, ctx.ops, ctx.rank
         grad_states = grad_states.contiguous()
         S_rev = ops.reduce_reverse(gates, grad_states)
-        S_all = _gather(S_rev.reshape(-1), group)  # (world, rows)
-        c_in_all, _ = ops.combine(P_all, S_all, None, reverse=True)
-        c_in = c_in_all[rank].reshape(h_in.shape).contiguous()
+        if ctx.exchange is not None:
+            c_in = ctx.exchange.exchange(P_keep, S_rev.reshape(-1).contiguous(), None, reverse=True)
+            c_in = c_in.reshape(h_in.shape)
+        else:
+            S_all = _gather(S_rev.reshape(-1), group)  # (world, rows)
+            c_in_all, _ = ops.combine(P_keep, S_all, None, reverse=True)
+            c_in = c_in_all[rank].reshape(h_in.shape).contiguous()
         grad_gates, grad_tokens, grad_h0 = ops.backward(gates, states, grad_states, h_in, c_in,
                                                         want_grad_h0=ctx.h0_needs_grad)
         d_h0 = None
@@ -80,7 +91,7 @@ class _TimeSplitScan(torch.autograd.Function):
             # dL/d(initial_state) is rank 0's carry-out; other ranks contribute nothing
             d_h0 = grad_h0 if rank == 0 else torch.zeros_like(grad_h0)
             d_h0 = d_h0.to(ctx.h0_dtype)
-        return grad_gates, grad_tokens, d_h0, None, None
+        return grad_gates, grad_tokens, d_h0, None, None, None
 
 
 def _validate_layout(gates, group):
@@ -98,7 +109,8 @@ def _validate_layout(gates, group):
             f"{everyone.tolist()} -- every rank must hold the same (B, D) rows of one dtype")
 
 
-def fm_scan_time_split(gates, tokens, initial_state=None, group=None, ops=None, validate=False):
+def fm_scan_time_split(gates, tokens, initial_state=None, group=None, ops=None, validate=False,
+                       exchange=None):
     """Differentiable scan of this rank's time block; ranks are ordered along T by group rank.
 
     Arguments:
@@ -106,6 +118,8 @@ def fm_scan_time_split(gates, tokens, initial_state=None, group=None, ops=None, 
         initial_state: (B, D) state before the first block; only rank 0's values are used.
         group: process group spanning the time blocks (default: the world group).
         ops: local scan passes (default ``CudaScanOps``).
+        exchange: a ``fm_b200.peer_exchange.PeerCarryExchange`` built for these rows: the carries
+            then travel as peer stores over NVLink with flags instead of an all-gather.
         validate: exchange a shape/dtype descriptor first and raise on every rank if the ranks
             disagree (one extra small all-gather; off by default).
     Returns:
@@ -117,4 +131,4 @@ def fm_scan_time_split(gates, tokens, initial_state=None, group=None, ops=None, 
         raise RuntimeError("gates and tokens must have the same shape")
     if validate:
         _validate_layout(gates, group)
-    return _TimeSplitScan.apply(gates, tokens, initial_state, group, ops or CudaScanOps)
+    return _TimeSplitScan.apply(gates, tokens, initial_state, group, ops or CudaScanOps, exchange)

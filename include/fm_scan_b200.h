@@ -260,6 +260,37 @@ int fms_plain_forward_split_static(const void *gates, const void *tokens, const 
                                    void *states, float *h_last, int64_t rows, int64_t T, int dtype,
                                    fms_stream_t stream);
 
+/* --------------------------------------- carry exchange over peer-mapped memory (one box) ---- */
+
+/*
+ * The exchange step of the split-along-T scan without a collective library: every rank owns a
+ * buffer of fms_peer_exchange_bytes() that all ranks have mapped (CUDA IPC / symmetric memory,
+ * zero-initialised once).  No reference counterpart (the reference is single-GPU).
+ *
+ * fms_peer_publish: store this block's carries (P, S) -- forward (reverse = 0) or reverse
+ * (reverse = 1; S is then the reverse carry) -- into slot `rank` of every peer's buffer and raise
+ * a flag there.  `peer_buffers` is a HOST array of `world` device pointers: rank p's buffer as
+ * mapped in this process (entry `rank` is the local buffer).  Plain peer stores only.
+ *
+ * fms_peer_wait_fold: wait until the blocks this rank depends on (those before it for forward,
+ * after it for reverse) have published exchange number `exchange`, polling flags in LOCAL memory
+ * with a bound of `max_wait_seconds` (<= 30; 2 if out of range), then fold their carries with
+ * `carry0` (nullable; the carry entering the first block in scan order) into carry_out (rows).
+ * If the bound is hit the kernel still ends normally, writes 1 + reverse into the buffer's
+ * status word (fms_peer_exchange_status_offset() bytes into the buffer) and leaves carry0 in
+ * carry_out; the host reads the word to learn of it.
+ *
+ * `exchange` numbers start at 1 and grow by one per exchange and direction on ALL ranks alike;
+ * two generations of slots (by parity) let a rank run one exchange ahead of a slower peer.
+ */
+#define FMS_MAX_PEERS 8
+size_t fms_peer_exchange_bytes(int64_t rows, int world);
+size_t fms_peer_exchange_status_offset(int64_t rows, int world);
+int fms_peer_publish(const float *P, const float *S, int64_t rows, void *const *peer_buffers, int world, int rank,
+                     int reverse, uint32_t exchange, fms_stream_t stream);
+int fms_peer_wait_fold(void *local_buffer, const float *carry0, float *carry_out, int64_t rows, int world, int rank,
+                       int reverse, uint32_t exchange, double max_wait_seconds, fms_stream_t stream);
+
 /* ------------------------------------------------------- host-buffer pipeline (one GPU) ---- */
 
 /*

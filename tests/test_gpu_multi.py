@@ -50,12 +50,22 @@ def _worker(rank, world, port, mode, storage, out_dir):
             ad, xd, gd = (G.dev(np.ascontiguousarray(v[:, tb[0]:tb[1]]), storage, dev)
                           .view(B, D, -1).requires_grad_(v is not Gd) for v in (a, x, Gd))
             h0d = G.dev(h0, storage, dev).view(B, D).requires_grad_(True)
-            h = fm_scan_time_split(ad, xd, h0d)
+            exchange = None
+            if mode == "time_peer":
+                from fm_b200.peer_exchange import PeerCarryExchange
+                exchange = PeerCarryExchange(B * D)
+            h = fm_scan_time_split(ad, xd, h0d, exchange=exchange)
             h.backward(gd)
+            if exchange is not None:
+                # a second round on the same buffers (next exchange numbers, other parity)
+                ad.grad = xd.grad = h0d.grad = None
+                h = fm_scan_time_split(ad, xd, h0d, exchange=exchange)
+                h.backward(gd)
+                exchange.check()
         torch.cuda.synchronize()
         out = dict(h=G.host(h).reshape(-1, h.shape[-1]), ga=G.host(ad.grad).reshape(-1, h.shape[-1]),
                    gx=G.host(xd.grad).reshape(-1, h.shape[-1]))
-        if mode == "time":
+        if mode != "rows":
             out["gh0"] = G.host(h0d.grad).reshape(-1)
         np.savez(os.path.join(out_dir, f"rank{rank}.npz"), **out)
         dist.barrier()
@@ -88,10 +98,12 @@ def test_row_sharding_is_bit_identical_to_one_gpu(tmp_path, storage):
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("transport", ["time", "time_peer"])
 @pytest.mark.parametrize("storage", ["f32", "bf16"])
-def test_time_split_over_nccl_matches_oracle(tmp_path, storage):
+def test_time_split_over_nccl_matches_oracle(tmp_path, storage, transport):
+    """transport "time": NCCL all-gather; "time_peer": peer stores + flags in symmetric memory."""
     world = min(_ngpu(), 8)
-    parts = _run(world, "time", storage, tmp_path)
+    parts = _run(world, transport, storage, tmp_path)
     B, D, T = 2, 24, 8 * 1031
     a, x, Gd, h0 = H.make_inputs(B * D, T, 123, "sigmoid+3", storage, with_h0=True)
     f64 = np.float64

@@ -1,0 +1,83 @@
+"""The peer-memory carry exchange on ONE GPU: ranks emulated one after the other (every flag is
+raised before the kernel that waits for it is launched), and the bounded wait running out."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from fm_b200 import capi
+from fm_b200.peer_exchange import _bind
+
+pytestmark = pytest.mark.gpu
+
+
+def _buffers(rows, world):
+    L = _bind()
+    nbytes = int(L.fms_peer_exchange_bytes(rows, world))
+    bufs = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    ptrs = (ctypes.c_void_p * world)(*[b.data_ptr() for b in bufs])
+    return L, bufs, ptrs, int(L.fms_peer_exchange_status_offset(rows, world))
+
+
+@pytest.mark.parametrize("world", [2, 3, 8])
+def test_publish_then_fold_reproduces_the_serial_fold(world):
+    rows = 1000
+    L, bufs, ptrs, status_off = _buffers(rows, world)
+    rng = np.random.default_rng(world)
+    P = rng.uniform(0.2, 1.0, (world, rows)).astype(np.float32)
+    S = rng.standard_normal((world, rows)).astype(np.float32)
+    c0 = rng.standard_normal(rows).astype(np.float32)
+    st = torch.cuda.current_stream().cuda_stream
+    for number in (1, 2, 3):  # three exchanges: both slot generations and reuse of the first
+        Pd = torch.from_numpy(P * number / 3).cuda()
+        Sd = torch.from_numpy(S + number).cuda()
+        for reverse in (0, 1):
+            for r in range(world):
+                assert L.fms_peer_publish(Pd[r].data_ptr(), Sd[r].data_ptr(), rows, ptrs, world, r, reverse,
+                                          number, st) == capi.FMS_OK
+            c0d = torch.from_numpy(c0).cuda()
+            for r in range(world):
+                out = torch.empty(rows, device="cuda")
+                assert L.fms_peer_wait_fold(bufs[r].data_ptr(), c0d.data_ptr(), out.data_ptr(), rows, world, r,
+                                            reverse, number, 0.5, st) == capi.FMS_OK
+                c = c0.astype(np.float64).copy()
+                order = range(r) if not reverse else range(world - 1, r, -1)
+                for src in order:
+                    c = (P[src] * number / 3).astype(np.float32) * c + (S[src] + number).astype(np.float32)
+                np.testing.assert_allclose(out.cpu().numpy(), c, rtol=1e-5, atol=1e-5)
+    torch.cuda.synchronize()
+    for b in bufs:
+        assert int(b[status_off:status_off + 4].view(torch.int32).item()) == 0
+
+
+def test_wait_runs_out_and_reports_it():
+    """Nothing raises the flag: the kernel gives up after its bound, records it and ends normally;
+    the context stays usable."""
+    rows, world = 64, 2
+    L, bufs, ptrs, status_off = _buffers(rows, world)
+    c0 = torch.arange(rows, device="cuda", dtype=torch.float32)
+    out = torch.full((rows,), -1.0, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    assert L.fms_peer_wait_fold(bufs[1].data_ptr(), c0.data_ptr(), out.data_ptr(), rows, world, 1, 0, 1, 0.05,
+                                st) == capi.FMS_OK
+    t1.record()
+    torch.cuda.synchronize()
+    assert 20.0 < t0.elapsed_time(t1) < 1000.0          # about the 50 ms bound, not forever
+    assert int(bufs[1][status_off:status_off + 4].view(torch.int32).item()) == 1
+    assert torch.equal(out, c0)                          # the carry-in is passed through
+    # reverse direction reports code 2; rank world-1 depends on nobody in reverse and does not wait
+    assert L.fms_peer_wait_fold(bufs[0].data_ptr(), None, out.data_ptr(), rows, world, 0, 1, 1, 0.05, st) == capi.FMS_OK
+    torch.cuda.synchronize()
+    assert int(bufs[0][status_off:status_off + 4].view(torch.int32).item()) == 2
+    assert float((torch.ones(4, device="cuda") * 2).sum()) == 8.0   # device still answers
+
+
+def test_argument_checks():
+    L = _bind()
+    assert L.fms_peer_exchange_bytes(100, 9) == 0 and L.fms_peer_exchange_bytes(100, 8) > 0
+    buf = (ctypes.c_void_p * 2)(None, None)
+    assert L.fms_peer_publish(None, None, 10, buf, 2, 0, 0, 1, None) == capi.FMS_ERR_NULL_POINTER
+    assert L.fms_peer_publish(None, None, 10, buf, 2, 5, 0, 1, None) == capi.FMS_ERR_BAD_SHAPE

@@ -447,11 +447,12 @@ int launch_fm_backward_blocked(const FmShape &sh, const void *gates, const void 
     if (sh.B > 0x7fffffffLL / m_blocks || sh.B * m_blocks > 0x7fffffffLL / d_blocks) return FMS_ERR_BAD_SHAPE;
     const unsigned grid = static_cast<unsigned>(sh.B * m_blocks * d_blocks);
     const int pd = tune_value("FMS_TUNE_FM_PD", 4);
+    // the shared-memory opt-in is per device, so it is (cheaply) repeated on every launch
     constexpr size_t smem = fms::fm_backward_blocked_smem<S, MC, DC>();
 #define FMS_LAUNCH_FM_BLOCKED(PDV)                                                                  \
     do {                                                                                            \
         auto kern = fms::fm_backward_blocked_kernel<S, MC, DC, PDV>;                                \
-        static const cudaError_t attr = cudaFuncSetAttribute(                                       \
+        const cudaError_t attr = cudaFuncSetAttribute(                                              \
             kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));             \
         if (int rc = record(attr)) return rc;                                                       \
         kern<<<grid, MC * 32, smem, st>>>(                                                          \
@@ -591,12 +592,12 @@ int launch_fm_readout(const FmShape &sh, const void *gates, const void *tokens, 
     auto k0 = fms::fm_readout_blocked_kernel<S, MC, DC, 0>;
     auto k1 = fms::fm_readout_blocked_kernel<S, MC, DC, 1>;
     auto k2 = fms::fm_readout_blocked_kernel<S, MC, DC, 2>;
-    static const cudaError_t a2 =
+    const cudaError_t a2 =
         cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (int rc = record(a2)) return rc;
-    static const cudaError_t a0 =
+    const cudaError_t a0 =
         cudaFuncSetAttribute(k0, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    static const cudaError_t a1 =
+    const cudaError_t a1 =
         cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (int rc = record(a0)) return rc;
     if (int rc = record(a1)) return rc;
@@ -689,7 +690,7 @@ int launch_fm_layer_backward(const FmShape &sh, const void *gates, const void *t
 #define FMS_LAUNCH_LAYER_BWD(EXTV, PDV)                                                                 \
     do {                                                                                                \
         auto kern = fms::fm_layer_backward_blocked_kernel<S, MC, DC, PDV, EXTV>;                        \
-        static const cudaError_t attr = cudaFuncSetAttribute(                                           \
+        const cudaError_t attr = cudaFuncSetAttribute(                                                  \
             kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));                 \
         if (int rc = record(attr)) return rc;                                                           \
         kern<<<grid, MC * 32, smem, st>>>(static_cast<const S *>(gates), static_cast<const S *>(tokens), hn_, dout_, \

@@ -71,7 +71,7 @@ def build_capi(force: bool = False, verbose: bool = False) -> Path:
         return CAPI_LIB
     LIB_DIR.mkdir(exist_ok=True)
     nvcc = _cuda_home() / "bin" / "nvcc"
-    cmd = [nvcc, *NVCC_ARCH, "-lineinfo", "-O3", "-std=c++17", "-Xptxas", "-v",
+    cmd = [nvcc, *NVCC_ARCH, "-lineinfo", "-O3", "-std=c++17", "--threads", "0", "-Xptxas", "-v",
            "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared", f"-I{INCLUDE}", f"-I{CSRC}",
            "-o", CAPI_LIB, *sorted(CSRC.glob("*.cu"))]
     res = _run(cmd, verbose)

@@ -424,3 +424,56 @@ def test_persistent_walk_over_several_rows(monkeypatch, K, storage, R, T, ctas):
     _, _, Srev_ref = oc.plain_backward(a.astype(f64), np.zeros_like(a, dtype=f64), Gd.astype(f64), dtype=f64)
     H.assert_close(G.host(P2), P_ref, 1e-4, 1e-30, "P (reverse)")
     H.assert_close(G.host(S2), Srev_ref, 1e-4, 1e-5, "S_rev")
+
+
+def test_randomised_shapes_and_launch_shapes(monkeypatch):
+    """Seeded sweep over dtype, rows, length, alignment offset and every launch-shape knob
+    (warps per row, tiles per step, persistent walk, grid cap) against the oracle in double."""
+    import random
+    rnd = random.Random(20261125)
+    done = 0
+    while done < 80:
+        storage = rnd.choice(["f32", "f16", "bf16"])
+        R = rnd.choice([1, 2, 3, 5, 17, 64, 257, 1000])
+        T = rnd.choice([1, 2, 7, 8, 15, 16, 31, 33, 100, 255, 256, 512, 777, 1024, 2048, 3000, 4097, 8192, 20000])
+        if R * T > 2_000_000:
+            continue
+        for name, choices in (("FMS_TUNE_FWD_K", [0, 1, 2, 4, 8]), ("FMS_TUNE_BWD_K", [0, 1, 2, 4, 8]),
+                              ("FMS_TUNE_FWD_U", [0, 1, 2, 4]), ("FMS_TUNE_BWD_U", [0, 1, 2, 4]),
+                              ("FMS_TUNE_PERSIST", [0, 1]), ("FMS_TUNE_MAX_CTAS", [0, 1, 3, 50])):
+            v = rnd.choice(choices)
+            if v:
+                monkeypatch.setenv(name, str(v))
+            else:
+                monkeypatch.delenv(name, raising=False)
+        gates = rnd.choice(["sigmoid", "sigmoid01", "sigmoid+3"])
+        off = rnd.choice([0, 0, 1, 3])
+        a, x, Gd, h0 = H.make_inputs(R, T, 9000 + done, gates, storage, with_h0=True)
+        cin = np.linspace(-1, 1, R).astype(np.float32)
+        dt = G.TORCH_DT[storage]
+
+        def place(arr):
+            buf = torch.zeros(R * T + 8, device="cuda", dtype=dt)
+            view = buf[off:off + R * T].view(R, T)
+            view.copy_(G.dev(arr, storage))
+            return view
+
+        ad, xd, gd = place(a), place(x), place(Gd)
+        h, hl = G.forward(ad, xd, G.dev(h0), want_last=True)
+        ga, gx, gh0 = G.backward(ad, h, gd, G.dev(h0), G.dev(cin), want_gh0=True)
+        torch.cuda.synchronize()
+        f64 = np.float64
+        hs = G.host(h)
+        h_ref = oc.plain_forward(a.astype(f64), x.astype(f64), h0.astype(f64), dtype=f64)
+        ga_ref, gx_ref, gh0_ref = oc.plain_backward(a.astype(f64), hs.astype(f64), Gd.astype(f64), h0.astype(f64),
+                                                    cin.astype(f64), dtype=f64)
+        what = f"case {done}: {storage} {R}x{T} {gates} offset {off}"
+        if storage == "f32":
+            tol = lambda r: (H.FP32_RTOL, H.FP32_ATOL * max(1.0, float(np.abs(r).max(initial=0))))
+        else:
+            tol = lambda r: (H.LOWP_RTOL, H.lowp_atol(r) + 1e-3)
+        H.assert_close(hs, h_ref, *tol(h_ref), what + " states")
+        H.assert_close(G.host(gx), gx_ref, *tol(gx_ref), what + " grad_tokens")
+        H.assert_close(G.host(ga), ga_ref, *tol(ga_ref), what + " grad_gates")
+        H.assert_close(G.host(gh0), gh0_ref, 1e-3, 1e-3 * max(1.0, float(np.abs(gh0_ref).max())), what + " grad_h0")
+        done += 1

@@ -6,6 +6,7 @@
 #include <cstdlib>
 #include <mutex>
 
+#include "btd_kernels.cuh"
 #include "fm_kernels.cuh"
 #include "scan_kernels.cuh"
 
@@ -768,6 +769,118 @@ FMS_EXPORT int fms_fm_layer_backward(const void *gates, const void *tokens, cons
                                                            grad_states_norm, rnorm, h0,
                                                            static_cast<float *>(workspace), grad_gates, grad_tokens,
                                                            grad_out_weight, grad_h0, st)));
+}
+
+// ------------------------------------------------------------------ channel-last layout -----
+namespace {
+
+bool make_btd_geom(fms::BtdGeom &g, int64_t B, int64_t T, int64_t D, int dtype) {
+    const int64_t E = 16 / static_cast<int64_t>(elem_size(dtype));
+    g.B = B;
+    g.T = T;
+    g.D = D;
+    g.dtiles = (D + 32 * E - 1) / (32 * E);
+    // enough warps to fill the GPU, chunks of at least 16 steps
+    int64_t want = (148 * 32 + B * g.dtiles - 1) / (B * g.dtiles);
+    want = std::max<int64_t>(1, std::min<int64_t>(want, (T + 15) / 16));
+    g.chunk = (T + want - 1) / want;
+    g.nchunks = (T + g.chunk - 1) / g.chunk;
+    return true;
+}
+
+int btd_check(int64_t B, int64_t T, int64_t D, int dtype) {
+    if (dtype != FMS_F32 && dtype != FMS_F16 && dtype != FMS_BF16) return FMS_ERR_BAD_DTYPE;
+    if (B < 0 || T < 0 || D < 0) return FMS_ERR_BAD_SHAPE;
+    if (B && D && (B > INT64_MAX / 8 / D || (T && B * D > INT64_MAX / 8 / T))) return FMS_ERR_BAD_SHAPE;
+    return FMS_OK;
+}
+
+inline int64_t btd_ctas(const fms::BtdGeom &g) {
+    return (g.B * g.nchunks * g.dtiles + fms::kBtdWarps - 1) / fms::kBtdWarps;
+}
+
+template <typename S>
+int launch_btd_forward(const fms::BtdGeom &g, const void *gates, const void *tokens, const float *h0, void *states,
+                       float *h_last, float *wP, float *wS, cudaStream_t st) {
+    const int64_t ctas = btd_ctas(g);
+    if (ctas > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;
+    const unsigned grid = static_cast<unsigned>(ctas), block = fms::kBtdWarps * 32;
+    fms::btd_reduce_kernel<S, false><<<grid, block, 0, st>>>(static_cast<const S *>(gates),
+                                                             static_cast<const S *>(tokens), wP, wS, g);
+    if (int rc = check_launch()) return rc;
+    const int64_t fb = (g.B * g.D + 255) / 256;
+    fms::btd_fold_kernel<<<static_cast<unsigned>(fb), 256, 0, st>>>(wP, wS, h0, h_last, g, 0);
+    if (int rc = check_launch()) return rc;
+    fms::btd_forward_kernel<S><<<grid, block, 0, st>>>(static_cast<const S *>(gates), static_cast<const S *>(tokens),
+                                                       wS, static_cast<S *>(states), g);
+    return check_launch();
+}
+
+template <typename S>
+int launch_btd_backward(const fms::BtdGeom &g, const void *gates, const void *states, const void *grad_states,
+                        const float *h0, void *grad_gates, void *grad_tokens, float *grad_h0, float *wP, float *wS,
+                        cudaStream_t st) {
+    const int64_t ctas = btd_ctas(g);
+    if (ctas > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;
+    const unsigned grid = static_cast<unsigned>(ctas), block = fms::kBtdWarps * 32;
+    fms::btd_reduce_kernel<S, true><<<grid, block, 0, st>>>(static_cast<const S *>(gates),
+                                                            static_cast<const S *>(grad_states), wP, wS, g);
+    if (int rc = check_launch()) return rc;
+    const int64_t fb = (g.B * g.D + 255) / 256;
+    fms::btd_fold_kernel<<<static_cast<unsigned>(fb), 256, 0, st>>>(wP, wS, nullptr, grad_h0, g, 1);
+    if (int rc = check_launch()) return rc;
+    fms::btd_backward_kernel<S><<<grid, block, 0, st>>>(static_cast<const S *>(gates), static_cast<const S *>(states),
+                                                        static_cast<const S *>(grad_states), h0, wS,
+                                                        static_cast<S *>(grad_gates), static_cast<S *>(grad_tokens), g);
+    return check_launch();
+}
+
+}  // namespace
+
+FMS_EXPORT size_t fms_btd_workspace_bytes(int64_t B, int64_t T, int64_t D, int dtype) {
+    if (btd_check(B, T, D, dtype) != FMS_OK || B == 0 || T == 0 || D == 0) return 0;
+    fms::BtdGeom g;
+    make_btd_geom(g, B, T, D, dtype);
+    return (static_cast<size_t>(2) * B * g.nchunks * D * sizeof(float) + 255) / 256 * 256;
+}
+
+FMS_EXPORT int fms_btd_forward(const void *gates, const void *tokens, const float *h0, void *states, float *h_last,
+                               int64_t B, int64_t T, int64_t D, int dtype, void *workspace, size_t workspace_bytes,
+                               fms_stream_t stream) {
+    if (int rc = btd_check(B, T, D, dtype)) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (B == 0 || D == 0) return FMS_OK;
+    if (T == 0) return copy_or_zero(h0, h_last, B * D, 0.f, st);
+    bool aligned = false;
+    if (int rc = fm_alignment(aligned, D, dtype, gates, tokens, static_cast<const void *>(states))) return rc;
+    if (!aligned) return FMS_ERR_MISALIGNED;  // D * element size must be a multiple of 16 bytes
+    const size_t need = fms_btd_workspace_bytes(B, T, D, dtype);
+    if (!workspace || !aligned_to(workspace, 16) || workspace_bytes < need) return FMS_ERR_WORKSPACE;
+    fms::BtdGeom g;
+    make_btd_geom(g, B, T, D, dtype);
+    float *wP = static_cast<float *>(workspace), *wS = wP + B * g.nchunks * D;
+    FMS_DISPATCH_DTYPE(dtype, (launch_btd_forward<S>(g, gates, tokens, h0, states, h_last, wP, wS, st)));
+}
+
+FMS_EXPORT int fms_btd_backward(const void *gates, const void *states, const void *grad_states, const float *h0,
+                                void *grad_gates, void *grad_tokens, float *grad_h0, int64_t B, int64_t T, int64_t D,
+                                int dtype, void *workspace, size_t workspace_bytes, fms_stream_t stream) {
+    if (int rc = btd_check(B, T, D, dtype)) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (B == 0 || D == 0) return FMS_OK;
+    if (T == 0) return copy_or_zero(nullptr, grad_h0, B * D, 0.f, st);
+    bool aligned = false;
+    if (int rc = fm_alignment(aligned, D, dtype, gates, states, grad_states, static_cast<const void *>(grad_gates),
+                              static_cast<const void *>(grad_tokens)))
+        return rc;
+    if (!aligned) return FMS_ERR_MISALIGNED;
+    const size_t need = fms_btd_workspace_bytes(B, T, D, dtype);
+    if (!workspace || !aligned_to(workspace, 16) || workspace_bytes < need) return FMS_ERR_WORKSPACE;
+    fms::BtdGeom g;
+    make_btd_geom(g, B, T, D, dtype);
+    float *wP = static_cast<float *>(workspace), *wS = wP + B * g.nchunks * D;
+    FMS_DISPATCH_DTYPE(dtype, (launch_btd_backward<S>(g, gates, states, grad_states, h0, grad_gates, grad_tokens,
+                                                      grad_h0, wP, wS, st)));
 }
 
 // ------------------------------------------------------------------ split inside one GPU ----

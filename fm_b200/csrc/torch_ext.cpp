@@ -317,6 +317,52 @@ void fm_memory_backward(const at::Tensor &gates, const at::Tensor &tokens, const
                  "fm_memory_backward");
 }
 
+// Channel-last layout: gates, tokens, out (B, T, D); initial_state (B, D) or None.
+at::Tensor fm_scan_btd_forward(const at::Tensor &gates, const at::Tensor &tokens,
+                               const c10::optional<at::Tensor> &initial_state, const at::Tensor &out) {
+    TORCH_CHECK(gates.is_cuda() && gates.is_contiguous() && gates.dim() == 3, "gates must be a contiguous CUDA (B,T,D) tensor");
+    check_big(tokens, gates, "tokens");
+    check_big(out, gates, "out");
+    const int64_t B = gates.size(0), T = gates.size(1), D = gates.size(2);
+    const int dtype = dtype_tag(gates);
+    const c10::cuda::CUDAGuard guard(gates.device());
+    at::Tensor h0 = carry_f32(initial_state, B * D, gates, "initial_state");
+    const size_t scratch = fms_btd_workspace_bytes(B, T, D, dtype);
+    at::Tensor ws = at::empty({static_cast<int64_t>(std::max<size_t>(scratch, 16))}, gates.options().dtype(at::kByte));
+    check_status(fms_btd_forward(gates.data_ptr(), tokens.data_ptr(), fptr(h0), out.data_ptr(), nullptr, B, T, D, dtype,
+                                 ws.data_ptr(), scratch, at::cuda::getCurrentCUDAStream().stream()),
+                 "fm_scan_forward (B,T,D)");
+    return out;
+}
+
+void fm_scan_btd_backward(const at::Tensor &gates, const at::Tensor &outGrad, const at::Tensor &tokenGradOut,
+                          const at::Tensor &cached_output, const at::Tensor &gateGradOut,
+                          const c10::optional<at::Tensor> &initial_state,
+                          const c10::optional<at::Tensor> &grad_initial_state) {
+    TORCH_CHECK(gates.is_cuda() && gates.is_contiguous() && gates.dim() == 3, "gates must be a contiguous CUDA (B,T,D) tensor");
+    check_big(outGrad, gates, "outGrad");
+    check_big(cached_output, gates, "cached_output");
+    check_big(tokenGradOut, gates, "tokenGradOut");
+    check_big(gateGradOut, gates, "gateGradOut");
+    const int64_t B = gates.size(0), T = gates.size(1), D = gates.size(2);
+    const int dtype = dtype_tag(gates);
+    const c10::cuda::CUDAGuard guard(gates.device());
+    at::Tensor h0 = carry_f32(initial_state, B * D, gates, "initial_state");
+    float *gh0 = nullptr;
+    if (grad_initial_state.has_value() && grad_initial_state->defined() && grad_initial_state->numel() > 0) {
+        TORCH_CHECK(grad_initial_state->is_cuda() && grad_initial_state->is_contiguous() &&
+                        grad_initial_state->scalar_type() == at::kFloat && grad_initial_state->numel() == B * D,
+                    "grad_initial_state must be a contiguous fp32 CUDA tensor of B*D elements");
+        gh0 = grad_initial_state->data_ptr<float>();
+    }
+    const size_t scratch = fms_btd_workspace_bytes(B, T, D, dtype);
+    at::Tensor ws = at::empty({static_cast<int64_t>(std::max<size_t>(scratch, 16))}, gates.options().dtype(at::kByte));
+    check_status(fms_btd_backward(gates.data_ptr(), cached_output.data_ptr(), outGrad.data_ptr(), fptr(h0),
+                                  gateGradOut.data_ptr(), tokenGradOut.data_ptr(), gh0, B, T, D, dtype, ws.data_ptr(),
+                                  scratch, at::cuda::getCurrentCUDAStream().stream()),
+                 "fm_scan_backward (B,T,D)");
+}
+
 // Backward with the reference's seven arguments.  firstPropGrad seeds the reverse scan
 // (fm/scan/fm_scan.cuh:120-122); the reference passes zeros (fm/scan/fm_scan.py:65).
 // input_tokens is accepted for signature compatibility and not read: with the token weight
@@ -343,6 +389,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("fm_scan_backward", &fm_scan_backward, "scan backward, reference signature");
     m.def("fm_scan_backward_ex", &fm_scan_backward_ex, "scan backward with h0 / carry_in / grad_h0");
     m.def("fm_scan_backward_fm", &fm_scan_backward_fm, "FM-mode backward with fused reductions");
+    m.def("fm_scan_btd_forward", &fm_scan_btd_forward, "scan forward on (B,T,D) tensors");
+    m.def("fm_scan_btd_backward", &fm_scan_btd_backward, "scan backward on (B,T,D) tensors");
     m.def("fm_memory_forward_train", &fm_memory_forward_train, "layer forward: output + normalised states");
     m.def("fm_memory_backward", &fm_memory_backward, "layer backward with the state gradient generated in-kernel");
     m.def("fm_memory_readout", &fm_memory_readout, "layer read-out without materialising the states");

@@ -130,6 +130,38 @@ class FM_Scan(torch.autograd.Function):
         return d_gates, d_tokens, d_h0
 
 
+class FM_Scan_BTD(torch.autograd.Function):
+    """The plain scan on channel-last tensors: gates, tokens, states (B, T, D), recurrence along T,
+    initial_state (B, D).  This is the layout the reference's layer holds before it transposes
+    for every call (fm/scan/fm_scan.py:118-119)."""
+
+    @staticmethod
+    def forward(ctx, gates, tokens, initial_state=None):
+        assert gates.dim() == 3 and gates.shape == tokens.shape
+        assert gates.is_contiguous()
+        assert tokens.is_contiguous()
+        if initial_state is not None:
+            assert initial_state.shape == (gates.shape[0], gates.shape[2])
+            assert initial_state.is_contiguous()
+        states = _load_ext().fm_scan_btd_forward(gates, tokens, initial_state, torch.empty_like(gates))
+        ctx.save_for_backward(gates, states, initial_state)
+        ctx.h0_needs_grad = initial_state is not None and ctx.needs_input_grad[2]
+        return states
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        gates, states, initial_state = ctx.saved_tensors
+        d_gates, d_tokens = torch.empty_like(gates), torch.empty_like(gates)
+        d_h0 = None
+        if ctx.h0_needs_grad:
+            d_h0 = torch.empty(initial_state.shape, device=gates.device, dtype=torch.float32)
+        _load_ext().fm_scan_btd_backward(gates, grad_output.contiguous(), d_tokens, states, d_gates,
+                                         initial_state, d_h0)
+        if d_h0 is not None:
+            d_h0 = d_h0.to(initial_state.dtype)
+        return d_gates, d_tokens, d_h0
+
+
 def fm_scan(gates, tokens, initial_state=None, mode="plain"):
     """Solve the first-order recurrence along the last axis.
 
@@ -144,10 +176,15 @@ def fm_scan(gates, tokens, initial_state=None, mode="plain"):
         ``h[b,m,d,t] = g[b,m,t] * h[b,m,d,t-1] + (1 - g[b,m,t]) * x[b,d,t]``
         gates (B, M, L), tokens (B, D, L), initial_state (B, M, D) -> states (B, M, D, L).
 
-    Arithmetic is fp32 in both modes.
+    ``mode="btd"``: the plain recurrence on channel-last tensors, gates, tokens (B, T, D),
+        initial_state (B, D) -> states (B, T, D); D * element size must be a multiple of 16 bytes.
+
+    Arithmetic is fp32 in all modes.
     """
+    if mode == "btd":
+        return FM_Scan_BTD.apply(gates, tokens, initial_state)
     if mode == "fm":
         return FM_Scan_Outer.apply(gates, tokens, initial_state)
     if mode != "plain":
-        raise ValueError("mode must be 'plain' or 'fm'")
+        raise ValueError("mode must be 'plain', 'fm' or 'btd'")
     return FM_Scan.apply(gates, tokens, initial_state)

@@ -199,6 +199,25 @@ int fms_fm_layer_backward(const void *gates, const void *tokens, const void *out
                           int64_t M, int64_t D, int64_t L, int dtype, void *workspace, size_t workspace_bytes,
                           fms_stream_t stream);
 
+/* ------------------------------------------------------------ channel-last layout (B, T, D) ---- */
+
+/*
+ * The plain scan on tensors laid out (B, T, D): one recurrence per (b, d) along T, channels
+ * contiguous.  This is the layout the reference's layer receives before it transposes to
+ * (B, ., L) for every call (fm/scan/fm_scan.py:118-119); scanning it directly removes those
+ * transposes.  h0, h_last, grad_h0: (B, D) fp32, nullable.  Time is cut into chunks (carries of
+ * every chunk, fold, scan from the true carry-in), which needs fms_btd_workspace_bytes() of
+ * caller scratch.  D * element size must be a multiple of 16 bytes and the bases 16-byte
+ * aligned (FMS_ERR_MISALIGNED otherwise).
+ */
+size_t fms_btd_workspace_bytes(int64_t B, int64_t T, int64_t D, int dtype);
+int fms_btd_forward(const void *gates, const void *tokens, const float *h0, void *states, float *h_last,
+                    int64_t B, int64_t T, int64_t D, int dtype, void *workspace, size_t workspace_bytes,
+                    fms_stream_t stream);
+int fms_btd_backward(const void *gates, const void *states, const void *grad_states, const float *h0,
+                     void *grad_gates, void *grad_tokens, float *grad_h0, int64_t B, int64_t T, int64_t D,
+                     int dtype, void *workspace, size_t workspace_bytes, fms_stream_t stream);
+
 /* ------------------------------------------------- few, long rows: split inside one GPU ---- */
 
 /*

@@ -16,8 +16,14 @@
 
 namespace fms {
 
-constexpr int kBtdWarps = 4;  // warps per CTA = adjacent channel tiles of one (b, chunk)
-constexpr int kBtdPF = 4;     // time steps in flight per lane
+#ifndef FMS_BTD_WARPS
+#define FMS_BTD_WARPS 4
+#endif
+#ifndef FMS_BTD_PF
+#define FMS_BTD_PF 4
+#endif
+constexpr int kBtdWarps = FMS_BTD_WARPS;  // warps per CTA = adjacent channel tiles of one (b, chunk)
+constexpr int kBtdPF = FMS_BTD_PF;        // time steps in flight per lane
 
 struct BtdGeom {
     int64_t B, T, D, nchunks, chunk, dtiles;  // dtiles = ceil(D / (32*E))

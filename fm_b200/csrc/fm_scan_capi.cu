@@ -781,7 +781,8 @@ bool make_btd_geom(fms::BtdGeom &g, int64_t B, int64_t T, int64_t D, int dtype) 
     g.D = D;
     g.dtiles = (D + 32 * E - 1) / (32 * E);
     // enough warps to fill the GPU, chunks of at least 16 steps
-    int64_t want = (148 * 32 + B * g.dtiles - 1) / (B * g.dtiles);
+    const int64_t target = std::max(1, tune_value("FMS_TUNE_BTD_WARPS_PER_SM", 32));
+    int64_t want = (148 * target + B * g.dtiles - 1) / (B * g.dtiles);
     want = std::max<int64_t>(1, std::min<int64_t>(want, (T + 15) / 16));
     g.chunk = (T + want - 1) / want;
     g.nchunks = (T + g.chunk - 1) / g.chunk;

@@ -519,6 +519,52 @@ def run_fm_mode(args):
     print(json.dumps(line), flush=True)
 
 
+def run_channel_last(args):
+    """Secondary workload: the plain scan on channel-last tensors (B,T,D) = (16,8192,2048) bf16
+    (`--rows` sets B; a small B is the profiler case).  One GPU; prints its own JSON line."""
+    import torch
+
+    from fm_b200.fm_scan import _load_ext
+
+    ext = _load_ext()
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    B, T, D = args.rows or 16, 8192, 2048
+    gen = torch.Generator(device=dev).manual_seed(1080)
+    a = (1.0 - torch.pow(10.0, -4.0 + 3.0 * torch.rand(B, T, D, device=dev, generator=gen))).to(torch.bfloat16)
+    x = torch.randn(B, T, D, device=dev, generator=gen).to(torch.bfloat16)
+    G = torch.randn(B, T, D, device=dev, generator=gen).to(torch.bfloat16)
+    h, ga, gx = torch.empty_like(a), torch.empty_like(a), torch.empty_like(a)
+    for _ in range(max(3, args.warmup)):
+        ext.fm_scan_btd_forward(a, x, None, h)
+        ext.fm_scan_btd_backward(a, G, gx, h, ga, None, None)
+    torch.cuda.synchronize()
+    K = args.steps
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+    with ClockSampler(physical_gpu_index(0)) as clocks:
+        for k in range(K):
+            ev[k][0].record()
+            ext.fm_scan_btd_forward(a, x, None, h)
+            ev[k][1].record()
+            ext.fm_scan_btd_backward(a, G, gx, h, ga, None, None)
+            ev[k][2].record()
+        torch.cuda.synchronize()
+    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+    bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+    n = B * T * D
+    peak, kind = measured_peak()
+    line = {"metric": "channel-last scan fwd+bwd elements/s", "value": n / ((fwd_ms + bwd_ms) * 1e-3), "unit": UNIT,
+            "n_gpus": 1, "steps": K, "warmup": max(3, args.warmup), "ms_per_step": fwd_ms + bwd_ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "plain scan on (B,T,D)=(%d,%d,%d) bf16 storage / fp32 accumulate" % (B, T, D)},
+            "gpu_launches": K * 6, "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
+            "roofline_fwd_bwd": {"algorithmic_GBs": 16 * n / ((fwd_ms + bwd_ms) * 1e-3) / 1e9,
+                                 "moved_GBs": 24 * n / ((fwd_ms + bwd_ms) * 1e-3) / 1e9, "peak": peak,
+                                 "peak_kind": kind},
+            "clocks": clocks.summary()}
+    print(json.dumps(line), flush=True)
+
+
 def run_e2e(args, a3, x3, G3, device, barrier):
     """Same step with pinned HOST inputs and outputs through the host-buffer entry of the C ABI.
 
@@ -566,9 +612,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
-    ap.add_argument("--workload", choices=["c3", "c4", "fm"], default="c3",
+    ap.add_argument("--workload", choices=["c3", "c4", "fm", "btd"], default="c3",
                     help="c3: the headline row-sharded workload; c4: the long sequence split along T; "
-                         "fm: the reference's (B,M,L)x(B,D,L)->(B,M,D,L) operator at its demo shape")
+                         "fm: the reference's (B,M,L)x(B,D,L)->(B,M,D,L) operator at its demo shape; "
+                         "btd: the plain scan on channel-last (B,T,D) tensors")
     ap.add_argument("--exchange", choices=["nccl", "peer"], default="nccl",
                     help="carry transport of --workload c4")
     ap.add_argument("--e2e-steps", type=int, default=5)
@@ -583,6 +630,8 @@ def main():
         run_time_split(args)
     elif args.workload == "fm":
         run_fm_mode(args)
+    elif args.workload == "btd":
+        run_channel_last(args)
     else:
         run_ours(args)
 

@@ -802,37 +802,49 @@ inline int64_t btd_ctas(const fms::BtdGeom &g) {
 
 template <typename S>
 int launch_btd_forward(const fms::BtdGeom &g, const void *gates, const void *tokens, const float *h0, void *states,
-                       float *h_last, float *wP, float *wS, cudaStream_t st) {
+                       float *h_last, float *wP, float *wS, float *wC, cudaStream_t st) {
     const int64_t ctas = btd_ctas(g);
     if (ctas > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;
     const unsigned grid = static_cast<unsigned>(ctas), block = fms::kBtdWarps * 32;
-    fms::btd_reduce_kernel<S, false><<<grid, block, 0, st>>>(static_cast<const S *>(gates),
-                                                             static_cast<const S *>(tokens), wP, wS, g);
+    constexpr size_t ring2 = fms::btd_ring_bytes<2>();
+    auto kr = fms::btd_reduce_kernel<S, false>;
+    auto kf = fms::btd_forward_kernel<S>;
+    if (int rc = record(cudaFuncSetAttribute(kr, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(ring2))))
+        return rc;
+    if (int rc = record(cudaFuncSetAttribute(kf, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(ring2))))
+        return rc;
+    kr<<<grid, block, ring2, st>>>(static_cast<const S *>(gates), static_cast<const S *>(tokens), wP, wS, g);
     if (int rc = check_launch()) return rc;
     const int64_t fb = (g.B * g.D + 255) / 256;
-    fms::btd_fold_kernel<<<static_cast<unsigned>(fb), 256, 0, st>>>(wP, wS, h0, h_last, g, 0);
+    fms::btd_fold_kernel<<<static_cast<unsigned>(fb), 256, 0, st>>>(wP, wS, wC, h0, h_last, g, 0);
     if (int rc = check_launch()) return rc;
-    fms::btd_forward_kernel<S><<<grid, block, 0, st>>>(static_cast<const S *>(gates), static_cast<const S *>(tokens),
-                                                       wS, static_cast<S *>(states), g);
+    kf<<<grid, block, ring2, st>>>(static_cast<const S *>(gates), static_cast<const S *>(tokens), wC,
+                                   static_cast<S *>(states), g);
     return check_launch();
 }
 
 template <typename S>
 int launch_btd_backward(const fms::BtdGeom &g, const void *gates, const void *states, const void *grad_states,
                         const float *h0, void *grad_gates, void *grad_tokens, float *grad_h0, float *wP, float *wS,
-                        cudaStream_t st) {
+                        float *wC, cudaStream_t st) {
     const int64_t ctas = btd_ctas(g);
     if (ctas > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;
     const unsigned grid = static_cast<unsigned>(ctas), block = fms::kBtdWarps * 32;
-    fms::btd_reduce_kernel<S, true><<<grid, block, 0, st>>>(static_cast<const S *>(gates),
-                                                            static_cast<const S *>(grad_states), wP, wS, g);
+    constexpr size_t ring2 = fms::btd_ring_bytes<2>(), ring3 = fms::btd_ring_bytes<3>();
+    auto kr = fms::btd_reduce_kernel<S, true>;
+    auto kb = fms::btd_backward_kernel<S>;
+    if (int rc = record(cudaFuncSetAttribute(kr, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(ring2))))
+        return rc;
+    if (int rc = record(cudaFuncSetAttribute(kb, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(ring3))))
+        return rc;
+    kr<<<grid, block, ring2, st>>>(static_cast<const S *>(gates), static_cast<const S *>(grad_states), wP, wS, g);
     if (int rc = check_launch()) return rc;
     const int64_t fb = (g.B * g.D + 255) / 256;
-    fms::btd_fold_kernel<<<static_cast<unsigned>(fb), 256, 0, st>>>(wP, wS, nullptr, grad_h0, g, 1);
+    fms::btd_fold_kernel<<<static_cast<unsigned>(fb), 256, 0, st>>>(wP, wS, wC, nullptr, grad_h0, g, 1);
     if (int rc = check_launch()) return rc;
-    fms::btd_backward_kernel<S><<<grid, block, 0, st>>>(static_cast<const S *>(gates), static_cast<const S *>(states),
-                                                        static_cast<const S *>(grad_states), h0, wS,
-                                                        static_cast<S *>(grad_gates), static_cast<S *>(grad_tokens), g);
+    kb<<<grid, block, ring3, st>>>(static_cast<const S *>(gates), static_cast<const S *>(states),
+                                   static_cast<const S *>(grad_states), h0, wC, static_cast<S *>(grad_gates),
+                                   static_cast<S *>(grad_tokens), g);
     return check_launch();
 }
 
@@ -842,7 +854,7 @@ FMS_EXPORT size_t fms_btd_workspace_bytes(int64_t B, int64_t T, int64_t D, int d
     if (btd_check(B, T, D, dtype) != FMS_OK || B == 0 || T == 0 || D == 0) return 0;
     fms::BtdGeom g;
     make_btd_geom(g, B, T, D, dtype);
-    return (static_cast<size_t>(2) * B * g.nchunks * D * sizeof(float) + 255) / 256 * 256;
+    return (static_cast<size_t>(3) * B * g.nchunks * D * sizeof(float) + 255) / 256 * 256;  // P, S, carries
 }
 
 FMS_EXPORT int fms_btd_forward(const void *gates, const void *tokens, const float *h0, void *states, float *h_last,
@@ -859,8 +871,8 @@ FMS_EXPORT int fms_btd_forward(const void *gates, const void *tokens, const floa
     if (!workspace || !aligned_to(workspace, 16) || workspace_bytes < need) return FMS_ERR_WORKSPACE;
     fms::BtdGeom g;
     make_btd_geom(g, B, T, D, dtype);
-    float *wP = static_cast<float *>(workspace), *wS = wP + B * g.nchunks * D;
-    FMS_DISPATCH_DTYPE(dtype, (launch_btd_forward<S>(g, gates, tokens, h0, states, h_last, wP, wS, st)));
+    float *wP = static_cast<float *>(workspace), *wS = wP + B * g.nchunks * D, *wC = wS + B * g.nchunks * D;
+    FMS_DISPATCH_DTYPE(dtype, (launch_btd_forward<S>(g, gates, tokens, h0, states, h_last, wP, wS, wC, st)));
 }
 
 FMS_EXPORT int fms_btd_backward(const void *gates, const void *states, const void *grad_states, const float *h0,
@@ -879,9 +891,9 @@ FMS_EXPORT int fms_btd_backward(const void *gates, const void *states, const voi
     if (!workspace || !aligned_to(workspace, 16) || workspace_bytes < need) return FMS_ERR_WORKSPACE;
     fms::BtdGeom g;
     make_btd_geom(g, B, T, D, dtype);
-    float *wP = static_cast<float *>(workspace), *wS = wP + B * g.nchunks * D;
+    float *wP = static_cast<float *>(workspace), *wS = wP + B * g.nchunks * D, *wC = wS + B * g.nchunks * D;
     FMS_DISPATCH_DTYPE(dtype, (launch_btd_backward<S>(g, gates, states, grad_states, h0, grad_gates, grad_tokens,
-                                                      grad_h0, wP, wS, st)));
+                                                      grad_h0, wP, wS, wC, st)));
 }
 
 // ------------------------------------------------------------------ split inside one GPU ----

@@ -195,3 +195,48 @@ def test_fused_layer_bf16_against_double(mem_norm):
     ref = [ref_out.detach(), h.detach()] + [a.grad for a in ref_args]
     for n, a, b in zip(["output", "states", "d_decay", "d_tokens", "d_weight"], got, ref):
         H.assert_close(a.numpy(), b.numpy(), 2e-2, 2e-2 * float(b.abs().pow(2).mean().sqrt()), n)
+
+
+def test_fm_randomised_shapes(monkeypatch):
+    """Seeded sweep over dtype, (B, M, D, L) with ragged blocks and tiles, exact 0/1 gates, with and
+    without an initial state, blocked and row-per-CTA kernels, against the oracle in double."""
+    import random
+    rnd = random.Random(1125)
+    done = 0
+    while done < 40:
+        storage = rnd.choice(["f32", "f16", "bf16"])
+        B, M, D = rnd.choice([1, 2, 3]), rnd.choice([1, 2, 7, 8, 9, 16, 33]), rnd.choice([1, 3, 8, 15, 16, 40, 65])
+        L = rnd.choice([8, 16, 24, 64, 128, 256, 264, 512, 1000, 1024, 2056])
+        if B * M * D * L > 1_500_000:
+            continue
+        monkeypatch.setenv("FMS_TUNE_FM_BLOCKED", str(rnd.choice([0, 1])))
+        rng = np.random.Generator(np.random.PCG64(7000 + done))
+        g = 0.3 + 0.7 * rng.random((B, M, L), dtype=np.float32)
+        if rnd.random() < 0.3:
+            mask = rng.random((B, M, L))
+            g = np.where(mask < 0.05, 0.0, np.where(mask > 0.95, 1.0, g)).astype(np.float32)
+        g = H.round_storage(g, storage)
+        x = H.round_storage(rng.standard_normal((B, D, L), dtype=np.float32), storage)
+        Gr = H.round_storage(rng.standard_normal((B, M, D, L), dtype=np.float32), storage)
+        h0 = H.round_storage(rng.standard_normal((B, M, D), dtype=np.float32), storage) if rnd.random() < 0.5 else None
+        gd, xd, Gd = G.dev(g, storage), G.dev(x, storage), G.dev(Gr, storage)
+        h0d = None if h0 is None else G.dev(h0)
+        h = G.fm_forward(gd, xd, h0d)
+        dg, dx, dh0 = G.fm_backward(gd, xd, h, Gd, h0d, want_gh0=True)
+        torch.cuda.synchronize()
+        f64 = np.float64
+        h064 = None if h0 is None else h0.astype(f64)
+        hs = G.host(h)
+        h_ref = oc.fm_forward(g.astype(f64), x.astype(f64), h064, dtype=f64)
+        dg_ref, dx_ref, dh0_ref = oc.fm_backward(g.astype(f64), x.astype(f64), hs.astype(f64), Gr.astype(f64), h064,
+                                                 dtype=f64)
+        if storage == "f32":
+            tol = lambda r: (1e-5, 2e-6 * max(1.0, float(np.abs(r).max())))
+        else:
+            tol = lambda r: (H.LOWP_RTOL, H.lowp_atol(r) + 1e-3)
+        what = f"case {done}: {storage} {(B, M, D, L)}"
+        H.assert_close(hs, h_ref, *tol(h_ref), what + " states")
+        H.assert_close(G.host(dx), dx_ref, *tol(dx_ref), what + " d_tokens")
+        H.assert_close(G.host(dg), dg_ref, *tol(dg_ref), what + " d_gates")
+        H.assert_close(G.host(dh0), dh0_ref, 1e-3, 1e-3 * max(1.0, float(np.abs(dh0_ref).max())), what + " d_h0")
+        done += 1

@@ -122,10 +122,11 @@ int choose_coop(int64_t units, int64_t T, size_t es, const char *env_name) {
     if (forced == 1 || forced == 2 || forced == 4 || forced == 8) return forced;
     // Measured on B200 (CUDA events, fwd+bwd GB/s): 16 KB rows x 32768 rows: K=2 6306, K=4 6182,
     // K=1 5797; 16 KB rows x 8192 rows: K=4 6026, K=2 5761; 128 KB rows x 4096 rows: K=8 6284,
-    // K=4 6143.  Rows shorter than 32 tiles keep one warp each.
+    // K=4 6143; 8 KB rows x 65536 rows: K=2 6374, K=1 6196, K=4 5770; 12 KB rows: K=2 6474,
+    // K=1 6217.  Rows shorter than 16 tiles keep one warp each.
     const int64_t tiles = (T * static_cast<int64_t>(es) + 511) / 512;
-    int k = tiles >= 128 ? 8 : tiles >= 64 ? 4 : tiles >= 32 ? 2 : 1;
-    if (k > 1 && k < 8 && units <= 8192) k *= 2;  // small launches: finer-grained CTAs shorten the tail
+    int k = tiles >= 128 ? 8 : tiles >= 64 ? 4 : tiles >= 16 ? 2 : 1;
+    if (tiles >= 32 && k < 8 && units <= 8192) k *= 2;  // small launches: finer-grained CTAs shorten the tail
     return k;
 }
 

@@ -6,17 +6,23 @@
 One "step" is one forward + one backward pass of the scan over the workload
 (B, D, T) = (16, 2048, 8192), bf16 storage / fp32 accumulation, long-memory gates
 a = 1 - 10^U(-4,-1), tokens and upstream gradient ~ N(0, 1), generated on the device from a
-seed (synthetic data).  Every tensor is 512 MiB, four times the L2, so no flush is needed
-between iterations.
+seed (synthetic data).  The six tensors of a step are at least three times the L2 at every N, so
+no flush is needed between iterations.
 
-For N > 1 launch under torchrun (one rank per GPU).  Rows are independent, so each rank scans
-its own (16, 2048, 8192) shard of a global batch of 16*N with no data-path collective (weak
-scaling); `--scaling strong` instead splits the fixed 32768 rows over the ranks.
+For N > 1 launch under torchrun (one rank per GPU).  Rows are independent, so they are sharded
+with no data-path collective.  The default is STRONG scaling -- the fixed 32768 rows of the
+workload are split over the ranks (32768 / N rows each) -- which is the curve the workload
+statement asks for; the weak figure (every rank a full 32768-row shard) rides along in the same
+line as `weak_scaling`, and `--scaling weak` makes it the headline instead.
 
 Rank 0 prints ONE JSON line.  `value` is device-timed whole-job throughput with inputs resident
 in HBM; `e2e` is the same metric through the host-buffer entry of the C ABI (pinned host
-inputs -> device -> pinned host outputs inside the timed region); `roofline` describes the
-dominant kernel (backward); `cpu_baseline` is the CPU port timed on this box's host cores.
+inputs -> device -> pinned host outputs inside the timed region) with the copy-only time of the
+same pipeline beside it; `roofline` describes the dominant kernel (backward); `cpu_baseline` is
+the CPU port timed on this box's host cores; `time_split` is the long-sequence problem
+(1, 4096, 262144) fp32 split along T over the N ranks, timed and checked against the oracle on a
+row subset; `reference_cuda` is the reference's own CUDA operator timed on the same GPU (a stated
+comparison, never the target).
 
 `--impl reference` times the CPU implementation of the path (the pinned C port of the
 reference loop, OpenMP over rows, all host threads) on a bounded sample of the same workload.
@@ -168,7 +174,8 @@ def run_reference_arm(args):
     line = {
         "impl": "reference", "metric": METRIC, "value": mean, "unit": UNIT, "n_gpus": args.gpus,
         "steps": len(times), "warmup": max(1, args.warmup),
-        "ms_per_step": 1e3 * statistics.mean(times), "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": 1e3 * statistics.mean(times), "higher_is_better": True,
+        "scaling": args.scaling or "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD["name"], "sample": sample},
         "cpu_baseline": {"value": mean, "unit": UNIT, "cores": threads, "kind": "port",
@@ -191,11 +198,62 @@ def make_device_inputs(rows, T, seed, device):
     return a, x, G
 
 
+def _cuda_events(n):
+    import torch
+    return [torch.cuda.Event(enable_timing=True) for _ in range(n)]
+
+
+def time_rows_workload(rows, T, seed, device, steps, warmup, barrier):
+    """Device-timed fwd+bwd over `rows` x T bf16 on this rank.
+
+    Returns (ms_per_step, fwd_ms, bwd_ms, tensors).  The headline loop holds nothing but the two
+    launches per step between one pair of events; the per-kernel split comes from a second, short
+    loop with an event after every launch (events between launches cost a few microseconds each,
+    which matters at 40-60 us kernels)."""
+    import torch
+
+    from fm_b200 import fm_scan_backward_ex, fm_scan_forward
+
+    a, x, G = make_device_inputs(rows, T, seed, device)
+    D = WORKLOAD["D"]
+    a3, x3, G3 = (t.view(-1, D, T) if rows % D == 0 else t.view(1, rows, T) for t in (a, x, G))
+    h, ga, gx = torch.empty_like(a3), torch.empty_like(a3), torch.empty_like(a3)
+
+    def step():
+        fm_scan_forward(a3, x3, None, h)
+        fm_scan_backward_ex(a3, G3, None, gx, h, ga, None, None)
+
+    for _ in range(max(3, warmup)):
+        step()
+    barrier()
+    start, end = _cuda_events(2)
+    barrier()
+    start.record()
+    for _ in range(steps):
+        step()
+    end.record()
+    barrier()
+    ms_per_step = start.elapsed_time(end) / steps
+
+    n_split = max(5, min(steps, 50))
+    ev = [_cuda_events(3) for _ in range(n_split)]
+    for k in range(n_split):
+        ev[k][0].record()
+        fm_scan_forward(a3, x3, None, h)
+        ev[k][1].record()
+        fm_scan_backward_ex(a3, G3, None, gx, h, ga, None, None)
+        ev[k][2].record()
+    torch.cuda.synchronize()
+    fwd_ms = statistics.median(e[0].elapsed_time(e[1]) for e in ev)
+    bwd_ms = statistics.median(e[1].elapsed_time(e[2]) for e in ev)
+    return ms_per_step, fwd_ms, bwd_ms, (a3, x3, G3)
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
 
-    from fm_b200 import capi, fm_scan_backward_ex, fm_scan_forward
+    from fm_b200 import capi
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -209,80 +267,73 @@ def run_ours(args):
     capi.lib()  # fail loudly if the CUDA library is missing
 
     B, D, T = WORKLOAD["B"], WORKLOAD["D"], WORKLOAD["T"]
-    total_rows = B * D
-    if args.rows > 0:
-        total_rows = args.rows
-    rows = total_rows // world if args.scaling == "strong" else total_rows
+    total_rows = args.rows if args.rows > 0 else B * D
+    scaling = args.scaling or "strong"  # at N = 1 the two modes are the same run
+    rows = total_rows // world if scaling == "strong" else total_rows
     global_rows = rows * world
-    a, x, G = make_device_inputs(rows, T, 1003 + rank, device)
-    a3, x3, G3 = (t.view(-1, D, T) if rows % D == 0 else t.view(1, rows, T) for t in (a, x, G))
-    h = torch.empty_like(a3)
-    ga = torch.empty_like(a3)
-    gx = torch.empty_like(a3)
     n_local = rows * T
-
-    def step():
-        fm_scan_forward(a3, x3, None, h)
-        fm_scan_backward_ex(a3, G3, None, gx, h, ga, None, None)
+    K = args.steps
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(3, args.warmup)):
-        step()
-    barrier()
+    def max_over_ranks(values):
+        if world == 1:
+            return [float(v) for v in values]
+        t = torch.tensor(values, device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return [float(v) for v in t.tolist()]
 
-    K = args.steps
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(physical_gpu_index(local_rank)) as clocks:
-        barrier()
-        start.record()
-        for k in range(K):
-            ev[k][0].record()
-            fm_scan_forward(a3, x3, None, h)
-            ev[k][1].record()
-            fm_scan_backward_ex(a3, G3, None, gx, h, ga, None, None)
-            ev[k][2].record()
-        end.record()
-        barrier()
-    total_ms = start.elapsed_time(end)
-    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
-    bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+        ms_per_step, fwd_ms, bwd_ms, tensors = time_rows_workload(rows, T, 1003 + rank, device, K,
+                                                                  args.warmup, barrier)
 
     # end to end through host buffers
     if args.no_e2e:
-        e2e = {"ms": float("nan"), "h2d": 0, "d2h": 0, "steps": 0, "path": "skipped (--no-e2e)"}
+        e2e = {"ms": float("nan"), "copy_only_ms": float("nan"), "h2d": 0, "d2h": 0, "steps": 0,
+               "launches_per_step": 0, "path": "skipped (--no-e2e)"}
     else:
-        e2e = run_e2e(args, a3, x3, G3, device, barrier)
+        e2e = run_e2e(args, *tensors, device, barrier)
+    del tensors
+    ms_per_step, fwd_ms, bwd_ms, e2e_ms, copy_ms = max_over_ranks(
+        [ms_per_step, fwd_ms, bwd_ms, e2e["ms"], e2e["copy_only_ms"]])
 
-    if world > 1:
-        t = torch.tensor([total_ms, fwd_ms, bwd_ms, e2e["ms"]], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms, fwd_ms, bwd_ms, e2e_ms = (float(v) for v in t.tolist())
-    else:
-        e2e_ms = e2e["ms"]
+    # the other scaling mode, as an extra figure of the same line (N > 1 only; identical at N = 1)
+    other = None
+    if world > 1 and not args.no_extras:
+        o_rows = total_rows if scaling == "strong" else total_rows // world
+        o_ms, _, _, o_t = time_rows_workload(o_rows, T, 1003 + rank, device, max(5, min(K, 50)), 3, barrier)
+        del o_t
+        (o_ms,) = max_over_ranks([o_ms])
+        other = {"rows_per_gpu": o_rows, "ms_per_step": o_ms, "value": o_rows * world * T / (o_ms * 1e-3),
+                 "unit": UNIT}
+    torch.cuda.empty_cache()
+
+    time_split = None
+    if not args.no_extras and args.rows == 0:
+        time_split = measure_time_split(args, world, rank, device, barrier, max_over_ranks)
+        torch.cuda.empty_cache()
 
     if rank == 0:
         s = 2  # bytes per stored element
-        ms_per_step = total_ms / K
         value = global_rows * T / (ms_per_step * 1e-3)
         peak, peak_kind = measured_peak()
         bwd_gbs = 5 * s * n_local / (bwd_ms * 1e-3) / 1e9
         fwd_gbs = 3 * s * n_local / (fwd_ms * 1e-3) / 1e9
-        both_gbs = 8 * s * n_local / ((fwd_ms + bwd_ms) * 1e-3) / 1e9
+        both_gbs = 8 * s * n_local / (ms_per_step * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K,
             "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD["name"], "rows_per_gpu": rows, "T": T,
+            "scaling": scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD["name"], "rows_per_gpu": rows, "global_rows": global_rows, "T": T,
                        "storage": "bf16", "accumulate": "f32",
                        "gates": "a = 1 - 10^U(-4,-1) rounded to bf16; x, G ~ N(0,1)",
-                       "l2": "inputs larger than L2 (each tensor %d MiB per GPU), no flush" %
+                       "l2": "inputs larger than L2 (six tensors of %d MiB per GPU touched per step), no flush" %
                              (n_local * s >> 20),
-                       "sharding": "rows over ranks, no collective"},
+                       "sharding": ("the fixed %d rows split over the ranks" % total_rows if scaling == "strong"
+                                    else "%d rows on every rank" % total_rows) + ", no collective"},
             "gpu_launches": 2 * K,
             "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
             "fwd_elements_per_s": global_rows * T / (fwd_ms * 1e-3),
@@ -296,12 +347,21 @@ def run_ours(args):
                                  "frac": fwd_gbs / peak, "frac_of_nominal_8TBs": fwd_gbs / NOMINAL_HBM_GBS,
                                  "algorithmic_bytes_per_launch": 3 * s * n_local},
             "roofline_fwd_bwd": {"achieved": both_gbs, "frac": both_gbs / peak,
-                                 "frac_of_nominal_8TBs": both_gbs / NOMINAL_HBM_GBS},
+                                 "frac_of_nominal_8TBs": both_gbs / NOMINAL_HBM_GBS,
+                                 "note": "8*s*N per step over ms_per_step (launch gaps included)"},
             "clocks": clocks.summary(),
             "e2e": {"value": global_rows * T / (e2e_ms * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
-                    "ms_per_step": e2e_ms, "steps": e2e["steps"], "path": e2e["path"]},
+                    "ms_per_step": e2e_ms, "steps": e2e["steps"], "path": e2e["path"],
+                    "copy_only_ms": copy_ms,
+                    "frac_of_copy_only": (copy_ms / e2e_ms) if e2e_ms == e2e_ms and e2e_ms > 0 else None,
+                    "copy_only": "the same pipeline with the kernels skipped: H2D and D2H of the same bytes "
+                                 "overlapped on the same streams, max over ranks"},
         }
+        if other is not None:
+            line["weak_scaling" if scaling == "strong" else "strong_scaling"] = other
+        if time_split is not None:
+            line["time_split"] = time_split
         if world == 1 and not args.no_cpu_baseline:
             best, mean, threads, times = cpu_port_throughput(CPU_SAMPLE_ROWS, T, repeats=5)
             line["cpu_baseline"] = {
@@ -311,9 +371,204 @@ def run_ours(args):
                 "best": best, "host_cpus": os.cpu_count(),
                 "torch_loop_elements_per_s": torch_loop_throughput(64, T),
                 "torch_loop_sample": f"64 rows x T={T}, one fwd+autograd-bwd pass of the time-step loop"}
+        if world == 1 and not args.no_extras and args.rows == 0:
+            line["reference_cuda"] = reference_cuda_figures(device, K)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------ long sequence, split along T
+C4_ROWS, C4_T = 4096, 262144
+C4_CHECK_ROWS = [0, 1, 2, 3, 1023, 1024, 2047, 2048, 2049, 3071, 3072, 4092, 4093, 4094, 4095, 777]
+
+
+def measure_time_split(args, world, rank, device, barrier, max_over_ranks):
+    """(B,D,T) = (1,4096,262144) fp32, gates sigmoid(N(0,1)+3): rank k owns time block k of every row;
+    at N = 1 the plain operator scans the whole rows.  Timed (fwd+bwd, CUDA events, max over ranks)
+    and checked on 16 rows over the FULL length against the C oracle run in double."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from fm_b200 import fm_scan
+    from fm_b200.time_split import fm_scan_time_split
+
+    B, D, T = 1, C4_ROWS, C4_T
+    Tk = T // world
+    gen = torch.Generator(device=device).manual_seed(1004 + rank)
+    a = torch.sigmoid(torch.randn(B, D, Tk, device=device, generator=gen) + 3.0).requires_grad_(True)
+    x = torch.randn(B, D, Tk, device=device, generator=gen).requires_grad_(True)
+    G = torch.randn(B, D, Tk, device=device, generator=gen)
+
+    exchange, transport = None, "none (one GPU, rows scanned whole)"
+    if world > 1:
+        transport = "NCCL all-gather of (P,S) fp32 carries, once per direction"
+        if args.exchange == "peer":
+            try:
+                from fm_b200.peer_exchange import PeerCarryExchange
+                exchange = PeerCarryExchange(B * D)
+                transport = "peer stores + flags in symmetric memory, fold on arrival"
+            except Exception as e:  # symmetric memory unavailable: keep the collective
+                transport += " (peer exchange unavailable: %s)" % type(e).__name__
+
+    def step():
+        h = fm_scan_time_split(a, x, exchange=exchange) if world > 1 else fm_scan(a, x)
+        ga, gx = torch.autograd.grad(h, (a, x), G)
+        return h, ga, gx
+
+    steps = max(3, min(args.steps, 20))
+    for _ in range(3):
+        out = step()
+    barrier()
+    start, end = _cuda_events(2)
+    barrier()
+    start.record()
+    for _ in range(steps):
+        out = step()
+    end.record()
+    barrier()
+    (ms,) = max_over_ranks([start.elapsed_time(end) / steps])
+    if exchange is not None:
+        exchange.check()
+
+    # parity: the check rows of every block travel to rank 0 (full T), oracle in double there
+    idx = torch.tensor(C4_CHECK_ROWS, device=device)
+    mine = torch.stack([t.detach()[0].index_select(0, idx) for t in (a, x, G, *out)])   # (6, 16, Tk)
+    del out
+    if world > 1:
+        allb = torch.empty((world,) + tuple(mine.shape), device=device, dtype=mine.dtype)
+        dist.all_gather_into_tensor(allb, mine.contiguous())
+        full = torch.cat([allb[k] for k in range(world)], dim=-1)
+    else:
+        full = mine
+    result = None
+    if rank == 0:
+        from oracle import c_oracle as oc
+        a_, x_, G_, h_, ga_, gx_ = (full[i].cpu().numpy() for i in range(6))
+        f64 = np.float64
+        h64 = oc.plain_forward(a_.astype(f64), x_.astype(f64), dtype=f64)
+        ga64, gx64, _ = oc.plain_backward(a_.astype(f64), h64, G_.astype(f64), dtype=f64)
+        h32 = oc.plain_forward(a_, x_)                      # the reference's own fp32 arithmetic
+        ga32, gx32, _ = oc.plain_backward(a_, h32, G_)
+        rtol, atol = 1e-5, 1e-6
+        checks = {}
+        worst = 0.0
+        for name, got, ref32, ref64 in (("states", h_, h32, h64), ("grad_gates", ga_, ga32, ga64),
+                                        ("grad_tokens", gx_, gx32, gx64)):
+            scaled = atol * max(1.0, float(np.abs(ref64).max())) + rtol * np.abs(ref64)
+            plain = atol + rtol * np.abs(ref64)
+            err, err32 = np.abs(got - ref64), np.abs(ref32 - ref64)
+            ratio = float((err / scaled).max())
+            worst = max(worst, ratio)
+            checks[name] = {"max_err_over_tol": ratio, "max_abs_ref": float(np.abs(ref64).max()),
+                            "exceed_unscaled_kernel": int((err > plain).sum()),
+                            "exceed_unscaled_reference_fp32": int((err32 > plain).sum()),
+                            "elements": int(err.size)}
+        n = B * D * T
+        peak, kind = measured_peak()
+        result = {
+            "workload": "scan fwd+bwd (B,D,T)=(1,%d,%d) fp32, T split in %d blocks" % (D, T, world),
+            "n_gpus": world, "ms_per_step": ms, "steps": steps, "value": n / (ms * 1e-3), "unit": UNIT,
+            "transport": transport,
+            "algorithmic_GBs_per_gpu": 8 * 4 * n / world / (ms * 1e-3) / 1e9, "peak": peak, "peak_kind": kind,
+            "max_err_over_tol": worst,
+            "tolerance": "rtol 1e-5, atol 1e-6 * max(1, max|ref|) against the oracle in double; "
+                         "exceed_unscaled_* count elements beyond rtol 1e-5 / atol 1e-6 unscaled, for the kernel "
+                         "and for the reference's own fp32 arithmetic (sequential loop)",
+            "checked": "%d rows incl. first and last, full T=%d (%d elements per tensor)" % (
+                len(C4_CHECK_ROWS), T, len(C4_CHECK_ROWS) * T),
+            "checks": checks,
+        }
+    return result
+
+
+# ------------------------------------------------------------------ the reference's own CUDA op
+def load_reference_cuda():
+    """Import the reference's fm/scan/fm_scan.py from baseline/_ref (baseline/make_ref.py put it there).
+
+    The module compiles its kernel at import through torch's load_inline.  When baseline/_ref holds
+    the extension already built from those same sources (make_ref.py --prebuild), load_inline is
+    answered with that build instead of compiling for minutes; everything else -- the kernel, its
+    flags, the autograd class, fm_scan() -- is the reference's own, unmodified."""
+    import importlib.util
+
+    import torch.utils.cpp_extension as ce
+
+    ref_root = ROOT / "baseline" / "_ref"
+    if not (ref_root / "fm" / "scan" / "fm_scan.py").exists():
+        raise FileNotFoundError("baseline/_ref is absent (python baseline/make_ref.py --prebuild)")
+    prebuilt = ref_root / "torch_extensions" / "fm_scan" / "fm_scan.so"
+    real = ce.load_inline
+    if prebuilt.exists():
+        def load_prebuilt(name, *a, **k):
+            spec = importlib.util.spec_from_file_location(name, str(prebuilt))
+            mod = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(mod)
+            return mod
+        ce.load_inline = load_prebuilt
+    else:
+        os.environ.setdefault("TORCH_EXTENSIONS_DIR", str(ref_root / "torch_extensions"))
+    try:
+        sys.path.insert(0, str(ref_root))
+        import fm.scan.fm_scan as ref
+    finally:
+        ce.load_inline = real
+        sys.path.remove(str(ref_root))
+    return ref, ("prebuilt extension" if prebuilt.exists() else "JIT build")
+
+
+def reference_cuda_figures(device, steps):
+    """fwd+bwd of the reference's CUDA operator through its public fm_scan() on this GPU: the
+    headline workload through the M = D = 1 fold (32768 rows -> B = 32768, bf16) and its own demo
+    shape (1, 32, 2048, 8192) bf16.  Any failure is reported as `unavailable`, never retried."""
+    import torch
+    try:
+        ref, how = load_reference_cuda()
+    except Exception as e:
+        return {"unavailable": "%s: %s" % (type(e).__name__, str(e)[:200])}
+    out = {"build": how, "api": "fm.scan.fm_scan.fm_scan + autograd (its two torch sums included)"}
+    try:
+        steps = max(3, min(steps, 20))
+
+        def timed(g, x, G):
+            g.requires_grad_(True)
+            x.requires_grad_(True)
+
+            def one():
+                h = ref.fm_scan(g, x)
+                return torch.autograd.grad(h, (g, x), G)
+
+            for _ in range(3):
+                one()
+            torch.cuda.synchronize()
+            ev = [_cuda_events(2) for _ in range(steps)]
+            for e in ev:
+                e[0].record()
+                one()
+                e[1].record()
+            torch.cuda.synchronize()
+            return statistics.median(e[0].elapsed_time(e[1]) for e in ev)
+
+        T = WORKLOAD["T"]
+        rows = WORKLOAD["B"] * WORKLOAD["D"]
+        a, x, G = make_device_inputs(rows, T, 1003, device)
+        ms = timed(a.view(rows, 1, T), x.view(rows, 1, T), G.view(rows, 1, 1, T))
+        out["headline_via_fold"] = {"shape": "(B,M,D,L)=(%d,1,1,%d) bf16" % (rows, T), "ms_per_step": ms,
+                                    "elements_per_s": rows * T / (ms * 1e-3)}
+        del a, x, G
+        torch.cuda.empty_cache()
+        B, M, D, L = 1, 32, 2048, 8192
+        gen = torch.Generator(device=device).manual_seed(1070)
+        g = (0.9 + 0.1 * torch.rand(B, M, L, device=device, generator=gen)).to(torch.bfloat16)
+        x = torch.randn(B, D, L, device=device, generator=gen).to(torch.bfloat16)
+        G = torch.randn(B, M, D, L, device=device, generator=gen).to(torch.bfloat16)
+        ms = timed(g, x, G)
+        out["demo_shape"] = {"shape": "(B,M,D,L)=(1,32,2048,8192) bf16", "ms_per_step": ms,
+                             "output_elements_per_s": B * M * D * L / (ms * 1e-3)}
+    except Exception as e:
+        out["unavailable"] = "%s: %s" % (type(e).__name__, str(e)[:200])
+    return out
 
 
 def run_time_split(args):
@@ -570,7 +825,8 @@ def run_e2e(args, a3, x3, G3, device, barrier):
 
     Per step, inside the timed region: the three inputs go host -> device, forward and backward
     run, the three results come device -> host (all of them: the host caller ends up with what
-    the reference's CPU scan would have left in host memory).
+    the reference's CPU scan would have left in host memory).  `copy_only_ms` is the same
+    pipeline with the kernels skipped -- the ceiling the copies alone set on this box.
     """
     import torch
 
@@ -585,21 +841,23 @@ def run_e2e(args, a3, x3, G3, device, barrier):
     pipe = HostPipeline(max(1, rows // 32), a3.shape[-1], a3.dtype, device)
     torch.cuda.synchronize()
 
-    def step():
-        pipe.forward_backward(host_in[0], host_in[1], host_in[2], host_out[0], host_out[1], host_out[2])
+    def timed(fn):
+        fn()
+        barrier()
+        start, end = _cuda_events(2)
+        start.record()
+        for _ in range(steps):
+            fn()
+        end.record()
+        barrier()
+        return start.elapsed_time(end) / steps
 
-    step()
-    barrier()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(steps):
-        step()
-    end.record()
-    barrier()
+    ms = timed(lambda: pipe.forward_backward(*host_in, *host_out))
+    copy_ms = timed(lambda: pipe.copy_only(*host_in, *host_out))
     pipe.close()
     nbytes = a3.numel() * a3.element_size()
     blocks = 32 if rows >= 2048 else (8 if rows >= 8 else 1)
-    return {"ms": start.elapsed_time(end) / steps, "h2d": 3 * nbytes, "d2h": 3 * nbytes,
+    return {"ms": ms, "copy_only_ms": copy_ms, "h2d": 3 * nbytes, "d2h": 3 * nbytes,
             "steps": steps, "launches_per_step": 2 * blocks,
             "path": "fms_plain_forward_backward_host: pinned host -> H2D | kernels | D2H overlapped in "
                     "%d row blocks -> pinned host" % blocks}
@@ -611,13 +869,17 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
+    ap.add_argument("--scaling", choices=["weak", "strong"], default=None,
+                    help="N > 1: strong (default) splits the fixed 32768 rows over the ranks; weak gives "
+                         "every rank all 32768")
     ap.add_argument("--workload", choices=["c3", "c4", "fm", "btd"], default="c3",
                     help="c3: the headline row-sharded workload; c4: the long sequence split along T; "
                          "fm: the reference's (B,M,L)x(B,D,L)->(B,M,D,L) operator at its demo shape; "
                          "btd: the plain scan on channel-last (B,T,D) tensors")
-    ap.add_argument("--exchange", choices=["nccl", "peer"], default="nccl",
-                    help="carry transport of --workload c4")
+    ap.add_argument("--exchange", choices=["nccl", "peer"], default="peer",
+                    help="carry transport of the long sequence split along T")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="headline only: skip time_split, the other scaling mode and reference_cuda")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling aid)")

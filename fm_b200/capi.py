@@ -62,6 +62,8 @@ def lib() -> ctypes.CDLL:
         L.fms_status_string.restype = ctypes.c_char_p
         L.fms_status_string.argtypes = [_I]
         L.fms_last_cuda_error.restype = _I
+        L.fms_tune_reload.restype = None
+        L.fms_tune_reload.argtypes = []
         L.fms_plain_split_segments.restype = _I64
         L.fms_plain_split_segments.argtypes = [_I64, _I64, _I]
         L.fms_plain_split_workspace_bytes.restype = ctypes.c_size_t

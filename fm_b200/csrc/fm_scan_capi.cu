@@ -40,12 +40,42 @@ inline bool sizes_ok(int64_t rows, int64_t T) {
     return rows <= (INT64_MAX / 8) / T;
 }
 
-// Tuning knobs read from the environment on every launch (FMS_TUNE_*): warps per row K, tiles
-// per warp and step U, persistence, a cap on the grid.  Unset, the choices below apply, which
+// Tuning knobs (FMS_TUNE_* environment variables): warps per row K, tiles per warp and step U,
+// the persistent walk, a cap on the grid.  The environment is read ONCE, at the first launch of
+// the process (getenv on every launch would sit on the host critical path of 30-60 us kernels and
+// race with setenv); fms_tune_reload() reads it again.  Unset, the choices made below apply, which
 // are the measured best on B200.
-int tune_value(const char *name, int dflt) {
-    const char *s = std::getenv(name);
-    return s ? std::atoi(s) : dflt;
+struct Tune {
+    int fwd_k = 0, bwd_k = 0, fwd_u = 0, bwd_u = 0;  // 0 = choose from the shape
+    int max_ctas = 0x7fffffff;                       // test knob: forces the multi-row walk
+    int persist = -1;                                // -1 = choose from the shape, 0 = off, 1 = on
+    int fm_pd = 4, fm_blocked = 1, btd_warps_per_sm = 32;
+};
+
+Tune g_tune;
+std::once_flag g_tune_once;
+
+void load_tune() {
+    auto get = [](const char *name, int dflt) {
+        const char *s = std::getenv(name);
+        return s ? std::atoi(s) : dflt;
+    };
+    Tune t;
+    t.fwd_k = get("FMS_TUNE_FWD_K", 0);
+    t.bwd_k = get("FMS_TUNE_BWD_K", 0);
+    t.fwd_u = get("FMS_TUNE_FWD_U", 0);
+    t.bwd_u = get("FMS_TUNE_BWD_U", 0);
+    t.max_ctas = std::max(1, get("FMS_TUNE_MAX_CTAS", 0x7fffffff));
+    t.persist = get("FMS_TUNE_PERSIST", -1);
+    t.fm_pd = get("FMS_TUNE_FM_PD", 4);
+    t.fm_blocked = get("FMS_TUNE_FM_BLOCKED", 1);
+    t.btd_warps_per_sm = std::max(1, get("FMS_TUNE_BTD_WARPS_PER_SM", 32));
+    g_tune = t;
+}
+
+inline const Tune &tune() {
+    std::call_once(g_tune_once, load_tune);
+    return g_tune;
 }
 
 struct Problem {
@@ -88,16 +118,15 @@ int copy_or_zero(const float *src, float *dst, int64_t n, float fill, cudaStream
     return check_launch();
 }
 
-// Grid of a persistent launch: no more CTAs than the GPU holds at once (each then walks several
-// units and prefetches across their boundaries), never more than there is work.  Measured on
-// B200 the hardware block scheduler with one unit per CTA is 1-5 % faster than this static
-// walk for every benchmark shape, so persistence is off unless FMS_TUNE_PERSIST=1 asks for it
-// (the kernels support both; the multi-unit walk is covered by the tests).
+// Number of SMs of the current device, asked once (every GPU of a box is alike); 148 on B200.
 int sm_count() {
-    int dev = 0, n = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
-    return n;
+    static const int count = []() {
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+        return n;
+    }();
+    return count;
 }
 
 template <typename Kernel>
@@ -106,6 +135,25 @@ int64_t resident_ctas(Kernel kernel, int threads) {
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0) != cudaSuccess || per_sm <= 0)
         per_sm = 1;
     return static_cast<int64_t>(per_sm) * sm_count();
+}
+
+// Grid of a persistent launch.  Every CTA walks the same number q of units, q being the fewest
+// whole passes over the work that the resident capacity allows: all CTAs are then resident from
+// the first cycle, carry the load pipeline across their unit boundaries, and finish together.
+// One unit per CTA under the hardware block scheduler instead leaves the last, partly filled
+// wave (2.77 and 4.61 waves for 4096 rows of 16 KB forward and backward) running at a fraction
+// of the bandwidth.
+inline int64_t balanced_grid(int64_t ctas, int64_t resident) {
+    const int64_t q = (ctas + resident - 1) / resident;
+    return (ctas + q - 1) / q;
+}
+
+// Whether a launch of `ctas` one-unit CTAs walks persistently instead.  FMS_TUNE_PERSIST forces
+// either answer.
+inline bool use_persistent(int64_t ctas, int64_t resident) {
+    const int forced = tune().persist;
+    if (forced >= 0) return forced != 0;
+    return ctas > resident;
 }
 
 // How a launch is cut into scan units and how many warps share a unit.
@@ -117,8 +165,7 @@ struct Split {
 // Warps per unit.  A CTA of K warps per row reads K*U*512 contiguous bytes per tensor per step
 // and lets the block scheduler balance at a finer grain (all rows have the same length, so whole
 // waves finish together); each row then takes fewer loop iterations to prefetch across.
-int choose_coop(int64_t units, int64_t T, size_t es, const char *env_name) {
-    const int forced = tune_value(env_name, 0);
+int choose_coop(int64_t units, int64_t T, size_t es, int forced) {
     if (forced == 1 || forced == 2 || forced == 4 || forced == 8) return forced;
     // Measured on B200 (CUDA events, fwd+bwd GB/s): 16 KB rows x 32768 rows: K=2 6306, K=4 6182,
     // K=1 5797; 16 KB rows x 8192 rows: K=4 6026, K=2 5761; 128 KB rows x 4096 rows: K=8 6284,
@@ -131,8 +178,7 @@ int choose_coop(int64_t units, int64_t T, size_t es, const char *env_name) {
 }
 
 // Tiles per warp and step: 4 unless the row is too short to fill K*4 tiles.
-int choose_unroll(int64_t T, size_t es, int K, const char *env_name) {
-    const int forced = tune_value(env_name, 0);
+int choose_unroll(int64_t T, size_t es, int K, int forced) {
     if (forced == 1 || forced == 2 || forced == 4) return forced;
     const int64_t tiles = (T * static_cast<int64_t>(es) + 511) / 512;
     if (tiles >= 4 * K) return 4;
@@ -144,22 +190,22 @@ template <typename S, bool WRITE>
 int launch_forward(const Problem &pb, const Split &sp, const void *gates, const void *tokens,
                    const float *h0, void *states, float *h_last, float *P, cudaStream_t st) {
     const int64_t units = pb.rows * sp.nseg;
-    int K = sp.nseg > 1 ? 1 : choose_coop(units, pb.T, sizeof(S), "FMS_TUNE_FWD_K");
+    int K = sp.nseg > 1 ? 1 : choose_coop(units, pb.T, sizeof(S), tune().fwd_k);
     // masked path (measured on 2304 rows x 16385 fp16): one warp per row is fastest forward
-    if (!pb.aligned && tune_value("FMS_TUNE_FWD_K", 0) == 0) K = 1;
-    const int unroll = choose_unroll(pb.T, sizeof(S), K, "FMS_TUNE_FWD_U");
+    if (!pb.aligned && tune().fwd_k == 0) K = 1;
+    const int unroll = choose_unroll(pb.T, sizeof(S), K, tune().fwd_u);
     const int64_t ctas = K == 1 ? (units + fms::kWarpsPerCta - 1) / fms::kWarpsPerCta : units;
     if (ctas > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;
     const int64_t seg_len = sp.nseg == 1 ? pb.T : sp.seg_len;
-    const int64_t max_ctas = std::max(1, tune_value("FMS_TUNE_MAX_CTAS", 0x7fffffff));  // test knob
-    const bool persist = tune_value("FMS_TUNE_PERSIST", 0) != 0;
+    const int64_t max_ctas = tune().max_ctas;
 #define FMS_LAUNCH_FWD_S(G, UU, KK, SS)                                                            \
     do {                                                                                           \
         auto kern = fms::plain_forward_kernel<S, G, UU, WRITE, KK, SS, false>;                            \
         int64_t nctas = ctas;                                                                      \
-        if (!(G) && !(SS) && persist) { /* persistent instantiation */                             \
+        if (!(G) && !(SS)) { /* instantiation that can walk several units */                       \
             static const int64_t resident = resident_ctas(kern, fms::Coop<KK>::kThreads);          \
-            nctas = std::min(ctas, std::min(resident, max_ctas));                                  \
+            if (use_persistent(ctas, resident)) nctas = balanced_grid(ctas, resident);             \
+            nctas = std::min(nctas, max_ctas);                                                     \
         }                                                                                          \
         kern<<<static_cast<unsigned>(nctas), fms::Coop<KK>::kThreads, 0, st>>>(                    \
             static_cast<const S *>(gates), static_cast<const S *>(tokens), h0,                     \
@@ -194,24 +240,24 @@ int launch_backward(const Problem &pb, const Split &sp, const void *gates, const
                     const void *grad_states, const float *h0, const float *carry_in, void *grad_gates,
                     void *grad_tokens, float *grad_h0, float *P, cudaStream_t st) {
     const int64_t units = pb.rows * sp.nseg;
-    int K = sp.nseg > 1 ? 1 : choose_coop(units, pb.T, sizeof(S), "FMS_TUNE_BWD_K");
+    int K = sp.nseg > 1 ? 1 : choose_coop(units, pb.T, sizeof(S), tune().bwd_k);
     // masked path (same measurement): two warps per row are fastest backward
-    if (!pb.aligned && tune_value("FMS_TUNE_BWD_K", 0) == 0) K = std::min(K, 2);
+    if (!pb.aligned && tune().bwd_k == 0) K = std::min(K, 2);
     // one warp per row: 2 tiles per step (4 costs occupancy: 141+ registers for three inputs)
-    const int unroll = K == 1 ? std::min(2, choose_unroll(pb.T, sizeof(S), K, "FMS_TUNE_BWD_U"))
-                              : choose_unroll(pb.T, sizeof(S), K, "FMS_TUNE_BWD_U");
+    const int unroll = K == 1 ? std::min(2, choose_unroll(pb.T, sizeof(S), K, tune().bwd_u))
+                              : choose_unroll(pb.T, sizeof(S), K, tune().bwd_u);
     const int64_t ctas = K == 1 ? (units + fms::kWarpsPerCta - 1) / fms::kWarpsPerCta : units;
     if (ctas > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;
     const int64_t seg_len = sp.nseg == 1 ? pb.T : sp.seg_len;
-    const int64_t max_ctas = std::max(1, tune_value("FMS_TUNE_MAX_CTAS", 0x7fffffff));  // test knob
-    const bool persist = tune_value("FMS_TUNE_PERSIST", 0) != 0;
+    const int64_t max_ctas = tune().max_ctas;
 #define FMS_LAUNCH_BWD_S(G, UU, KK, SS)                                                            \
     do {                                                                                           \
         auto kern = fms::plain_backward_kernel<S, G, UU, WRITE, KK, SS, false>;                           \
         int64_t nctas = ctas;                                                                      \
-        if (!(G) && !(SS) && persist) {                                                            \
+        if (!(G) && !(SS)) {                                                                       \
             static const int64_t resident = resident_ctas(kern, fms::Coop<KK>::kThreads);          \
-            nctas = std::min(ctas, std::min(resident, max_ctas));                                  \
+            if (use_persistent(ctas, resident)) nctas = balanced_grid(ctas, resident);             \
+            nctas = std::min(nctas, max_ctas);                                                     \
         }                                                                                          \
         kern<<<static_cast<unsigned>(nctas), fms::Coop<KK>::kThreads, 0, st>>>(                    \
             static_cast<const S *>(gates), static_cast<const S *>(states),                         \
@@ -263,7 +309,12 @@ int launch_combine(const float *P, const float *S, const float *carry0, float *c
 
 }  // namespace
 
-FMS_EXPORT int fms_version(void) { return 100; }
+FMS_EXPORT int fms_version(void) { return 200; }
+
+FMS_EXPORT void fms_tune_reload(void) {
+    tune();  // make sure the one-time load has happened, then read the environment again
+    load_tune();
+}
 
 FMS_EXPORT const char *fms_status_string(int status) {
     switch (status) {
@@ -372,8 +423,8 @@ int make_fm_shape(FmShape &sh, int64_t B, int64_t M, int64_t D, int64_t L, int d
 template <typename S>
 int launch_fm_forward(const FmShape &sh, bool aligned, const void *gates, const void *tokens, const float *h0,
                       void *states, cudaStream_t st) {
-    const int K = choose_coop(sh.rows, sh.L, sizeof(S), "FMS_TUNE_FWD_K");
-    const int unroll = std::min(2, choose_unroll(sh.L, sizeof(S), K, "FMS_TUNE_FWD_U"));
+    const int K = choose_coop(sh.rows, sh.L, sizeof(S), tune().fwd_k);
+    const int unroll = std::min(2, choose_unroll(sh.L, sizeof(S), K, tune().fwd_u));
     const int64_t ctas = K == 1 ? (sh.rows + fms::kWarpsPerCta - 1) / fms::kWarpsPerCta : sh.rows;
     if (ctas > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;
 #define FMS_LAUNCH_FM_FWD(G, UU, KK)                                                               \
@@ -396,20 +447,24 @@ int launch_fm_forward(const FmShape &sh, bool aligned, const void *gates, const 
     return check_launch();
 }
 
+// full_gates / full_tokens non-null: store the per-row terms into (B,M,D,L) tensors instead of
+// accumulating the sums (acc_* are then unused).
 template <typename S>
 int launch_fm_backward(const FmShape &sh, bool aligned, const void *gates, const void *tokens,
                        const void *states, const void *grad_states, const float *h0, float *acc_gates,
-                       float *acc_tokens, float *grad_h0, cudaStream_t st) {
-    const int K = choose_coop(sh.rows, sh.L, sizeof(S), "FMS_TUNE_BWD_K");
-    const int unroll = std::min(2, choose_unroll(sh.L, sizeof(S), K, "FMS_TUNE_BWD_U"));
+                       float *acc_tokens, float *grad_h0, cudaStream_t st, void *full_gates = nullptr,
+                       void *full_tokens = nullptr) {
+    const int K = choose_coop(sh.rows, sh.L, sizeof(S), tune().bwd_k);
+    const int unroll = std::min(2, choose_unroll(sh.L, sizeof(S), K, tune().bwd_u));
     const int64_t ctas = K == 1 ? (sh.rows + fms::kWarpsPerCta - 1) / fms::kWarpsPerCta : sh.rows;
     if (ctas > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;
 #define FMS_LAUNCH_FM_BWD(G, UU, KK)                                                               \
     fms::plain_backward_kernel<S, G, UU, true, KK, false, true>                                    \
         <<<static_cast<unsigned>(ctas), fms::Coop<KK>::kThreads, 0, st>>>(                         \
             static_cast<const S *>(gates), static_cast<const S *>(states),                         \
-            static_cast<const S *>(grad_states), h0, nullptr, nullptr, nullptr, grad_h0, nullptr,  \
-            sh.rows, sh.L, 1, sh.L, static_cast<const S *>(tokens), acc_gates, acc_tokens, sh.M, sh.D)
+            static_cast<const S *>(grad_states), h0, nullptr, static_cast<S *>(full_gates),        \
+            static_cast<S *>(full_tokens), grad_h0, nullptr, sh.rows, sh.L, 1, sh.L,               \
+            static_cast<const S *>(tokens), acc_gates, acc_tokens, sh.M, sh.D)
 #define FMS_LAUNCH_FM_BWD_K(G, UU)                                                                 \
     switch (K) {                                                                                   \
         case 1: FMS_LAUNCH_FM_BWD(G, UU, 1); break;                                                \
@@ -448,7 +503,7 @@ int launch_fm_backward_blocked(const FmShape &sh, const void *gates, const void 
     const int64_t m_blocks = (sh.M + MC - 1) / MC, d_blocks = (sh.D + DC - 1) / DC;
     if (sh.B > 0x7fffffffLL / m_blocks || sh.B * m_blocks > 0x7fffffffLL / d_blocks) return FMS_ERR_BAD_SHAPE;
     const unsigned grid = static_cast<unsigned>(sh.B * m_blocks * d_blocks);
-    const int pd = tune_value("FMS_TUNE_FM_PD", 4);
+    const int pd = tune().fm_pd;
     // the shared-memory opt-in is per device, so it is (cheaply) repeated on every launch
     constexpr size_t smem = fms::fm_backward_blocked_smem<S, MC, DC>();
 #define FMS_LAUNCH_FM_BLOCKED(PDV)                                                                  \
@@ -506,7 +561,7 @@ FMS_EXPORT int fms_fm_forward(const void *gates, const void *tokens, const float
     bool aligned = false;
     if (int rc = fm_alignment(aligned, L, dtype, gates, tokens, static_cast<const void *>(states))) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (aligned && tune_value("FMS_TUNE_FM_BLOCKED", 1) != 0) {
+    if (aligned && tune().fm_blocked != 0) {
         FMS_DISPATCH_DTYPE(dtype, (launch_fm_forward_blocked<S>(sh, gates, tokens, h0, states, st)));
     }
     FMS_DISPATCH_DTYPE(dtype, (launch_fm_forward<S>(sh, aligned, gates, tokens, h0, states, st)));
@@ -529,9 +584,10 @@ FMS_EXPORT int fms_fm_backward(const void *gates, const void *tokens, const void
     const size_t es = elem_size(dtype);
     const size_t n_g = static_cast<size_t>(B) * M * L, n_x = static_cast<size_t>(B) * D * L;
     if (sh.rows == 0 || L == 0) {
-        // a sum over an empty axis is zero
+        // a sum over an empty axis is zero; with no positions nothing depends on h0 either
         if (grad_gates && n_g) if (int rc = record(cudaMemsetAsync(grad_gates, 0, n_g * es, st))) return rc;
         if (grad_tokens && n_x) if (int rc = record(cudaMemsetAsync(grad_tokens, 0, n_x * es, st))) return rc;
+        if (grad_h0 && sh.rows) return copy_or_zero(nullptr, grad_h0, sh.rows, 0.f, st);
         return FMS_OK;
     }
     bool aligned = false;
@@ -557,7 +613,7 @@ FMS_EXPORT int fms_fm_backward(const void *gates, const void *tokens, const void
     {
         // rows that share a gate or a token row are reduced inside a CTA before any global
         // atomic when everything is 16-byte aligned; the row-per-CTA kernel covers the rest
-        const bool blocked = aligned && tune_value("FMS_TUNE_FM_BLOCKED", 1) != 0;
+        const bool blocked = aligned && tune().fm_blocked != 0;
         auto pass = [&]() -> int {
             if (blocked) {
                 FMS_DISPATCH_DTYPE(dtype, (launch_fm_backward_blocked<S>(sh, gates, tokens, states, grad_states,
@@ -574,6 +630,23 @@ FMS_EXPORT int fms_fm_backward(const void *gates, const void *tokens, const void
         if (int rc = cast_g()) return rc;
     }
     FMS_DISPATCH_DTYPE(dtype, (launch_cast<S>(acc_x, grad_tokens, n_x, st)));
+}
+
+FMS_EXPORT int fms_fm_backward_unreduced(const void *gates, const void *tokens, const void *states,
+                                         const void *grad_states, const float *h0, void *grad_gates_full,
+                                         void *grad_tokens_full, float *grad_h0, int64_t B, int64_t M, int64_t D,
+                                         int64_t L, int dtype, fms_stream_t stream) {
+    FmShape sh;
+    if (int rc = make_fm_shape(sh, B, M, D, L, dtype)) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (sh.rows == 0) return FMS_OK;
+    if (L == 0) return copy_or_zero(nullptr, grad_h0, sh.rows, 0.f, st);
+    bool aligned = false;
+    if (int rc = fm_alignment(aligned, L, dtype, gates, tokens, states, grad_states,
+                              static_cast<const void *>(grad_gates_full), static_cast<const void *>(grad_tokens_full)))
+        return rc;
+    FMS_DISPATCH_DTYPE(dtype, (launch_fm_backward<S>(sh, aligned, gates, tokens, states, grad_states, h0, nullptr,
+                                                     nullptr, grad_h0, st, grad_gates_full, grad_tokens_full)));
 }
 
 // ------------------------------------------------------------------ FM layer read-out -------
@@ -667,7 +740,7 @@ int launch_fm_layer_backward(const FmShape &sh, const void *gates, const void *t
                              const float *h0, float *ws, void *grad_gates, void *grad_tokens, void *grad_weight,
                              float *grad_h0, cudaStream_t st) {
     constexpr int MC = 8, DC = 8;
-    const int pd = tune_value("FMS_TUNE_FM_PD", 4);
+    const int pd = tune().fm_pd;
     const int64_t m_blocks = (sh.M + MC - 1) / MC, d_blocks = (sh.D + DC - 1) / DC;
     if (sh.B > 0x7fffffffLL / m_blocks || sh.B * m_blocks > 0x7fffffffLL / d_blocks) return FMS_ERR_BAD_SHAPE;
     const unsigned grid = static_cast<unsigned>(sh.B * m_blocks * d_blocks);
@@ -782,8 +855,8 @@ bool make_btd_geom(fms::BtdGeom &g, int64_t B, int64_t T, int64_t D, int dtype) 
     g.D = D;
     g.dtiles = (D + 32 * E - 1) / (32 * E);
     // enough warps to fill the GPU, chunks of at least 16 steps
-    const int64_t target = std::max(1, tune_value("FMS_TUNE_BTD_WARPS_PER_SM", 32));
-    int64_t want = (148 * target + B * g.dtiles - 1) / (B * g.dtiles);
+    const int64_t target = tune().btd_warps_per_sm;
+    int64_t want = (sm_count() * target + B * g.dtiles - 1) / (B * g.dtiles);
     want = std::max<int64_t>(1, std::min<int64_t>(want, (T + 15) / 16));
     g.chunk = (T + want - 1) / want;
     g.nchunks = (T + g.chunk - 1) / g.chunk;
@@ -1030,10 +1103,21 @@ FMS_EXPORT int fms_plain_forward_split_static(const void *gates, const void *tok
     Problem pb;
     if (int rc = make_problem(pb, rows, T, dtype, gates, tokens, static_cast<const void *>(states)))
         return rc;
-    const SplitPlan plan = plan_split(rows, T);
+    SplitPlan plan = plan_split(rows, T);
     if (plan.nseg == 1)  // no scratch involved
         return fms_plain_forward(gates, tokens, h0, states, h_last, rows, T, dtype, stream);
-    if (plan.units > FMS_STATIC_SCRATCH_MAX_UNITS) return FMS_ERR_TOO_LARGE;
+    if (plan.units > FMS_STATIC_SCRATCH_MAX_UNITS) {
+        // The library's own plan aims a little above the array's capacity.  Re-plan inside it with
+        // fewer, longer segments; refuse only when not even two segments per row fit.
+        if (rows * 2 > FMS_STATIC_SCRATCH_MAX_UNITS) return FMS_ERR_TOO_LARGE;
+        const int64_t want = std::min<int64_t>(plan.nseg, FMS_STATIC_SCRATCH_MAX_UNITS / rows);
+        int64_t seg = (T + want - 1) / want;
+        seg = (seg + kSplitQuantum - 1) / kSplitQuantum * kSplitQuantum;
+        plan.nseg = (T + seg - 1) / seg;
+        plan.seg_len = seg;
+        plan.units = rows * plan.nseg;
+        if (plan.nseg < 2) return fms_plain_forward(gates, tokens, h0, states, h_last, rows, T, dtype, stream);
+    }
     float *scratch = nullptr;
     if (int rc = static_scratch_on_current_device(&scratch)) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -78,10 +78,12 @@ FMS_EXPORT int fms_pipeline_create(fms_pipeline **out, void *workspace, size_t w
 
 FMS_EXPORT int fms_pipeline_destroy(fms_pipeline *pipe) { return destroy(pipe); }
 
-FMS_EXPORT int fms_plain_forward_backward_host(fms_pipeline *p, const void *gates_h, const void *tokens_h,
-                                               const void *grad_states_h, void *states_h,
-                                               void *grad_gates_h, void *grad_tokens_h, int64_t rows,
-                                               int64_t T, int dtype, fms_stream_t stream) {
+namespace {
+
+// kernels = false: the copies and their ordering only (what the PCIe links allow on their own).
+int run_pipeline(fms_pipeline *p, const void *gates_h, const void *tokens_h, const void *grad_states_h,
+                 void *states_h, void *grad_gates_h, void *grad_tokens_h, int64_t rows, int64_t T, int dtype,
+                 fms_stream_t stream, bool kernels) {
     if (!p) return FMS_ERR_NULL_POINTER;
     if (!dtype_ok(dtype)) return FMS_ERR_BAD_DTYPE;
     if (rows < 0 || T < 0) return FMS_ERR_BAD_SHAPE;
@@ -128,12 +130,14 @@ FMS_EXPORT int fms_plain_forward_backward_host(fms_pipeline *p, const void *gate
         // kernels
         FMS_CUDA(cudaStreamWaitEvent(p->s_compute, p->in_ready[s], 0));
         if (b >= 2) FMS_CUDA(cudaStreamWaitEvent(p->s_compute, p->out_free[s], 0));
-        int rc = fms_plain_forward(in_buf[s][0], in_buf[s][1], nullptr, out_buf[s][0], nullptr, nr, T, dtype,
-                                   p->s_compute);
-        if (rc != FMS_OK) return rc;
-        rc = fms_plain_backward(in_buf[s][0], out_buf[s][0], in_buf[s][2], nullptr, nullptr, out_buf[s][1],
-                                out_buf[s][2], nullptr, nr, T, dtype, p->s_compute);
-        if (rc != FMS_OK) return rc;
+        if (kernels) {
+            int rc = fms_plain_forward(in_buf[s][0], in_buf[s][1], nullptr, out_buf[s][0], nullptr, nr, T, dtype,
+                                       p->s_compute);
+            if (rc != FMS_OK) return rc;
+            rc = fms_plain_backward(in_buf[s][0], out_buf[s][0], in_buf[s][2], nullptr, nullptr, out_buf[s][1],
+                                    out_buf[s][2], nullptr, nr, T, dtype, p->s_compute);
+            if (rc != FMS_OK) return rc;
+        }
         FMS_CUDA(cudaEventRecord(p->in_free[s], p->s_compute));
         FMS_CUDA(cudaEventRecord(p->out_ready[s], p->s_compute));
         // device -> host
@@ -149,4 +153,22 @@ FMS_EXPORT int fms_plain_forward_backward_host(fms_pipeline *p, const void *gate
     FMS_CUDA(cudaStreamWaitEvent(user, p->done_compute, 0));
     FMS_CUDA(cudaStreamWaitEvent(user, p->done_out, 0));
     return FMS_OK;
+}
+
+}  // namespace
+
+FMS_EXPORT int fms_plain_forward_backward_host(fms_pipeline *p, const void *gates_h, const void *tokens_h,
+                                               const void *grad_states_h, void *states_h,
+                                               void *grad_gates_h, void *grad_tokens_h, int64_t rows,
+                                               int64_t T, int dtype, fms_stream_t stream) {
+    return run_pipeline(p, gates_h, tokens_h, grad_states_h, states_h, grad_gates_h, grad_tokens_h, rows, T, dtype,
+                        stream, true);
+}
+
+FMS_EXPORT int fms_pipeline_copy_probe(fms_pipeline *p, const void *gates_h, const void *tokens_h,
+                                       const void *grad_states_h, void *states_h, void *grad_gates_h,
+                                       void *grad_tokens_h, int64_t rows, int64_t T, int dtype,
+                                       fms_stream_t stream) {
+    return run_pipeline(p, gates_h, tokens_h, grad_states_h, states_h, grad_gates_h, grad_tokens_h, rows, T, dtype,
+                        stream, false);
 }

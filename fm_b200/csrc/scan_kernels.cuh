@@ -465,7 +465,9 @@ plain_forward_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
 //     acc_gates [b,m,t] += (h_{t-1} - x_t) * delta_t     (sum over d; fm/scan/fm_scan.cuh:188-207
 //                                                          followed by fm/scan/fm_scan.py:76)
 //     acc_tokens[b,d,t] += (1 - g_t) * delta_t           (sum over m; fm_scan.cuh:184-185, fm_scan.py:78)
-// with vector reductions, so the reference's two (B,M,D,L) temporaries never exist.
+// with vector reductions, so the reference's two (B,M,D,L) temporaries never exist.  When the
+// caller does pass (B,M,D,L) outputs in grad_gates / grad_tokens (the unmodified reference caller,
+// fm/scan/fm_scan.py:70-73, which sums them itself), the per-row terms are stored there instead.
 template <typename S, bool GENERIC, int U, bool WRITE, int K, bool SEG, bool FM>
 __global__ void __launch_bounds__(Coop<K>::kThreads)
 plain_backward_kernel(const S *__restrict__ gates, const S *__restrict__ states,
@@ -500,8 +502,10 @@ plain_backward_kernel(const S *__restrict__ gates, const S *__restrict__ states,
     const int64_t vbase = row_phase<S, GENERIC>(gates + FMS_GOFF);
     const bool ph_g = !GENERIC || same_phase16(gates + FMS_GOFF, grad_states + off);
     const bool ph_h = !GENERIC || !WRITE || same_phase16(gates + FMS_GOFF, states + off);
-    const bool ph_ga = !GENERIC || !WRITE || FM || same_phase16(gates + off, grad_gates + off);
-    const bool ph_gx = !GENERIC || !WRITE || FM || same_phase16(gates + off, grad_tokens + off);
+    // FM mode stores per-row gradients only when the caller passed (B,M,D,L) outputs
+    const bool fm_unreduced = FM && grad_gates != nullptr;
+    const bool ph_ga = !GENERIC || !WRITE || (FM && !fm_unreduced) || same_phase16(gates + FMS_GOFF, grad_gates + off);
+    const bool ph_gx = !GENERIC || !WRITE || (FM && !fm_unreduced) || same_phase16(gates + FMS_GOFF, grad_tokens + off);
     const bool ph_x = !GENERIC || !FM || same_phase16(gates + FMS_GOFF, tokens_fm + toff_fm);
     const int64_t ngroups = (L - vbase + SUPER - 1) / SUPER;
     // this lane's first vector in the LAST group of a unit (the first one the reverse walk visits)
@@ -654,7 +658,7 @@ plain_backward_kernel(const S *__restrict__ gates, const S *__restrict__ states,
                         da[i] = delta * hp;
                     }
                 }
-                if constexpr (FM) {
+                if (FM && !fm_unreduced) {
                     red_vec<E, GENERIC>(acc_tokens + toff_fm, v + j * TILE, L, dx);
                     red_vec<E, GENERIC>(acc_gates + goff_fm, v + j * TILE, L, da);
                 } else {

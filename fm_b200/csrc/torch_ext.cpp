@@ -167,9 +167,11 @@ void fm_scan_backward_ex(const at::Tensor &gates, const at::Tensor &outGrad,
                  "fm_scan_backward");
 }
 
-// FM-mode backward with fused reductions: tokenGradOut (B,D,L), gateGradOut (B,M,L) -- the shapes
-// the reference's Python reaches only after materialising two (B,M,D,L) tensors and summing them
-// (fm/scan/fm_scan.py:70-78).  initial_state is the forward h0; grad_initial_state (B,M,D) fp32.
+// FM-mode backward.  tokenGradOut (B,D,L), gateGradOut (B,M,L): the reductions are fused -- the
+// shapes the reference's Python reaches only after materialising two (B,M,D,L) tensors and summing
+// them (fm/scan/fm_scan.py:70-78).  tokenGradOut, gateGradOut both (B,M,D,L): the reference's own
+// contract, per-row terms for a caller that sums them itself.  initial_state is the forward h0;
+// grad_initial_state (B,M,D) fp32.
 void fm_scan_backward_fm(const at::Tensor &gates, const at::Tensor &outGrad, const at::Tensor &tokenGradOut,
                          const at::Tensor &cached_output, const at::Tensor &input_tokens,
                          const at::Tensor &gateGradOut, const c10::optional<at::Tensor> &initial_state,
@@ -185,8 +187,16 @@ void fm_scan_backward_fm(const at::Tensor &gates, const at::Tensor &outGrad, con
     same(input_tokens, {B, D, L}, "input_tokens");
     same(cached_output, {B, M, D, L}, "cached_output");
     same(outGrad, {B, M, D, L}, "outGrad");
-    same(tokenGradOut, {B, D, L}, "tokenGradOut (fused reduction over M)");
-    same(gateGradOut, {B, M, L}, "gateGradOut (fused reduction over D)");
+    // (B,M,D,L) outputs: the reference's own contract -- per-row terms, summed by the caller
+    // (fm/scan/fm_scan.py:70-78); reduced shapes: the sums are fused into the kernel.
+    const bool unreduced = tokenGradOut.dim() == 4 && gateGradOut.dim() == 4;
+    if (unreduced) {
+        same(tokenGradOut, {B, M, D, L}, "tokenGradOut");
+        same(gateGradOut, {B, M, D, L}, "gateGradOut");
+    } else {
+        same(tokenGradOut, {B, D, L}, "tokenGradOut (fused reduction over M)");
+        same(gateGradOut, {B, M, L}, "gateGradOut (fused reduction over D)");
+    }
     const int dtype = dtype_tag(gates);
     const c10::cuda::CUDAGuard guard(gates.device());
     at::Tensor h0 = carry_f32(initial_state, B * M * D, gates, "initial_state");
@@ -196,6 +206,14 @@ void fm_scan_backward_fm(const at::Tensor &gates, const at::Tensor &outGrad, con
         TORCH_CHECK(g.is_cuda() && g.is_contiguous() && g.scalar_type() == at::kFloat && g.numel() == B * M * D,
                     "grad_initial_state must be a contiguous fp32 CUDA tensor of B*M*D elements");
         gh0 = g.data_ptr<float>();
+    }
+    if (unreduced) {
+        check_status(fms_fm_backward_unreduced(gates.data_ptr(), input_tokens.data_ptr(), cached_output.data_ptr(),
+                                               outGrad.data_ptr(), fptr(h0), gateGradOut.data_ptr(),
+                                               tokenGradOut.data_ptr(), gh0, B, M, D, L, dtype,
+                                               at::cuda::getCurrentCUDAStream().stream()),
+                     "fm_scan_backward");
+        return;
     }
     const size_t scratch = fms_fm_backward_workspace_bytes(B, M, D, L, dtype);
     at::Tensor ws;
@@ -373,7 +391,7 @@ void fm_scan_backward(const at::Tensor &gates, const at::Tensor &outGrad,
                       const c10::optional<at::Tensor> &firstPropGrad, const at::Tensor &tokenGradOut,
                       const at::Tensor &cached_output, const c10::optional<at::Tensor> &input_tokens,
                       const at::Tensor &gateGradOut) {
-    if (cached_output.dim() == gates.dim() + 1) {  // FM mode: outputs already reduced, h_{-1} = 0
+    if (cached_output.dim() == gates.dim() + 1) {  // FM mode, h_{-1} = 0; outputs reduced or (B,M,D,L)
         TORCH_CHECK(input_tokens.has_value() && input_tokens->defined(), "FM mode needs input_tokens");
         fm_scan_backward_fm(gates, outGrad, tokenGradOut, cached_output, *input_tokens, gateGradOut,
                             c10::nullopt, c10::nullopt);

@@ -28,6 +28,8 @@ def _bind():
         L.fms_pipeline_destroy.argtypes = [_P]
         L.fms_plain_forward_backward_host.restype = _I
         L.fms_plain_forward_backward_host.argtypes = [_P] * 7 + [_I64, _I64, _I, _P]
+        L.fms_pipeline_copy_probe.restype = _I
+        L.fms_pipeline_copy_probe.argtypes = [_P] * 7 + [_I64, _I64, _I, _P]
         L._fms_pipeline_bound = True
     return L
 
@@ -60,6 +62,14 @@ class HostPipeline:
         Asynchronous with respect to the host: the work is ordered on the current stream of the
         pipeline's device; synchronise that stream before reading the outputs.
         """
+        self._run("fms_plain_forward_backward_host", gates, tokens, grad_states, states, grad_gates, grad_tokens)
+
+    def copy_only(self, gates, tokens, grad_states, states, grad_gates, grad_tokens):
+        """The same copies in the same order with the kernels skipped (``fms_pipeline_copy_probe``):
+        what the host links alone allow.  The outputs receive stale staging data."""
+        self._run("fms_pipeline_copy_probe", gates, tokens, grad_states, states, grad_gates, grad_tokens)
+
+    def _run(self, entry, gates, tokens, grad_states, states, grad_gates, grad_tokens):
         ts = (gates, tokens, grad_states, states, grad_gates, grad_tokens)
         for t in ts:
             if t.is_cuda or not t.is_contiguous() or t.shape != gates.shape or t.dtype != gates.dtype:
@@ -67,11 +77,11 @@ class HostPipeline:
         T = gates.shape[-1]
         rows = gates.numel() // T if T else 0
         with torch.cuda.device(self.device):
-            rc = self._L.fms_plain_forward_backward_host(
+            rc = getattr(self._L, entry)(
                 self._handle, *(t.data_ptr() for t in ts), rows, T, capi.dtype_tag(gates.dtype),
                 torch.cuda.current_stream(self.device).cuda_stream)
         if rc != capi.FMS_OK:
-            raise capi.FmsError("fms_plain_forward_backward_host", rc, capi.status_string(rc),
+            raise capi.FmsError(entry, rc, capi.status_string(rc),
                                 int(self._L.fms_last_cuda_error()))
 
     def close(self):

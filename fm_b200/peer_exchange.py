@@ -8,6 +8,9 @@ the default path of ``fm_b200.time_split`` by two small kernels per direction.
 
 All ranks must create the object together and then perform the same sequence of forward and
 backward exchanges (the usual SPMD discipline): exchange numbers are counted per direction.
+Consumers acknowledge every fold and publishers wait for the acknowledgement of the exchange two
+before theirs, so any sequence is safe -- forward-only loops (inference) included: a fast rank
+runs at most one exchange ahead of the slowest rank that reads its carries.
 """
 from __future__ import annotations
 
@@ -29,9 +32,9 @@ def _bind():
         L.fms_peer_exchange_status_offset.restype = ctypes.c_size_t
         L.fms_peer_exchange_status_offset.argtypes = [_I64, _I]
         L.fms_peer_publish.restype = _I
-        L.fms_peer_publish.argtypes = [_P, _P, _I64, ctypes.POINTER(_P), _I, _I, _I, _U32, _P]
+        L.fms_peer_publish.argtypes = [_P, _P, _I64, ctypes.POINTER(_P), _I, _I, _I, _U32, ctypes.c_double, _P]
         L.fms_peer_wait_fold.restype = _I
-        L.fms_peer_wait_fold.argtypes = [_P, _P, _P, _I64, _I, _I, _I, _U32, ctypes.c_double, _P]
+        L.fms_peer_wait_fold.argtypes = [ctypes.POINTER(_P), _P, _P, _I64, _I, _I, _I, _U32, ctypes.c_double, _P]
         L._fms_peer_bound = True
     return L
 
@@ -81,9 +84,9 @@ class PeerCarryExchange:
         out = torch.empty(self.rows, device=self.device, dtype=torch.float32)
         with torch.cuda.device(self.device):
             rc = self._L.fms_peer_publish(P.data_ptr(), S.data_ptr(), self.rows, self._peers, self.world, self.rank,
-                                          d, number, self._stream())
+                                          d, number, self.max_wait_seconds, self._stream())
             if rc == capi.FMS_OK:
-                rc = self._L.fms_peer_wait_fold(self.buffer.data_ptr(), capi.ptr(carry0), out.data_ptr(), self.rows,
+                rc = self._L.fms_peer_wait_fold(self._peers, capi.ptr(carry0), out.data_ptr(), self.rows,
                                                 self.world, self.rank, d, number, self.max_wait_seconds,
                                                 self._stream())
         if rc != capi.FMS_OK:
@@ -91,11 +94,16 @@ class PeerCarryExchange:
                                 int(self._L.fms_last_cuda_error()))
         return out
 
+    _FAULTS = {1: "a block this rank depends on was not published in time (forward exchange)",
+               2: "a block this rank depends on was not published in time (reverse exchange)",
+               3: "a slot already held a later exchange than the one waited for (numbering broken)",
+               4: "a reader did not acknowledge the exchange two before this one in time"}
+
     def check(self) -> None:
-        """Synchronise and raise if any wait ran into its bound since the last check."""
+        """Synchronise and raise if an exchange recorded a fault.  After a fault the ranks'
+        exchange numbers no longer agree: build a new ``PeerCarryExchange``."""
         code = int(self.status.item())
         if code != 0:
-            self.status.zero_()
             raise PeerExchangeTimeout(
-                f"rank {self.rank}: a peer did not publish its carries within {self.max_wait_seconds} s "
-                f"({'reverse' if code == 2 else 'forward'} exchange)")
+                f"rank {self.rank}: {self._FAULTS.get(code, 'unknown fault %d' % code)} "
+                f"(bound {self.max_wait_seconds} s)")

@@ -7,7 +7,8 @@ sequence is what one CTA walks serially (fm/scan/fm_scan.cuh:84,211-216, at most
 Forward, per rank:
     1. carry-only pass        (P_k, S_k) = (prod a, h_last from a zero start)        reads a, x
     2. one all-gather of (P, S) -- 2 x rows fp32 per rank
-    3. fold the carries of the ranks before k  ->  h_in,k   (h_in,0 = initial_state or 0)
+    3. fold the carries of the ranks before k  ->  h_in,k   (h_in,0 = initial_state or 0; rank 0
+       folds the initial state into the S it publishes, the other ranks ignore theirs)
     4. the ordinary forward scan of the block with h0 = h_in,k                        reads a, x; writes h
 Backward mirrors it in reverse time order with c_t = a_t * delta_t as the carried quantity:
     1. carry-only reverse pass S'_k = c at the block start from a zero carry-in       reads a, G
@@ -48,12 +49,13 @@ class _TimeSplitScan(torch.autograd.Function):
         world = dist.get_world_size(group)
         rows_shape = gates.shape[:-1]
         P, S = ops.reduce(gates, tokens)
+        # The initial state belongs to the first block only.  Rank 0 folds it into the carry it
+        # publishes (S_0 <- P_0*h0 + S_0) and scans from it; the other ranks never look at their
+        # `initial_state` argument, so no collective depends on who passed one.
         carry0 = None
-        if initial_state is not None:
-            # every rank must fold the same h0: take rank 0's
-            carry0 = initial_state.to(torch.float32).reshape(-1).contiguous().clone()
-            dist.broadcast(carry0, src=dist.get_global_rank(group, 0) if group is not None else 0,
-                           group=group)
+        if rank == 0 and initial_state is not None:
+            carry0 = initial_state.to(torch.float32).reshape(-1).contiguous()
+            S = torch.addcmul(S.reshape(-1), P.reshape(-1), carry0)
         if exchange is not None:
             # peer stores + flags over NVLink, fold on arrival (fm_b200.peer_exchange)
             P_keep = P.reshape(-1).contiguous()
@@ -62,8 +64,11 @@ class _TimeSplitScan(torch.autograd.Function):
         else:
             PS = _gather(torch.stack([P.reshape(-1), S.reshape(-1)]), group)  # (world, 2, rows)
             P_keep = PS[:, 0].contiguous()
-            h_in_all, _ = ops.combine(P_keep, PS[:, 1].contiguous(), carry0, reverse=False)
-            h_in = h_in_all[rank].reshape(rows_shape).contiguous()
+            if rank == 0:
+                h_in = (carry0 if carry0 is not None else torch.zeros_like(P_keep[0])).reshape(rows_shape)
+            else:
+                h_in_all, _ = ops.combine(P_keep, PS[:, 1].contiguous(), None, reverse=False)
+                h_in = h_in_all[rank].reshape(rows_shape).contiguous()
         states = ops.forward(gates, tokens, h_in)
         ctx.save_for_backward(gates, states, h_in, P_keep)
         ctx.group, ctx.ops, ctx.rank, ctx.world, ctx.exchange = group, ops, rank, world, exchange
@@ -115,7 +120,8 @@ def fm_scan_time_split(gates, tokens, initial_state=None, group=None, ops=None, 
 
     Arguments:
         gates, tokens: (B, D, T_k) contiguous tensors of this rank's block (same dtype).
-        initial_state: (B, D) state before the first block; only rank 0's values are used.
+        initial_state: (B, D) state before the first block.  Only rank 0's argument is read; the
+            other ranks may pass anything, None included (no collective depends on it).
         group: process group spanning the time blocks (default: the world group).
         ops: local scan passes (default ``CudaScanOps``).
         exchange: a ``fm_b200.peer_exchange.PeerCarryExchange`` built for these rows: the carries

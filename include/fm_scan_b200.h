@@ -67,6 +67,14 @@ int fms_version(void);
 const char *fms_status_string(int status);
 /* The cudaError_t (as int) recorded by the last failing runtime call of this thread, 0 if none. */
 int fms_last_cuda_error(void);
+/*
+ * Launch-shape knobs (warps per row, tiles per step, the persistent walk, ...) can be forced with
+ * FMS_TUNE_* environment variables.  The library reads them once, at its first launch in the
+ * process; this call reads them again (tests and tuning sweeps use it; it is not synchronised
+ * with launches running on other threads).  No reference counterpart: the reference's launch
+ * geometry is compile-time (fm/scan/fm_scan.cuh:221-244).
+ */
+void fms_tune_reload(void);
 
 /* ------------------------------------------------------------------ PLAIN mode, one GPU ---- */
 
@@ -156,6 +164,19 @@ int fms_fm_backward(const void *gates, const void *tokens, const void *states, c
                     const float *h0, void *grad_gates, void *grad_tokens, float *grad_h0, int64_t B,
                     int64_t M, int64_t D, int64_t L, int dtype, void *workspace, size_t workspace_bytes,
                     fms_stream_t stream);
+
+/*
+ * FM backward WITHOUT the reductions, for the unmodified reference caller: fm_scan_backward's own
+ * output contract (fm/scan/fm_scan.cuh:184-207) is two (B,M,D,L) tensors
+ *   grad_tokens_full[b,m,d,t] = (1 - g[b,m,t]) * delta[b,m,d,t]
+ *   grad_gates_full [b,m,d,t] = (h[b,m,d,t-1] - x[b,d,t]) * delta[b,m,d,t]
+ * which FM_Scan.backward then sums over m and d itself (fm/scan/fm_scan.py:70-78).  Same inputs as
+ * fms_fm_backward; no workspace.  It moves the two full-size outputs that fms_fm_backward exists to
+ * avoid, so prefer that one wherever the caller can take reduced gradients.
+ */
+int fms_fm_backward_unreduced(const void *gates, const void *tokens, const void *states, const void *grad_states,
+                              const float *h0, void *grad_gates_full, void *grad_tokens_full, float *grad_h0,
+                              int64_t B, int64_t M, int64_t D, int64_t L, int dtype, fms_stream_t stream);
 
 /*
  * Read-out of the layer around the scan WITHOUT materialising the states: what
@@ -259,15 +280,19 @@ int fms_plain_backward_split(const void *gates, const void *states, const void *
  * cudaMalloc / cudaFree and no allocating library routine; inputs and outputs are still the
  * caller's.
  *
- * Limit: at most FMS_STATIC_SCRATCH_MAX_UNITS = 4096 scan units (rows x segments per row, see
- * fms_plain_split_segments); the array is 3 x 4096 fp32 = 48 KiB and every GPU that loads the
- * library holds it until the process exits.  A larger problem is refused with
- * FMS_ERR_TOO_LARGE and nothing is launched.  Shapes that need no split (segments == 1) use no
- * scratch and are always accepted.
+ * Limit: at most FMS_STATIC_SCRATCH_MAX_UNITS = 4096 scan units (rows x segments per row); the
+ * array is 3 x 4096 fp32 = 48 KiB and every GPU that loads the library holds it until the
+ * process exits.  When the library's usual plan (fms_plain_split_segments) would need more units
+ * than that, this entry point re-plans with fewer, longer segments -- at most 4096 / rows per
+ * row -- so every shape with rows <= 2048 is accepted; with more rows than that (and a shape that
+ * would be split at all) the call is refused with FMS_ERR_TOO_LARGE and nothing is launched.
+ * Shapes that need no split (segments == 1) use no scratch and are always accepted.
  *
  * Set-up: the first call on each device looks up the array's device address (once per device,
  * with that device current) and caches it.  Make that first call during initialisation, before
- * any stream capture is begun on the device.
+ * any stream capture is begun on the device.  The cached address belongs to the device's current
+ * primary context: a host that resets the device (cudaDeviceReset) must not call this entry
+ * point again in the same process.
  *
  * Sharing: all calls on a device use the same array and it keeps the last call's contents.
  * Nothing in it has to start at zero -- every call overwrites each slot it later reads -- but
@@ -292,23 +317,40 @@ int fms_plain_forward_split_static(const void *gates, const void *tokens, const 
  * mapped in this process (entry `rank` is the local buffer).  Plain peer stores only.
  *
  * fms_peer_wait_fold: wait until the blocks this rank depends on (those before it for forward,
- * after it for reverse) have published exchange number `exchange`, polling flags in LOCAL memory
- * with a bound of `max_wait_seconds` (<= 30; 2 if out of range), then fold their carries with
- * `carry0` (nullable; the carry entering the first block in scan order) into carry_out (rows).
- * If the bound is hit the kernel still ends normally, writes 1 + reverse into the buffer's
- * status word (fms_peer_exchange_status_offset() bytes into the buffer) and leaves carry0 in
- * carry_out; the host reads the word to learn of it.
+ * after it for reverse) have published exchange number `exchange`, polling flags in LOCAL memory,
+ * then fold their carries with `carry0` (nullable; the carry entering the first block in scan
+ * order) into carry_out (rows), and acknowledge the exchange to every rank (peer stores).
  *
- * `exchange` numbers start at 1 and grow by one per exchange and direction on ALL ranks alike;
- * two generations of slots (by parity) let a rank run one exchange ahead of a slower peer.
+ * Numbering and back-pressure: `exchange` numbers start at 1 and grow by one per exchange and
+ * direction on ALL ranks alike.  There are two generations of slots (by parity of the number), so
+ * exchange e+2 reuses the slots of e.  fms_peer_publish(e) therefore first waits until every rank
+ * that reads this rank's slot has acknowledged e-2: a rank runs at most one exchange ahead of the
+ * slowest rank that reads from it, whatever the mix of directions (forward-only loops included).
+ *
+ * Every wait is bounded by `max_wait_seconds` (<= 30; 2 if out of range) and polls local memory
+ * only.  When something goes wrong the kernel still ends normally and the FIRST fault is written
+ * to the local buffer's status word (fms_peer_exchange_status_offset() bytes into the buffer;
+ * the host reads it):
+ *   FMS_PEER_ERR_WAIT_TIMEOUT(_REVERSE)  a block this rank depends on was not published in time;
+ *                                        carry0 is passed through to carry_out
+ *   FMS_PEER_ERR_OVERRUN                 a slot already held a later exchange than the one asked
+ *                                        for (the numbering was broken); carry0 is passed through
+ *   FMS_PEER_ERR_ACK_TIMEOUT             a reader did not acknowledge e-2 in time; nothing is
+ *                                        published (the slot may still be in use)
+ * A fold that saw a fault, or a non-zero status word, sends no acknowledgement.  After a fault the
+ * exchange numbers of the ranks no longer agree: build new buffers.
  */
 #define FMS_MAX_PEERS 8
+#define FMS_PEER_ERR_WAIT_TIMEOUT 1
+#define FMS_PEER_ERR_WAIT_TIMEOUT_REVERSE 2
+#define FMS_PEER_ERR_OVERRUN 3
+#define FMS_PEER_ERR_ACK_TIMEOUT 4
 size_t fms_peer_exchange_bytes(int64_t rows, int world);
 size_t fms_peer_exchange_status_offset(int64_t rows, int world);
 int fms_peer_publish(const float *P, const float *S, int64_t rows, void *const *peer_buffers, int world, int rank,
-                     int reverse, uint32_t exchange, fms_stream_t stream);
-int fms_peer_wait_fold(void *local_buffer, const float *carry0, float *carry_out, int64_t rows, int world, int rank,
-                       int reverse, uint32_t exchange, double max_wait_seconds, fms_stream_t stream);
+                     int reverse, uint32_t exchange, double max_wait_seconds, fms_stream_t stream);
+int fms_peer_wait_fold(void *const *peer_buffers, const float *carry0, float *carry_out, int64_t rows, int world,
+                       int rank, int reverse, uint32_t exchange, double max_wait_seconds, fms_stream_t stream);
 
 /* ------------------------------------------------------- host-buffer pipeline (one GPU) ---- */
 
@@ -344,6 +386,18 @@ int fms_plain_forward_backward_host(fms_pipeline *pipe, const void *gates_h, con
                                     const void *grad_states_h, void *states_h, void *grad_gates_h,
                                     void *grad_tokens_h, int64_t rows, int64_t T, int dtype,
                                     fms_stream_t stream);
+
+/*
+ * The same pipeline with the kernels left out: the three inputs go host -> device into the
+ * staging slots and the three output slots come back device -> host, block by block, with the
+ * same streams, events and ordering.  The output buffers receive whatever the staging slots held;
+ * the call exists to MEASURE the ceiling the copies alone put on the end-to-end rate of this box
+ * (a benchmark reports it beside the full call).  Same arguments and rules as
+ * fms_plain_forward_backward_host.  No reference counterpart.
+ */
+int fms_pipeline_copy_probe(fms_pipeline *pipe, const void *gates_h, const void *tokens_h,
+                            const void *grad_states_h, void *states_h, void *grad_gates_h,
+                            void *grad_tokens_h, int64_t rows, int64_t T, int dtype, fms_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -25,3 +25,14 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def _restore_launch_knobs():
+    """The library caches its FMS_TUNE_* environment; a test that changed it (monkeypatch, then
+    ``gpu_util.reload_tune()``) must not leak its launch shapes into the next test.  Set up before
+    and therefore torn down after ``monkeypatch``, so the reload sees the restored environment."""
+    yield
+    from fm_b200 import capi
+    if capi._lib is not None:
+        capi._lib.fms_tune_reload()

@@ -4,6 +4,8 @@ Run where the reference checkout is available (it is not needed to run the tests
 
     FM_REFERENCE=/path/to/lexionbear-fm python tests/golden/make_golden.py
 
+    FM_REFERENCE=... python tests/golden/make_golden.py layer_     # only cases whose name starts so
+
 It imports ``fm_scan_pytorch`` from the reference's ``fm/scan/fm_pytorch.py``
 (pure torch, CPU), runs it -- forward and autograd backward with the loss
 ``(states * G).sum()`` -- on seeded inputs shaped like the benchmark configurations,
@@ -17,6 +19,13 @@ R rows is pinned through the fold  M = D = 1, B = R:
 
 where primes are the plain scan's gradients.  Inputs of 16-bit cases are rounded
 once to bf16/fp16 and stored as float32, so every consumer sees the same bits.
+
+The ``layer_*`` cases pin the layer around the scan.  The reference's module
+``fm/scan/fm_scan.py`` cannot be imported without a GPU (it JIT-compiles its CUDA at
+import, fm_scan.py:18-33), so the FUNCTION ``fm_memory`` (fm_scan.py:102-133) is taken out
+of the file's syntax tree, compiled unchanged, and run with the name ``fm_scan`` bound to
+the reference's CPU scan ``fm_scan_pytorch`` -- the reference's own layer arithmetic over
+the reference's own scan, in fp32 and fp64, with all five input gradients.
 """
 from __future__ import annotations
 
@@ -130,7 +139,52 @@ def fm_case(name, B, M, D, L, seed, gate_kind="sigmoid", with_h0=False):
     return name, arrays, meta
 
 
+def reference_fm_memory():
+    """The reference's ``fm_memory`` compiled from its source file without importing the module."""
+    import ast
+    path = Path(REF) / "fm" / "scan" / "fm_scan.py"
+    tree = ast.parse(path.read_text(), filename=str(path))
+    fn = [n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name == "fm_memory"]
+    assert len(fn) == 1, "fm_memory not found in the reference"
+    module = ast.Module(body=fn, type_ignores=[])
+    ns = {"torch": torch, "fm_scan": fm_scan_pytorch}
+    exec(compile(module, str(path), "exec"), ns)
+    return ns["fm_memory"]
+
+
+def layer_case(name, B, L, M, D, seed, mem_norm, with_h0):
+    """fm_memory(alpha (B,L,M), update_scale (B,L,1), output_scale (B,L,1), inputs (B,L,D), h0)
+    with the loss (output * W).sum() + (memory_states * Gs).sum()."""
+    fm_memory = reference_fm_memory()
+    gen = torch.Generator().manual_seed(seed)
+    alpha = torch.softmax(torch.randn(B, L, M, generator=gen), dim=-1)
+    upd = torch.sigmoid(torch.randn(B, L, 1, generator=gen))
+    outs = torch.sigmoid(torch.randn(B, L, 1, generator=gen))
+    inp = torch.randn(B, L, D, generator=gen)
+    W = torch.randn(B, L, D, generator=gen)
+    Gs = 0.1 * torch.randn(B, M, D, L, generator=gen)
+    h0 = torch.randn(B, M, D, generator=gen) if with_h0 else None
+    arrays = {"alpha": alpha.numpy(), "update_scale": upd.numpy(), "output_scale": outs.numpy(),
+              "inputs": inp.numpy(), "W": W.numpy(), "Gs": Gs.numpy()}
+    if h0 is not None:
+        arrays["h0"] = h0.numpy()
+    for tag, dt in (("ref32_", torch.float32), ("ref64_", torch.float64)):
+        args = [t.to(dt).clone().requires_grad_(True) for t in (alpha, upd, outs, inp)]
+        h0t = None if h0 is None else h0.to(dt).clone().requires_grad_(True)
+        out, states = fm_memory(*args, initial_state=h0t, mem_norm=mem_norm)
+        ((out * W.to(dt)).sum() + (states * Gs.to(dt)).sum()).backward()
+        arrays[tag + "out"] = out.detach().numpy()
+        arrays[tag + "states"] = states.detach().numpy()
+        for k, t in zip(("d_alpha", "d_update_scale", "d_output_scale", "d_inputs"), args):
+            arrays[tag + k] = t.grad.numpy()
+        if h0t is not None:
+            arrays[tag + "d_h0"] = h0t.grad.numpy()
+    meta = dict(name=name, mode="layer", B=B, L=L, M=M, D=D, seed=seed, mem_norm=bool(mem_norm))
+    return name, arrays, meta
+
+
 def main():
+    only = sys.argv[1] if len(sys.argv) > 1 else ""
     cases = [
         # configuration 1 of the benchmark: fp32 (2,64,1024), full shape
         folded_case("c1_fp32_2x64x1024", 128, 1024, 1001, "sigmoid", want64=False),
@@ -153,8 +207,14 @@ def main():
         # general FM mode with broadcast over M and D, with initial state
         fm_case("fm_2x3x5x64_h0", 2, 3, 5, 64, 1071, "sigmoid", with_h0=True),
         fm_case("fm_1x4x8x300", 1, 4, 8, 300, 1072, "sigmoid"),
-    ]
-    manifest = {}
+    ] if not only else []
+    # the layer around the scan (fm_memory), with and without the RMS norm / initial state
+    layer_specs = [("layer_norm_h0_2x64x3x8", 2, 64, 3, 8, 1080, True, True),
+                   ("layer_nonorm_1x128x4x8", 1, 128, 4, 8, 1081, False, False),
+                   ("layer_norm_1x40x8x16", 1, 40, 8, 16, 1082, True, False)]
+    cases += [layer_case(*spec) for spec in layer_specs if spec[0].startswith(only)]
+    manifest_path = HERE / "manifest.json"
+    manifest = json.loads(manifest_path.read_text())["cases"] if only and manifest_path.exists() else {}
     for name, arrays, meta in cases:
         path = HERE / f"{name}.npz"
         np.savez_compressed(path, **arrays)
@@ -167,6 +227,7 @@ def main():
         manifest[name] = meta
         print(name, {k: v.shape for k, v in arrays.items()}, f"{path.stat().st_size/1e3:.0f} kB")
     meta_all = {"torch": torch.__version__, "reference_function": "fm/scan/fm_pytorch.py:fm_scan_pytorch",
+                "reference_layer": "fm/scan/fm_scan.py:fm_memory (from the syntax tree) over fm_scan_pytorch",
                 "cases": manifest}
     (HERE / "manifest.json").write_text(json.dumps(meta_all, indent=1) + "\n")
 

@@ -20,6 +20,11 @@ def host(t):
     return None if t is None else t.detach().to(torch.float32).cpu().numpy()
 
 
+def reload_tune():
+    """Make the library read its FMS_TUNE_* environment again (it reads it once per process)."""
+    capi.lib().fms_tune_reload()
+
+
 def stream_ptr():
     return torch.cuda.current_stream().cuda_stream
 

@@ -114,6 +114,6 @@ def test_split_plan_is_pure_arithmetic():
     # the built-in scratch refuses more units than it holds, before touching the device
     buf = (ctypes.c_char * 64)()
     p = (ctypes.addressof(buf) + 15) // 16 * 16
-    rc = capi.call("fms_plain_forward_split_static", p, p, None, p, None, 2000, 16384, capi.FMS_F32, None,
+    rc = capi.call("fms_plain_forward_split_static", p, p, None, p, None, 2100, 16384, capi.FMS_F32, None,
                    check=False)
-    assert rc == capi.FMS_ERR_TOO_LARGE
+    assert rc == capi.FMS_ERR_TOO_LARGE   # not even two segments for each of 2100 rows fit 4096 units

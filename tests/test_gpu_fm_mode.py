@@ -38,6 +38,7 @@ def test_fm_goldens_from_the_reference(name):
 def test_fm_against_oracle(monkeypatch, blocked, storage, B, M, D, L):
     # blocked = 1: CTA-blocked reductions (aligned shapes); 0: one output row per CTA
     monkeypatch.setenv("FMS_TUNE_FM_BLOCKED", str(blocked))
+    G.reload_tune()
     rng = np.random.Generator(np.random.PCG64(B * 1000 + M * 100 + D * 10 + L))
     g = H.round_storage((0.5 + 0.5 * rng.random((B, M, L), dtype=np.float32)), storage)
     x = H.round_storage(rng.standard_normal((B, D, L), dtype=np.float32), storage)
@@ -85,6 +86,7 @@ def test_fm_equals_plain_on_broadcast_rows(monkeypatch):
     (row-per-CTA forward; the blocked forward associates the tile scan differently and is
     covered by the oracle cases)."""
     monkeypatch.setenv("FMS_TUNE_FM_BLOCKED", "0")
+    G.reload_tune()
     rng = np.random.Generator(np.random.PCG64(5))
     B, M, D, L = 2, 3, 4, 512
     g = rng.random((B, M, L), dtype=np.float32)
@@ -210,6 +212,7 @@ def test_fm_randomised_shapes(monkeypatch):
         if B * M * D * L > 1_500_000:
             continue
         monkeypatch.setenv("FMS_TUNE_FM_BLOCKED", str(rnd.choice([0, 1])))
+        G.reload_tune()
         rng = np.random.Generator(np.random.PCG64(7000 + done))
         g = 0.3 + 0.7 * rng.random((B, M, L), dtype=np.float32)
         if rnd.random() < 0.3:
@@ -240,3 +243,39 @@ def test_fm_randomised_shapes(monkeypatch):
         H.assert_close(G.host(dg), dg_ref, *tol(dg_ref), what + " d_gates")
         H.assert_close(G.host(dh0), dh0_ref, 1e-3, 1e-3 * max(1.0, float(np.abs(dh0_ref).max())), what + " d_h0")
         done += 1
+
+
+@pytest.mark.parametrize("path", ["fused", "composed", "readout"])
+@pytest.mark.parametrize("name", H.golden_names("layer"))
+def test_layer_against_reference_goldens(name, path):
+    """The layer on the GPU against outputs of the reference's own ``fm_memory`` (see
+    tests/golden/make_golden.py): the fused training op, the reference's composition over the
+    FM-mode scan, and the read-out that never writes the states.  Compared with the reference's
+    double-precision run; fp32 tolerance scaled by each tensor's largest magnitude."""
+    from fm_b200 import fm_memory
+    g = H.load_golden(name)
+    mem_norm = H.manifest()[name]["mem_norm"]
+    dev = "cuda"
+    args = [torch.from_numpy(g[k]).to(dev).requires_grad_(path != "readout")
+            for k in ("alpha", "update_scale", "output_scale", "inputs")]
+    h0 = torch.from_numpy(g["h0"]).to(dev).requires_grad_(path != "readout") if "h0" in g else None
+
+    def close(got, key, rtol=1e-4, atol=2e-5):
+        ref = g["ref64_" + key]
+        H.assert_close(got.detach().double().cpu().numpy(), ref, rtol, atol * max(1.0, float(np.abs(ref).max())),
+                       f"{name} {path} {key}")
+
+    if path == "readout":
+        with torch.no_grad():
+            out, states = fm_memory(*args, initial_state=h0, mem_norm=mem_norm, need_states=False)
+        assert states is None
+        close(out, "out")
+        return
+    out, states = fm_memory(*args, initial_state=h0, mem_norm=mem_norm, fused=(path == "fused"))
+    ((out * torch.from_numpy(g["W"]).to(dev)).sum() + (states * torch.from_numpy(g["Gs"]).to(dev)).sum()).backward()
+    close(out, "out")
+    close(states, "states")
+    for k, t in zip(("d_alpha", "d_update_scale", "d_output_scale", "d_inputs"), args):
+        close(t.grad, k)
+    if h0 is not None:
+        close(h0.grad, "d_h0")

@@ -39,6 +39,25 @@ def _worker(rank, world, port, mode, storage, out_dir):
 
         B, D, T = 2, 24, 8 * 1031
         a, x, Gd, h0 = H.make_inputs(B * D, T, 123, "sigmoid+3", storage, with_h0=True)
+        if mode == "time_peer_forward_only":
+            # inference-style loop: forward exchanges only, one rank lagging behind the others
+            import time
+            from fm_b200.peer_exchange import PeerCarryExchange
+            tb = sharding.time_blocks(T, world)[rank]
+            ad, xd = (G.dev(np.ascontiguousarray(v[:, tb[0]:tb[1]]), storage, dev).view(B, D, -1) for v in (a, x))
+            exchange = PeerCarryExchange(B * D)
+            outs = []
+            with torch.no_grad():
+                for it in range(6):
+                    if rank == world - 1 and it % 2 == 1:
+                        torch.cuda.synchronize()
+                        time.sleep(0.05)            # the last block falls behind
+                    outs.append(G.host(fm_scan_time_split(ad, xd * float(it + 1), exchange=exchange)))
+            exchange.check()
+            torch.cuda.synchronize()
+            np.savez(os.path.join(out_dir, f"rank{rank}.npz"), **{f"h{i}": o.reshape(B * D, -1) for i, o in enumerate(outs)})
+            dist.barrier()
+            return
         if mode == "rows":
             blk = sharding.row_blocks(B * D, world)[rank]
             ad, xd, gd = (G.dev(v[blk[0]:blk[1]], storage, dev).requires_grad_(v is not Gd)
@@ -120,3 +139,19 @@ def test_time_split_over_nccl_matches_oracle(tmp_path, storage, transport):
     H.assert_close(np.concatenate([p["ga"] for p in parts], 1), ga_ref, *tol(ga_ref), "time-split grad_gates")
     H.assert_close(parts[0]["gh0"], gh0_ref, 1e-2 if storage != "f32" else 1e-4, 1e-2 if storage != "f32" else 1e-5,
                    "time-split grad_h0")
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_forward_only_loop_over_peer_exchange_with_a_lagging_rank(tmp_path):
+    """No backward pass orders the ranks here: only the acknowledgements keep a fast rank from
+    reusing a slot generation that the lagging rank has not folded yet."""
+    world = min(_ngpu(), 4)
+    parts = _run(world, "time_peer_forward_only", "f32", tmp_path)
+    B, D, T = 2, 24, 8 * 1031
+    a, x, _, _ = H.make_inputs(B * D, T, 123, "sigmoid+3", "f32", with_h0=True)
+    f64 = np.float64
+    for it in range(6):
+        h = np.concatenate([p[f"h{it}"] for p in parts], 1)
+        h_ref = oc.plain_forward(a.astype(f64), (x * np.float32(it + 1)).astype(f64), dtype=f64)
+        H.assert_close(h, h_ref, H.FP32_RTOL, H.FP32_ATOL * max(1.0, float(np.abs(h_ref).max())),
+                       f"forward-only iteration {it}")

@@ -383,6 +383,7 @@ def test_warps_per_row_variants_agree(monkeypatch, K, storage, T):
     """K warps cooperating on a row (shared-memory carry exchange) against the oracle."""
     monkeypatch.setenv("FMS_TUNE_FWD_K", str(K))
     monkeypatch.setenv("FMS_TUNE_BWD_K", str(K))
+    G.reload_tune()
     a, x, Gd, h0 = H.make_inputs(7, T, 400 + T, "sigmoid01", storage, with_h0=True)
     cin = np.linspace(-1, 1, 7).astype(np.float32)
     check_fwd_bwd(a, x, Gd, storage, h0, cin, f"K={K} {storage} T={T}")
@@ -397,6 +398,7 @@ def test_warps_per_row_variants_agree(monkeypatch, K, storage, T):
 def test_unroll_variants_agree(monkeypatch, U):
     monkeypatch.setenv("FMS_TUNE_FWD_U", str(U))
     monkeypatch.setenv("FMS_TUNE_BWD_U", str(U))
+    G.reload_tune()
     a, x, Gd = H.make_inputs(9, 4096 + 512, 17, "sigmoid", "bf16")
     check_fwd_bwd(a, x, Gd, "bf16", what=f"U={U}")
 
@@ -410,6 +412,7 @@ def test_persistent_walk_over_several_rows(monkeypatch, K, storage, R, T, ctas):
     monkeypatch.setenv("FMS_TUNE_MAX_CTAS", str(ctas))
     monkeypatch.setenv("FMS_TUNE_FWD_K", str(K))
     monkeypatch.setenv("FMS_TUNE_BWD_K", str(K))
+    G.reload_tune()
     a, x, Gd, h0 = H.make_inputs(R, T, 600 + R, "sigmoid01", storage, with_h0=True)
     cin = np.linspace(-1, 1, R).astype(np.float32)
     check_fwd_bwd(a, x, Gd, storage, h0, cin, f"persistent K={K} {storage} {R}x{T}")
@@ -446,6 +449,7 @@ def test_randomised_shapes_and_launch_shapes(monkeypatch):
                 monkeypatch.setenv(name, str(v))
             else:
                 monkeypatch.delenv(name, raising=False)
+        G.reload_tune()
         gates = rnd.choice(["sigmoid", "sigmoid01", "sigmoid+3"])
         off = rnd.choice([0, 0, 1, 3])
         a, x, Gd, h0 = H.make_inputs(R, T, 9000 + done, gates, storage, with_h0=True)

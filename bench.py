@@ -404,11 +404,16 @@ def measure_time_split(args, world, rank, device, barrier, max_over_ranks):
     exchange, transport = None, "none (one GPU, rows scanned whole)"
     if world > 1:
         transport = "NCCL all-gather of (P,S) fp32 carries, once per direction"
-        if args.exchange == "peer":
+        if args.exchange in ("fused", "peer"):
             try:
-                from fm_b200.peer_exchange import PeerCarryExchange
-                exchange = PeerCarryExchange(B * D)
-                transport = "peer stores + flags in symmetric memory, fold on arrival"
+                from fm_b200.peer_exchange import FusedTimeSplit, PeerCarryExchange
+                if args.exchange == "fused":
+                    exchange = FusedTimeSplit(B * D)
+                    transport = ("one kernel per direction: carry pass, peer stores + bounded local polls, scan "
+                                 "pass fused row by row (second pass re-reads the row from L2)")
+                else:
+                    exchange = PeerCarryExchange(B * D)
+                    transport = "peer stores + flags in symmetric memory, fold on arrival"
             except Exception as e:  # symmetric memory unavailable: keep the collective
                 transport += " (peer exchange unavailable: %s)" % type(e).__name__
 
@@ -599,9 +604,9 @@ def run_time_split(args):
     G = torch.randn(B, D, Tk, device=device, generator=gen)
 
     exchange = None
-    if world > 1 and args.exchange == "peer":
-        from fm_b200.peer_exchange import PeerCarryExchange
-        exchange = PeerCarryExchange(B * D)
+    if world > 1 and args.exchange in ("peer", "fused"):
+        from fm_b200.peer_exchange import FusedTimeSplit, PeerCarryExchange
+        exchange = FusedTimeSplit(B * D) if args.exchange == "fused" else PeerCarryExchange(B * D)
 
     def step():
         h = fm_scan_time_split(a, x, exchange=exchange) if world > 1 else fm_scan(a, x)
@@ -641,7 +646,7 @@ def run_time_split(args):
                 "data": "synthetic",
                 "config": {"workload": "scan fwd+bwd (B,D,T)=(1,%d,262144) fp32, T split in %d blocks" % (D, world),
                            "gates": "a = sigmoid(N(0,1)+3); x, G ~ N(0,1)",
-                           "exchange": ("peer stores + flags in symmetric memory, fold on arrival"
+                           "exchange": (type(exchange).__name__ + ": peer stores + flags in symmetric memory"
                                         if exchange is not None else
                                         "NCCL all-gather of (P,S) fp32 carries, once per direction")},
                 "gpu_launches": K * (2 if world == 1 else 6),
@@ -876,7 +881,7 @@ def main():
                     help="c3: the headline row-sharded workload; c4: the long sequence split along T; "
                          "fm: the reference's (B,M,L)x(B,D,L)->(B,M,D,L) operator at its demo shape; "
                          "btd: the plain scan on channel-last (B,T,D) tensors")
-    ap.add_argument("--exchange", choices=["nccl", "peer"], default="peer",
+    ap.add_argument("--exchange", choices=["nccl", "peer", "fused"], default="fused",
                     help="carry transport of the long sequence split along T")
     ap.add_argument("--no-extras", action="store_true",
                     help="headline only: skip time_split, the other scaling mode and reference_cuda")

@@ -50,6 +50,8 @@ struct Tune {
     int max_ctas = 0x7fffffff;                       // test knob: forces the multi-row walk
     int persist = -1;                                // -1 = choose from the shape, 0 = off, 1 = on
     int fm_pd = 4, fm_blocked = 1, btd_warps_per_sm = 32;
+    int bwd_descending = 1;  // backward visits rows last-to-first (re-reads the forward's latest rows from L2)
+    int fwd_keep = 0;        // L2 policy of the forward's state stores: 0 evict-first, 1 normal, 2 evict-last
 };
 
 Tune g_tune;
@@ -70,6 +72,8 @@ void load_tune() {
     t.fm_pd = get("FMS_TUNE_FM_PD", 4);
     t.fm_blocked = get("FMS_TUNE_FM_BLOCKED", 1);
     t.btd_warps_per_sm = std::max(1, get("FMS_TUNE_BTD_WARPS_PER_SM", 32));
+    t.bwd_descending = get("FMS_TUNE_BWD_DESCENDING", 1);
+    t.fwd_keep = get("FMS_TUNE_FWD_KEEP", 0);
     g_tune = t;
 }
 
@@ -209,7 +213,8 @@ int launch_forward(const Problem &pb, const Split &sp, const void *gates, const 
         }                                                                                          \
         kern<<<static_cast<unsigned>(nctas), fms::Coop<KK>::kThreads, 0, st>>>(                    \
             static_cast<const S *>(gates), static_cast<const S *>(tokens), h0,                     \
-            static_cast<S *>(states), h_last, P, units, pb.T, sp.nseg, seg_len, 0, 0);             \
+            static_cast<S *>(states), h_last, P, units, pb.T, sp.nseg, seg_len, 0, 0,              \
+            tune().fwd_keep);                                                                      \
     } while (0)
 #define FMS_LAUNCH_FWD(G, UU, KK) FMS_LAUNCH_FWD_S(G, UU, KK, false)
 #define FMS_LAUNCH_FWD_K(G, UU)                                                                    \
@@ -263,7 +268,7 @@ int launch_backward(const Problem &pb, const Split &sp, const void *gates, const
             static_cast<const S *>(gates), static_cast<const S *>(states),                         \
             static_cast<const S *>(grad_states), h0, carry_in, static_cast<S *>(grad_gates),       \
             static_cast<S *>(grad_tokens), grad_h0, P, units, pb.T, sp.nseg, seg_len, nullptr,     \
-            nullptr, nullptr, 0, 0);                                                               \
+            nullptr, nullptr, 0, 0, tune().bwd_descending);                                        \
     } while (0)
 #define FMS_LAUNCH_BWD(G, UU, KK) FMS_LAUNCH_BWD_S(G, UU, KK, false)
 #define FMS_LAUNCH_BWD_K(G, UU)                                                                    \
@@ -431,7 +436,7 @@ int launch_fm_forward(const FmShape &sh, bool aligned, const void *gates, const 
     fms::plain_forward_kernel<S, G, UU, true, KK, false, true>                                     \
         <<<static_cast<unsigned>(ctas), fms::Coop<KK>::kThreads, 0, st>>>(                         \
             static_cast<const S *>(gates), static_cast<const S *>(tokens), h0,                     \
-            static_cast<S *>(states), nullptr, nullptr, sh.rows, sh.L, 1, sh.L, sh.M, sh.D)
+            static_cast<S *>(states), nullptr, nullptr, sh.rows, sh.L, 1, sh.L, sh.M, sh.D, 0)
 #define FMS_LAUNCH_FM_FWD_K(G, UU)                                                                 \
     switch (K) {                                                                                   \
         case 1: FMS_LAUNCH_FM_FWD(G, UU, 1); break;                                                \
@@ -464,7 +469,7 @@ int launch_fm_backward(const FmShape &sh, bool aligned, const void *gates, const
             static_cast<const S *>(gates), static_cast<const S *>(states),                         \
             static_cast<const S *>(grad_states), h0, nullptr, static_cast<S *>(full_gates),        \
             static_cast<S *>(full_tokens), grad_h0, nullptr, sh.rows, sh.L, 1, sh.L,               \
-            static_cast<const S *>(tokens), acc_gates, acc_tokens, sh.M, sh.D)
+            static_cast<const S *>(tokens), acc_gates, acc_tokens, sh.M, sh.D, 0)
 #define FMS_LAUNCH_FM_BWD_K(G, UU)                                                                 \
     switch (K) {                                                                                   \
         case 1: FMS_LAUNCH_FM_BWD(G, UU, 1); break;                                                \

@@ -136,6 +136,24 @@ __device__ __forceinline__ void stg_stream(void *p, const uint4 &v) {
                  : "memory");
 }
 
+// The same store under an L2 eviction policy chosen at run time (one instruction either way, no
+// branch): evict-first for write-once streams, evict-normal / evict-last for data the NEXT kernel
+// reads back soon (the states a forward writes and the backward of the same step re-reads, latest
+// rows first).  mode: 0 evict-first, 1 evict-normal, 2 evict-last.
+__device__ __forceinline__ uint64_t make_store_policy(int mode) {
+    uint64_t pol;
+    if (mode == 2) asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    else if (mode == 1) asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(pol));
+    else asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+
+__device__ __forceinline__ void stg_policy(void *p, const uint4 &v, uint64_t pol) {
+    asm volatile("st.global.L2::cache_hint.v4.u32 [%0], {%1,%2,%3,%4}, %5;" ::"l"(p), "r"(v.x), "r"(v.y),
+                 "r"(v.z), "r"(v.w), "l"(pol)
+                 : "memory");
+}
+
 // One lane's vector of a row: positions [v, v+E).  `fill` is the 32-bit pattern returned for
 // positions outside [0, T) (packed ones for gates, zero otherwise).  In the aligned
 // instantiation a vector is either wholly inside the row or wholly outside it.
@@ -183,6 +201,17 @@ __device__ __forceinline__ void store_vec(S *__restrict__ row, int64_t v, int64_
             const int64_t t = v + i;
             if (t >= 0 && t < T) row[t] = u.s[i];
         }
+    }
+}
+
+// store_vec whose full-vector stores carry an L2 eviction policy (make_store_policy).
+template <typename S, bool GENERIC>
+__device__ __forceinline__ void store_vec_policy(S *__restrict__ row, int64_t v, int64_t T, bool same_phase,
+                                                 const uint4 &q, uint64_t pol) {
+    if constexpr (!GENERIC) {
+        if (v < T) stg_policy(row + v, q, pol);
+    } else {
+        store_vec<S, GENERIC>(row, v, T, same_phase, q);
     }
 }
 
@@ -285,7 +314,7 @@ __global__ void __launch_bounds__(Coop<K>::kThreads)
 plain_forward_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
                      const float *__restrict__ h0, S *__restrict__ states,
                      float *__restrict__ h_last, float *__restrict__ P_out, int64_t R, int64_t T,
-                     int64_t nseg, int64_t seg_len, int64_t M, int64_t D) {
+                     int64_t nseg, int64_t seg_len, int64_t M, int64_t D, int keep_states) {
     static_assert(!(FM && SEG), "FM mode has no segmented variant");
     constexpr int E = Store<S>::E;
     constexpr int TILE = 32 * E;
@@ -317,6 +346,8 @@ plain_forward_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
 
     float carry = h0 ? h0[unit] : 0.f;  // state entering the current super-tile
     float prod = 1.f;                   // product of the unit's gates so far (reduce only)
+    uint64_t store_pol = 0;
+    if constexpr (WRITE && !GENERIC) store_pol = make_store_policy(keep_states);
 
     int64_t v = v0;  // this lane's first vector of the current group, relative to the unit
     int64_t g = 0;
@@ -421,7 +452,7 @@ plain_forward_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
                     s = fmaf(fa[j][i], s, fx[j][i]);
                     out[i] = s;
                 }
-                store_vec<S, GENERIC>(states + off, v + j * TILE, L, ph_h, Store<S>::pack(out));
+                store_vec_policy<S, GENERIC>(states + off, v + j * TILE, L, ph_h, Store<S>::pack(out), store_pol);
             } else if constexpr (K == 1) {
                 prod *= tA;
             }
@@ -476,7 +507,7 @@ plain_backward_kernel(const S *__restrict__ gates, const S *__restrict__ states,
                       S *__restrict__ grad_tokens, float *__restrict__ grad_h0,
                       float *__restrict__ P_out, int64_t R, int64_t T, int64_t nseg,
                       int64_t seg_len, const S *__restrict__ tokens_fm, float *__restrict__ acc_gates,
-                      float *__restrict__ acc_tokens, int64_t M, int64_t D) {
+                      float *__restrict__ acc_tokens, int64_t M, int64_t D, int descending) {
     static_assert(!(FM && SEG) && !(FM && !WRITE), "FM mode: whole rows, full backward only");
     constexpr int E = Store<S>::E;
     constexpr int TILE = 32 * E;
@@ -487,7 +518,13 @@ plain_backward_kernel(const S *__restrict__ gates, const S *__restrict__ states,
     const int w = Coop<K>::warp_in_unit();
     int64_t unit = Coop<K>::first_unit();
     if (unit >= R) return;
-    const int64_t stride = Coop<K>::unit_stride();
+    // descending: units are visited from the last one down, so that the rows a forward over the
+    // same tensors touched last (still in L2) are re-read first
+    int64_t stride = Coop<K>::unit_stride();
+    if (descending) {
+        unit = R - 1 - unit;
+        stride = -stride;
+    }
 
     const Unit q = unit_of<SEG>(unit, T, nseg, seg_len);
     const int64_t L = q.len;
@@ -553,7 +590,7 @@ plain_backward_kernel(const S *__restrict__ gates, const S *__restrict__ states,
         int64_t noff = off, nv = v - SUPER;
         bool more = true;
         if (last_group) {
-            if (PERSIST && unit + stride < R) {
+            if (PERSIST && unit + stride < R && unit + stride >= 0) {
                 noff = (unit + stride) * T;
                 nv = v_last;
             } else {
@@ -719,7 +756,7 @@ __global__ void cast_from_f32_kernel(const float *__restrict__ src, S *__restric
 // Element (chunk k, row r) of P, S and carry_out lives at k*chunk_stride + r*row_stride:
 // (R, 1) for the chunk-major layout an all-gather produces, (1, nchunks) for the row-major
 // layout of the one-GPU split path.
-__global__ void combine_carries_kernel(const float *__restrict__ P, const float *__restrict__ S,
+static __global__ void combine_carries_kernel(const float *__restrict__ P, const float *__restrict__ S,
                                        const float *__restrict__ carry0,
                                        float *__restrict__ carry_out, float *__restrict__ total,
                                        int64_t nchunks, int64_t R, int reverse,

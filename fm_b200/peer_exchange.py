@@ -43,6 +43,111 @@ class PeerExchangeTimeout(RuntimeError):
     pass
 
 
+_FAULTS = {1: "a block this rank depends on was not published in time (forward exchange)",
+           2: "a block this rank depends on was not published in time (reverse exchange)",
+           3: "a slot already held a later exchange than the one waited for (numbering broken)",
+           4: "a reader did not acknowledge the exchange two before this one in time"}
+
+
+def _bind_fused():
+    L = capi.lib()
+    if not getattr(L, "_fms_tsplit_bound", False):
+        L.fms_tsplit_exchange_bytes.restype = ctypes.c_size_t
+        L.fms_tsplit_exchange_bytes.argtypes = [_I64, _I]
+        L.fms_tsplit_exchange_status_offset.restype = ctypes.c_size_t
+        L.fms_tsplit_exchange_status_offset.argtypes = [_I64, _I]
+        L.fms_tsplit_forward.restype = _I
+        L.fms_tsplit_forward.argtypes = [_P, _P, _P, _P, _P, _I64, _I64, _I, ctypes.POINTER(_P), _I, _I, _U32,
+                                         ctypes.c_double, _P]
+        L.fms_tsplit_backward.restype = _I
+        L.fms_tsplit_backward.argtypes = [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I, ctypes.POINTER(_P), _I, _I,
+                                          _U32, ctypes.c_double, _P]
+        L._fms_tsplit_bound = True
+    return L
+
+
+class FusedTimeSplit:
+    """The split-along-T scan as ONE kernel per direction (``fms_tsplit_forward`` / ``_backward``).
+
+    Owns this rank's exchange buffer in torch symmetric memory.  Carry pass, exchange of the
+    carries (peer stores, bounded local polls) and scan pass run fused row by row inside the kernel,
+    so a row's operands are re-read from L2 and the block moves the HBM bytes of an unsplit scan.
+    All ranks create the object together and call ``forward`` / ``backward`` in the same order.
+    Needs 16-byte aligned rows (``T_k * element size % 16 == 0``); ``applies()`` tells.
+    """
+
+    def __init__(self, rows: int, group=None, device=None, max_wait_seconds: float = 2.0):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self._L = _bind_fused()
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank = dist.get_rank(self.group)
+        self.world = dist.get_world_size(self.group)
+        if self.world > 8:
+            raise ValueError("the fused split covers one box: at most 8 ranks")
+        self.rows = int(rows)
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.max_wait_seconds = float(max_wait_seconds)
+        nbytes = int(self._L.fms_tsplit_exchange_bytes(self.rows, self.world))
+        self.buffer = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+        self.buffer.zero_()
+        self.handle = symm_mem.rendezvous(self.buffer, self.group)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)  # every buffer is zeroed before anyone publishes
+        self._peers = (_P * self.world)(*[int(p) for p in self.handle.buffer_ptrs])
+        off = int(self._L.fms_tsplit_exchange_status_offset(self.rows, self.world))
+        self.status = self.buffer[off:off + 4].view(torch.int32)
+        self._count = [0, 0]
+
+    @staticmethod
+    def applies(gates: torch.Tensor) -> bool:
+        T = gates.shape[-1]
+        return gates.is_cuda and T >= 1 and (T * gates.element_size()) % 16 == 0 and gates.data_ptr() % 16 == 0
+
+    def _stream(self):
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def _raise(self, what, rc):
+        raise capi.FmsError(what, rc, capi.status_string(rc), int(self._L.fms_last_cuda_error()))
+
+    def forward(self, gates, tokens, h0=None):
+        """-> (states, h_in): this block's states and the fp32 carry (rows) that entered the block."""
+        T = gates.shape[-1]
+        states = torch.empty_like(gates)
+        h_in = torch.empty(self.rows, device=self.device, dtype=torch.float32)
+        self._count[0] += 1
+        with torch.cuda.device(self.device):
+            rc = self._L.fms_tsplit_forward(gates.data_ptr(), tokens.data_ptr(), capi.ptr(h0), states.data_ptr(),
+                                            h_in.data_ptr(), self.rows, T, capi.dtype_tag(gates.dtype), self._peers,
+                                            self.world, self.rank, self._count[0], self.max_wait_seconds,
+                                            self._stream())
+        if rc != capi.FMS_OK:
+            self._raise("fms_tsplit_forward", rc)
+        return states, h_in
+
+    def backward(self, gates, states, grad_states, h_in, want_grad_h0=False):
+        T = gates.shape[-1]
+        grad_gates, grad_tokens = torch.empty_like(gates), torch.empty_like(gates)
+        grad_h0 = torch.empty(self.rows, device=self.device, dtype=torch.float32) if want_grad_h0 else None
+        self._count[1] += 1
+        with torch.cuda.device(self.device):
+            rc = self._L.fms_tsplit_backward(gates.data_ptr(), states.data_ptr(), grad_states.data_ptr(),
+                                             h_in.data_ptr(), grad_gates.data_ptr(), grad_tokens.data_ptr(),
+                                             capi.ptr(grad_h0), self.rows, T, capi.dtype_tag(gates.dtype),
+                                             self._peers, self.world, self.rank, self._count[1],
+                                             self.max_wait_seconds, self._stream())
+        if rc != capi.FMS_OK:
+            self._raise("fms_tsplit_backward", rc)
+        return grad_gates, grad_tokens, grad_h0
+
+    def check(self) -> None:
+        """Synchronise and raise if a kernel recorded a fault (a wait ran out, numbering broken)."""
+        code = int(self.status.item())
+        if code != 0:
+            raise PeerExchangeTimeout(
+                f"rank {self.rank}: {_FAULTS.get(code, 'unknown fault %d' % code)} (bound {self.max_wait_seconds} s)")
+
+
 class PeerCarryExchange:
     def __init__(self, rows: int, group=None, device=None, max_wait_seconds: float = 2.0):
         import torch.distributed._symmetric_memory as symm_mem
@@ -94,16 +199,11 @@ class PeerCarryExchange:
                                 int(self._L.fms_last_cuda_error()))
         return out
 
-    _FAULTS = {1: "a block this rank depends on was not published in time (forward exchange)",
-               2: "a block this rank depends on was not published in time (reverse exchange)",
-               3: "a slot already held a later exchange than the one waited for (numbering broken)",
-               4: "a reader did not acknowledge the exchange two before this one in time"}
-
     def check(self) -> None:
         """Synchronise and raise if an exchange recorded a fault.  After a fault the ranks'
         exchange numbers no longer agree: build a new ``PeerCarryExchange``."""
         code = int(self.status.item())
         if code != 0:
             raise PeerExchangeTimeout(
-                f"rank {self.rank}: {self._FAULTS.get(code, 'unknown fault %d' % code)} "
+                f"rank {self.rank}: {_FAULTS.get(code, 'unknown fault %d' % code)} "
                 f"(bound {self.max_wait_seconds} s)")

@@ -20,7 +20,8 @@ Rank 0's dL/dh0 output is the gradient of ``initial_state``.
 
 The collective is whatever the group's backend provides (NCCL over NVLink on GPUs); with a
 ``PeerCarryExchange`` the all-gather and the fold are replaced by peer stores + flags in
-symmetric memory and a fold-on-arrival kernel.  The local
+symmetric memory and a fold-on-arrival kernel; with a ``FusedTimeSplit`` steps 1-4 of each
+direction are one kernel (the second pass re-reads the row from L2).  The local
 passes come from an ops object: ``CudaScanOps`` (the CUDA kernels) by default.  Tests on CPU
 ranks inject another ops object to exercise the exchange logic over gloo; the package itself
 ships no CPU scan.
@@ -31,6 +32,7 @@ import torch
 import torch.distributed as dist
 
 from .ops import CudaScanOps
+from .peer_exchange import FusedTimeSplit
 
 
 def _gather(t: torch.Tensor, group) -> torch.Tensor:
@@ -48,6 +50,23 @@ class _TimeSplitScan(torch.autograd.Function):
         rank = dist.get_rank(group)
         world = dist.get_world_size(group)
         rows_shape = gates.shape[:-1]
+        ctx.fused = False
+        if isinstance(exchange, FusedTimeSplit) and FusedTimeSplit.applies(gates):
+            # one kernel: carry pass, peer exchange and scan pass fused row by row
+            h0 = None
+            if rank == 0 and initial_state is not None:
+                h0 = initial_state.to(torch.float32).reshape(-1).contiguous()
+            states, h_in = exchange.forward(gates, tokens, h0)
+            ctx.save_for_backward(gates, states, h_in)
+            ctx.group, ctx.ops, ctx.rank, ctx.world, ctx.exchange = group, ops, rank, world, exchange
+            ctx.fused = True
+            ctx.h0_dtype = None if initial_state is None else initial_state.dtype
+            ctx.h0_needs_grad = initial_state is not None and ctx.needs_input_grad[2]
+            ctx.h0_shape = None if initial_state is None else initial_state.shape
+            return states
+        if isinstance(exchange, FusedTimeSplit):
+            raise RuntimeError("FusedTimeSplit needs 16-byte aligned rows (T_k * element size % 16 == 0); "
+                               "use PeerCarryExchange or the default all-gather for this shape")
         P, S = ops.reduce(gates, tokens)
         # The initial state belongs to the first block only.  Rank 0 folds it into the carry it
         # publishes (S_0 <- P_0*h0 + S_0) and scans from it; the other ranks never look at their
@@ -78,6 +97,15 @@ class _TimeSplitScan(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_states):
+        if ctx.fused:
+            gates, states, h_in = ctx.saved_tensors
+            grad_gates, grad_tokens, grad_h0 = ctx.exchange.backward(
+                gates, states, grad_states.contiguous(), h_in, want_grad_h0=ctx.h0_needs_grad)
+            d_h0 = None
+            if ctx.h0_needs_grad:
+                d_h0 = grad_h0 if ctx.rank == 0 else torch.zeros_like(grad_h0)
+                d_h0 = d_h0.reshape(ctx.h0_shape).to(ctx.h0_dtype)
+            return grad_gates, grad_tokens, d_h0, None, None, None
         gates, states, h_in, P_keep = ctx.saved_tensors
         group, ops, rank = ctx.group, ctx.ops, ctx.rank
         grad_states = grad_states.contiguous()
@@ -125,7 +153,10 @@ def fm_scan_time_split(gates, tokens, initial_state=None, group=None, ops=None, 
         group: process group spanning the time blocks (default: the world group).
         ops: local scan passes (default ``CudaScanOps``).
         exchange: a ``fm_b200.peer_exchange.PeerCarryExchange`` built for these rows: the carries
-            then travel as peer stores over NVLink with flags instead of an all-gather.
+            then travel as peer stores over NVLink with flags instead of an all-gather.  A
+            ``fm_b200.peer_exchange.FusedTimeSplit`` goes further: each direction is ONE kernel in
+            which the carry pass, the exchange and the scan pass are fused row by row, so the block
+            moves the HBM bytes of an unsplit scan (needs 16-byte aligned rows).
         validate: exchange a shape/dtype descriptor first and raise on every rank if the ranks
             disagree (one extra small all-gather; off by default).
     Returns:

@@ -352,6 +352,48 @@ int fms_peer_publish(const float *P, const float *S, int64_t rows, void *const *
 int fms_peer_wait_fold(void *const *peer_buffers, const float *carry0, float *carry_out, int64_t rows, int world,
                        int rank, int reverse, uint32_t exchange, double max_wait_seconds, fms_stream_t stream);
 
+/* ------------------------- split along T as one kernel per direction (one box, peer memory) ---- */
+
+/*
+ * The whole split-along-T step of one rank in ONE launch per direction: carry pass, exchange of
+ * the carries over peer-mapped memory and scan pass, fused row by row, so that the second pass
+ * finds the row's operands still in L2 and the block costs the HBM traffic of an unsplit scan
+ * (3 element passes forward, 5 backward, instead of 5 and 7 with fms_plain_reduce + exchange +
+ * fms_plain_forward).  No reference counterpart (the reference is single-GPU and stops at 131072
+ * steps, fm/scan/fm_scan.cuh:323-329).
+ *
+ * Every rank owns a buffer of fms_tsplit_exchange_bytes(rows, world) that all ranks have mapped
+ * (symmetric memory / CUDA IPC), zeroed once before first use; `peer_buffers` is a HOST array of
+ * the `world` device pointers as mapped in this process.  Rank k holds time block k of every row:
+ * gates, tokens, states ... are this rank's (rows, T) blocks.  All ranks call with the same
+ * `exchange` number, counted from 1 per direction, and must be running concurrently on DIFFERENT
+ * GPUs (the kernels wait on one another; never run two ranks as separate launches on one GPU
+ * unless an earlier rank's kernel has finished before a later one starts).
+ *
+ * fms_tsplit_forward:  h0 (rank 0 only, nullable) is the state before the first block;
+ *                      h_in_out (rows, fp32) receives the carry that entered this block.
+ * fms_tsplit_backward: h_in is that carry; grad_h0 (nullable, meaningful on rank 0) receives the
+ *                      carry leaving this block towards earlier time, a_0 * delta_0.
+ *
+ * Requirements: T * element size a multiple of 16 bytes and 16-byte aligned tensors
+ * (FMS_ERR_MISALIGNED otherwise: use the three-step path), T >= 1.  Peer traffic is plain stores
+ * into peer buffers and local loads.  Waits are bounded by max_wait_seconds (<= 30; 2 if out of
+ * range); faults are reported in the local buffer's status word
+ * (fms_tsplit_exchange_status_offset) with the FMS_PEER_ERR_* codes, the kernel always ends, and
+ * the outputs of rows whose carries did not arrive are computed from a zero carry.  Slot
+ * generations and acknowledgements work as for fms_peer_publish: a rank runs at most one exchange
+ * ahead of the slowest rank that reads from it.
+ */
+size_t fms_tsplit_exchange_bytes(int64_t rows, int world);
+size_t fms_tsplit_exchange_status_offset(int64_t rows, int world);
+int fms_tsplit_forward(const void *gates, const void *tokens, const float *h0, void *states, float *h_in_out,
+                       int64_t rows, int64_t T, int dtype, void *const *peer_buffers, int world, int rank,
+                       uint32_t exchange, double max_wait_seconds, fms_stream_t stream);
+int fms_tsplit_backward(const void *gates, const void *states, const void *grad_states, const float *h_in,
+                        void *grad_gates, void *grad_tokens, float *grad_h0, int64_t rows, int64_t T, int dtype,
+                        void *const *peer_buffers, int world, int rank, uint32_t exchange, double max_wait_seconds,
+                        fms_stream_t stream);
+
 /* ------------------------------------------------------- host-buffer pipeline (one GPU) ---- */
 
 /*

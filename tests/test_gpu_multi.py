@@ -26,6 +26,11 @@ def _free_port():
         return s.getsockname()[1]
 
 
+def _length(mode):
+    """Total sequence length: blocks of the fused kernels must be 16-byte aligned for every world size."""
+    return 8 * 1032 if mode == "time_fused" else 8 * 1031
+
+
 def _worker(rank, world, port, mode, storage, out_dir):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -37,7 +42,7 @@ def _worker(rank, world, port, mode, storage, out_dir):
         from fm_b200.time_split import fm_scan_time_split
         from tests import gpu_util as G
 
-        B, D, T = 2, 24, 8 * 1031
+        B, D, T = 2, 24, _length(mode)
         a, x, Gd, h0 = H.make_inputs(B * D, T, 123, "sigmoid+3", storage, with_h0=True)
         if mode == "time_peer_forward_only":
             # inference-style loop: forward exchanges only, one rank lagging behind the others
@@ -73,6 +78,9 @@ def _worker(rank, world, port, mode, storage, out_dir):
             if mode == "time_peer":
                 from fm_b200.peer_exchange import PeerCarryExchange
                 exchange = PeerCarryExchange(B * D)
+            if mode == "time_fused":
+                from fm_b200.peer_exchange import FusedTimeSplit
+                exchange = FusedTimeSplit(B * D)
             h = fm_scan_time_split(ad, xd, h0d, exchange=exchange)
             h.backward(gd)
             if exchange is not None:
@@ -117,13 +125,14 @@ def test_row_sharding_is_bit_identical_to_one_gpu(tmp_path, storage):
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("transport", ["time", "time_peer"])
+@pytest.mark.parametrize("transport", ["time", "time_peer", "time_fused"])
 @pytest.mark.parametrize("storage", ["f32", "bf16"])
 def test_time_split_over_nccl_matches_oracle(tmp_path, storage, transport):
-    """transport "time": NCCL all-gather; "time_peer": peer stores + flags in symmetric memory."""
+    """transport "time": NCCL all-gather; "time_peer": peer stores + flags in symmetric memory;
+    "time_fused": one kernel per direction with the exchange inside it."""
     world = min(_ngpu(), 8)
     parts = _run(world, transport, storage, tmp_path)
-    B, D, T = 2, 24, 8 * 1031
+    B, D, T = 2, 24, _length(transport)
     a, x, Gd, h0 = H.make_inputs(B * D, T, 123, "sigmoid+3", storage, with_h0=True)
     f64 = np.float64
     h = np.concatenate([p["h"] for p in parts], 1)

@@ -659,6 +659,76 @@ def run_time_split(args):
         dist.destroy_process_group()
 
 
+def run_time_split_block(args):
+    """Profiler case: ONE rank's block of the long sequence split along T -- (rows, 32768) fp32, the
+    per-GPU share of (1,4096,262144) over 8 ranks -- through the fused kernels with a world of 1 (no
+    peers, nothing to wait for), beside the three-launch path on the same data.  One GPU."""
+    import ctypes
+
+    import torch
+
+    from fm_b200 import capi
+    from fm_b200.ops import CudaScanOps as ops
+    from fm_b200.peer_exchange import _bind_fused
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    L = _bind_fused()
+    R, T = args.rows or 4096, 32768
+    gen = torch.Generator(device=dev).manual_seed(1004)
+    a = torch.sigmoid(torch.randn(R, T, device=dev, generator=gen) + 3.0)
+    x = torch.randn(R, T, device=dev, generator=gen)
+    G = torch.randn(R, T, device=dev, generator=gen)
+    h, ga, gx = torch.empty_like(a), torch.empty_like(a), torch.empty_like(a)
+    hin = torch.empty(R, device=dev)
+    buf = torch.zeros(int(L.fms_tsplit_exchange_bytes(R, 1)), dtype=torch.uint8, device=dev)
+    ptrs = (ctypes.c_void_p * 1)(buf.data_ptr())
+    st = torch.cuda.current_stream().cuda_stream
+    count = [0]
+
+    def fused():
+        count[0] += 1
+        rc = L.fms_tsplit_forward(a.data_ptr(), x.data_ptr(), None, h.data_ptr(), hin.data_ptr(), R, T, capi.FMS_F32,
+                                  ptrs, 1, 0, count[0], 1.0, st)
+        rc = rc or L.fms_tsplit_backward(a.data_ptr(), h.data_ptr(), G.data_ptr(), hin.data_ptr(), ga.data_ptr(),
+                                         gx.data_ptr(), None, R, T, capi.FMS_F32, ptrs, 1, 0, count[0], 1.0, st)
+        assert rc == 0, capi.status_string(rc)
+
+    def three_launch():
+        P, S = ops.reduce(a, x)
+        hh = ops.forward(a, x, torch.zeros_like(S))
+        ops.reduce_reverse(a, G)
+        ops.backward(a, hh, G, None, None)
+
+    def timed(fn, steps):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        s0, s1 = _cuda_events(2)
+        s0.record()
+        for _ in range(steps):
+            fn()
+        s1.record()
+        torch.cuda.synchronize()
+        return s0.elapsed_time(s1) / steps
+
+    K = args.steps
+    fused_ms = timed(fused, K)
+    three_ms = timed(three_launch, K)
+    n = R * T
+    peak, kind = measured_peak()
+    line = {"metric": "scan fwd+bwd elements/s (one block of the split along T)", "value": n / (fused_ms * 1e-3),
+            "unit": UNIT, "n_gpus": 1, "steps": K, "warmup": max(3, args.warmup), "ms_per_step": fused_ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "one time block (rows,T)=(%d,%d) fp32 of the split along T, world of 1" % (R, T)},
+            "gpu_launches": 2 * K,
+            "three_launch_ms": three_ms,
+            "roofline_fwd_bwd": {"algorithmic_GBs": 8 * 4 * n / (fused_ms * 1e-3) / 1e9,
+                                 "three_launch_algorithmic_GBs": 8 * 4 * n / (three_ms * 1e-3) / 1e9,
+                                 "peak": peak, "peak_kind": kind}}
+    print(json.dumps(line), flush=True)
+
+
 def run_fm_mode(args):
     """Secondary workload: the reference's own operator and demo shape, gates (1,32,8192),
     tokens (1,D,8192) -> states (1,32,D,8192), bf16 (fm_test.ipynb:29-33 uses D = 2048).
@@ -877,8 +947,9 @@ def main():
     ap.add_argument("--scaling", choices=["weak", "strong"], default=None,
                     help="N > 1: strong (default) splits the fixed 32768 rows over the ranks; weak gives "
                          "every rank all 32768")
-    ap.add_argument("--workload", choices=["c3", "c4", "fm", "btd"], default="c3",
+    ap.add_argument("--workload", choices=["c3", "c4", "c4block", "fm", "btd"], default="c3",
                     help="c3: the headline row-sharded workload; c4: the long sequence split along T; "
+                         "c4block: one rank's block of c4 through the fused kernels (profiler case); "
                          "fm: the reference's (B,M,L)x(B,D,L)->(B,M,D,L) operator at its demo shape; "
                          "btd: the plain scan on channel-last (B,T,D) tensors")
     ap.add_argument("--exchange", choices=["nccl", "peer", "fused"], default="fused",
@@ -895,6 +966,8 @@ def main():
         run_reference_arm(args)
     elif args.workload == "c4":
         run_time_split(args)
+    elif args.workload == "c4block":
+        run_time_split_block(args)
     elif args.workload == "fm":
         run_fm_mode(args)
     elif args.workload == "btd":

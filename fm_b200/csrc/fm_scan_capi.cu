@@ -82,6 +82,14 @@ inline const Tune &tune() {
     return g_tune;
 }
 
+// The default build holds the launch shapes the choices below can reach; -DFMS_ALL_VARIANTS adds
+// every (warps per row, tiles per step) combination the FMS_TUNE_* knobs can name (tuning builds).
+#ifdef FMS_ALL_VARIANTS
+constexpr bool kAllVariants = true;
+#else
+constexpr bool kAllVariants = false;
+#endif
+
 struct Problem {
     int64_t rows, T;
     bool aligned;  // every row of every tensor starts on a 16-byte boundary
@@ -195,9 +203,11 @@ int launch_forward(const Problem &pb, const Split &sp, const void *gates, const 
                    const float *h0, void *states, float *h_last, float *P, cudaStream_t st) {
     const int64_t units = pb.rows * sp.nseg;
     int K = sp.nseg > 1 ? 1 : choose_coop(units, pb.T, sizeof(S), tune().fwd_k);
-    // masked path (measured on 2304 rows x 16385 fp16): one warp per row is fastest forward
-    if (!pb.aligned && tune().fwd_k == 0) K = 1;
-    const int unroll = choose_unroll(pb.T, sizeof(S), K, tune().fwd_u);
+    // masked path (measured on 2304 rows x 16385 fp16): one warp per row is fastest forward when
+    // rows are plentiful; with few rows the warps-per-row choice above keeps the GPU filled
+    if (!pb.aligned && tune().fwd_k == 0 && units >= 1024) K = 1;
+    int unroll = choose_unroll(pb.T, sizeof(S), K, tune().fwd_u);
+    if (!kAllVariants && K > 1) unroll = 4;
     const int64_t ctas = K == 1 ? (units + fms::kWarpsPerCta - 1) / fms::kWarpsPerCta : units;
     if (ctas > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;
     const int64_t seg_len = sp.nseg == 1 ? pb.T : sp.seg_len;
@@ -224,16 +234,22 @@ int launch_forward(const Problem &pb, const Split &sp, const void *gates, const 
         case 4: FMS_LAUNCH_FWD(G, UU, 4); break;                                                   \
         default: FMS_LAUNCH_FWD(G, UU, 8); break;                                                  \
     }
+#ifdef FMS_ALL_VARIANTS
+#define FMS_LAUNCH_FWD_KLOW(G, UU) FMS_LAUNCH_FWD_K(G, UU)
+#else  // fewer than 4 tiles per step is only ever chosen with one warp per row
+#define FMS_LAUNCH_FWD_KLOW(G, UU) FMS_LAUNCH_FWD(G, UU, 1);
+#endif
     if (sp.nseg > 1) {  // split path: units are plentiful by construction, one warp each
         if (pb.aligned) FMS_LAUNCH_FWD_S(false, 2, 1, true);
         else FMS_LAUNCH_FWD_S(true, 2, 1, true);
     } else if (pb.aligned) {
         if (unroll == 4) { FMS_LAUNCH_FWD_K(false, 4) }
-        else if (unroll == 2) { FMS_LAUNCH_FWD_K(false, 2) }
-        else { FMS_LAUNCH_FWD_K(false, 1) }
+        else if (unroll == 2) { FMS_LAUNCH_FWD_KLOW(false, 2) }
+        else { FMS_LAUNCH_FWD_KLOW(false, 1) }
     } else {
         FMS_LAUNCH_FWD_K(true, 2)
     }
+#undef FMS_LAUNCH_FWD_KLOW
 #undef FMS_LAUNCH_FWD_K
 #undef FMS_LAUNCH_FWD
 #undef FMS_LAUNCH_FWD_S
@@ -246,11 +262,12 @@ int launch_backward(const Problem &pb, const Split &sp, const void *gates, const
                     void *grad_tokens, float *grad_h0, float *P, cudaStream_t st) {
     const int64_t units = pb.rows * sp.nseg;
     int K = sp.nseg > 1 ? 1 : choose_coop(units, pb.T, sizeof(S), tune().bwd_k);
-    // masked path (same measurement): two warps per row are fastest backward
-    if (!pb.aligned && tune().bwd_k == 0) K = std::min(K, 2);
+    // masked path (same measurement): two warps per row are fastest backward when rows are plentiful
+    if (!pb.aligned && tune().bwd_k == 0 && units >= 1024) K = std::min(K, 2);
     // one warp per row: 2 tiles per step (4 costs occupancy: 141+ registers for three inputs)
-    const int unroll = K == 1 ? std::min(2, choose_unroll(pb.T, sizeof(S), K, tune().bwd_u))
-                              : choose_unroll(pb.T, sizeof(S), K, tune().bwd_u);
+    int unroll = K == 1 ? std::min(2, choose_unroll(pb.T, sizeof(S), K, tune().bwd_u))
+                        : choose_unroll(pb.T, sizeof(S), K, tune().bwd_u);
+    if (!kAllVariants && K > 1) unroll = 4;
     const int64_t ctas = K == 1 ? (units + fms::kWarpsPerCta - 1) / fms::kWarpsPerCta : units;
     if (ctas > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;
     const int64_t seg_len = sp.nseg == 1 ? pb.T : sp.seg_len;
@@ -278,16 +295,30 @@ int launch_backward(const Problem &pb, const Split &sp, const void *gates, const
         case 4: FMS_LAUNCH_BWD(G, UU, 4); break;                                                   \
         default: FMS_LAUNCH_BWD(G, UU, 8); break;                                                  \
     }
+#ifdef FMS_ALL_VARIANTS
+#define FMS_LAUNCH_BWD_KLOW(G, UU) FMS_LAUNCH_BWD_K(G, UU)
+#define FMS_LAUNCH_BWD_KHIGH(G, UU) FMS_LAUNCH_BWD_K(G, UU)
+#else  // one warp per row walks at most 2 tiles per step, several warps per row always 4
+#define FMS_LAUNCH_BWD_KLOW(G, UU) FMS_LAUNCH_BWD(G, UU, 1);
+#define FMS_LAUNCH_BWD_KHIGH(G, UU)                                                                \
+    switch (K) {                                                                                   \
+        case 2: FMS_LAUNCH_BWD(G, UU, 2); break;                                                   \
+        case 4: FMS_LAUNCH_BWD(G, UU, 4); break;                                                   \
+        default: FMS_LAUNCH_BWD(G, UU, 8); break;                                                  \
+    }
+#endif
     if (sp.nseg > 1) {
         if (pb.aligned) FMS_LAUNCH_BWD_S(false, 2, 1, true);
         else FMS_LAUNCH_BWD_S(true, 1, 1, true);
     } else if (pb.aligned) {
-        if (unroll == 4) { FMS_LAUNCH_BWD_K(false, 4) }
-        else if (unroll == 2) { FMS_LAUNCH_BWD_K(false, 2) }
-        else { FMS_LAUNCH_BWD_K(false, 1) }
+        if (unroll == 4) { FMS_LAUNCH_BWD_KHIGH(false, 4) }
+        else if (unroll == 2) { FMS_LAUNCH_BWD_KLOW(false, 2) }
+        else { FMS_LAUNCH_BWD_KLOW(false, 1) }
     } else {
         FMS_LAUNCH_BWD_K(true, 1)
     }
+#undef FMS_LAUNCH_BWD_KHIGH
+#undef FMS_LAUNCH_BWD_KLOW
 #undef FMS_LAUNCH_BWD_K
 #undef FMS_LAUNCH_BWD
 #undef FMS_LAUNCH_BWD_S
@@ -429,7 +460,8 @@ template <typename S>
 int launch_fm_forward(const FmShape &sh, bool aligned, const void *gates, const void *tokens, const float *h0,
                       void *states, cudaStream_t st) {
     const int K = choose_coop(sh.rows, sh.L, sizeof(S), tune().fwd_k);
-    const int unroll = std::min(2, choose_unroll(sh.L, sizeof(S), K, tune().fwd_u));
+    int unroll = std::min(2, choose_unroll(sh.L, sizeof(S), K, tune().fwd_u));
+    if (!kAllVariants && K > 1) unroll = 2;
     const int64_t ctas = K == 1 ? (sh.rows + fms::kWarpsPerCta - 1) / fms::kWarpsPerCta : sh.rows;
     if (ctas > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;
 #define FMS_LAUNCH_FM_FWD(G, UU, KK)                                                               \
@@ -446,7 +478,11 @@ int launch_fm_forward(const FmShape &sh, bool aligned, const void *gates, const 
     }
     if (!aligned) { FMS_LAUNCH_FM_FWD_K(true, 1) }
     else if (unroll == 2) { FMS_LAUNCH_FM_FWD_K(false, 2) }
+#ifdef FMS_ALL_VARIANTS
     else { FMS_LAUNCH_FM_FWD_K(false, 1) }
+#else
+    else { FMS_LAUNCH_FM_FWD(false, 1, 1); }
+#endif
 #undef FMS_LAUNCH_FM_FWD_K
 #undef FMS_LAUNCH_FM_FWD
     return check_launch();
@@ -460,7 +496,8 @@ int launch_fm_backward(const FmShape &sh, bool aligned, const void *gates, const
                        float *acc_tokens, float *grad_h0, cudaStream_t st, void *full_gates = nullptr,
                        void *full_tokens = nullptr) {
     const int K = choose_coop(sh.rows, sh.L, sizeof(S), tune().bwd_k);
-    const int unroll = std::min(2, choose_unroll(sh.L, sizeof(S), K, tune().bwd_u));
+    int unroll = std::min(2, choose_unroll(sh.L, sizeof(S), K, tune().bwd_u));
+    if (!kAllVariants && K > 1) unroll = 2;
     const int64_t ctas = K == 1 ? (sh.rows + fms::kWarpsPerCta - 1) / fms::kWarpsPerCta : sh.rows;
     if (ctas > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;
 #define FMS_LAUNCH_FM_BWD(G, UU, KK)                                                               \
@@ -479,7 +516,11 @@ int launch_fm_backward(const FmShape &sh, bool aligned, const void *gates, const
     }
     if (!aligned) { FMS_LAUNCH_FM_BWD_K(true, 1) }
     else if (unroll == 2) { FMS_LAUNCH_FM_BWD_K(false, 2) }
+#ifdef FMS_ALL_VARIANTS
     else { FMS_LAUNCH_FM_BWD_K(false, 1) }
+#else
+    else { FMS_LAUNCH_FM_BWD(false, 1, 1); }
+#endif
 #undef FMS_LAUNCH_FM_BWD_K
 #undef FMS_LAUNCH_FM_BWD
     return check_launch();
@@ -522,9 +563,13 @@ int launch_fm_backward_blocked(const FmShape &sh, const void *gates, const void 
             static_cast<const S *>(states), static_cast<const S *>(grad_states), h0, acc_gates,     \
             acc_tokens, grad_h0, sh.M, sh.D, sh.L, m_blocks, d_blocks);                             \
     } while (0)
+#ifdef FMS_ALL_VARIANTS
     if (pd == 2) FMS_LAUNCH_FM_BLOCKED(2);
     else if (pd == 8) FMS_LAUNCH_FM_BLOCKED(8);
-    else FMS_LAUNCH_FM_BLOCKED(4);
+    else
+#endif
+        FMS_LAUNCH_FM_BLOCKED(4);
+    (void)pd;
 #undef FMS_LAUNCH_FM_BLOCKED
     return check_launch();
 }
@@ -777,13 +822,20 @@ int launch_fm_layer_backward(const FmShape &sh, const void *gates, const void *t
                                           ext_, p1, dotc, rinv, rnorm, h0, acc_g, acc_x, grad_h0, sh.M, sh.D,    \
                                           sh.L, m_blocks, d_blocks);                                    \
     } while (0)
+    (void)pd;
     if (ext) {
+#ifdef FMS_ALL_VARIANTS
         if (pd == 2) FMS_LAUNCH_LAYER_BWD(true, 2);
-        else FMS_LAUNCH_LAYER_BWD(true, 4);
+        else
+#endif
+            FMS_LAUNCH_LAYER_BWD(true, 4);
     } else {
+#ifdef FMS_ALL_VARIANTS
         if (pd == 2) FMS_LAUNCH_LAYER_BWD(false, 2);
         else if (pd == 8) FMS_LAUNCH_LAYER_BWD(false, 8);
-        else FMS_LAUNCH_LAYER_BWD(false, 4);
+        else
+#endif
+            FMS_LAUNCH_LAYER_BWD(false, 4);
     }
 #undef FMS_LAUNCH_LAYER_BWD
     if (int rc = check_launch()) return rc;
@@ -1011,6 +1063,18 @@ FMS_EXPORT int64_t fms_plain_split_segments(int64_t rows, int64_t T, int dtype) 
     if (dtype != FMS_F32 && dtype != FMS_F16 && dtype != FMS_BF16) return 1;
     if (!sizes_ok(rows, T)) return 1;
     return plan_split(rows, T).nseg;
+}
+
+// Measured on B200 (fwd+bwd, CUDA events, L2 flushed): with K warps sharing a row the unsplit
+// kernels beat the three-launch split down to 64 rows at every length tried (8192 ... 131072;
+// e.g. 64 rows x 131072 fp32: 99 us against 110 us; 256 x 32768: 52 against 97; 2304 x 16385 fp16:
+// 127 against 242).  The split pays only when there are too few rows to give every SM a CTA of
+// K warps.
+FMS_EXPORT int fms_plain_split_recommended(int64_t rows, int64_t T, int dtype) {
+    if (dtype != FMS_F32 && dtype != FMS_F16 && dtype != FMS_BF16) return 0;
+    if (!sizes_ok(rows, T)) return 0;
+    if (plan_split(rows, T).nseg < 2) return 0;
+    return rows * 4 <= sm_count() ? 1 : 0;
 }
 
 FMS_EXPORT size_t fms_plain_split_workspace_bytes(int64_t rows, int64_t T, int dtype) {

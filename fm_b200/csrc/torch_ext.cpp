@@ -105,7 +105,7 @@ at::Tensor fm_scan_forward(const at::Tensor &gates, const at::Tensor &tokens,
     at::Tensor h0 = carry_f32(initial_state, rows, gates, "initial_state");
     auto stream = at::cuda::getCurrentCUDAStream().stream();
     // A handful of very long rows: cut them into segments so the whole GPU works (needs scratch).
-    const size_t scratch = fms_plain_split_workspace_bytes(rows, T, dtype);
+    const size_t scratch = fms_plain_split_recommended(rows, T, dtype) ? fms_plain_split_workspace_bytes(rows, T, dtype) : 0;
     if (scratch > 0) {
         at::Tensor ws = at::empty({static_cast<int64_t>(scratch)}, gates.options().dtype(at::kByte));
         check_status(fms_plain_forward_split(gates.data_ptr(), tokens.data_ptr(), fptr(h0), out.data_ptr(),
@@ -151,7 +151,7 @@ void fm_scan_backward_ex(const at::Tensor &gates, const at::Tensor &outGrad,
         gh0 = grad_initial_state.data_ptr<float>();
     }
     auto stream = at::cuda::getCurrentCUDAStream().stream();
-    const size_t scratch = fms_plain_split_workspace_bytes(rows, T, dtype);
+    const size_t scratch = fms_plain_split_recommended(rows, T, dtype) ? fms_plain_split_workspace_bytes(rows, T, dtype) : 0;
     if (scratch > 0) {
         at::Tensor ws = at::empty({static_cast<int64_t>(scratch)}, gates.options().dtype(at::kByte));
         check_status(fms_plain_backward_split(gates.data_ptr(), cached_output.data_ptr(), outGrad.data_ptr(),

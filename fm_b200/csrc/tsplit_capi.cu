@@ -4,6 +4,7 @@
 
 #include "fm_scan_b200.h"
 #include "tsplit_kernels.cuh"
+#include "tsplit_tma_kernels.cuh"
 
 #define FMS_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -38,11 +39,20 @@ int env_int(const char *name, int dflt) {
 // fewer rows in flight, which is what lets pass B find its operands in L2 (rows in flight x row
 // bytes x tensors must stay well inside the 126 MB).  Read once per process.
 struct TsTune {
-    int k, u, bwd_u, ctas_per_sm;
+    int k, u, bwd_u, ctas_per_sm, staged;
 };
 const TsTune &ts_tune() {
-    static const TsTune t = {env_int("FMS_TUNE_TSPLIT_K", 8), env_int("FMS_TUNE_TSPLIT_U", 4),
-                             env_int("FMS_TUNE_TSPLIT_BWD_U", 2), env_int("FMS_TUNE_TSPLIT_CTAS_PER_SM", 2)};
+    // staged = 1 (default): operands come through the bulk-copy shared-memory ring, one CTA per SM
+    // (K defaults to 16 there); 0: the register-prefetch kernels (K defaults to 8, two CTAs per SM)
+    static const TsTune t = []() {
+        TsTune v;
+        v.staged = env_int("FMS_TUNE_TSPLIT_STAGED", 1);
+        v.k = env_int("FMS_TUNE_TSPLIT_K", v.staged ? 16 : 8);
+        v.u = env_int("FMS_TUNE_TSPLIT_U", 4);
+        v.bwd_u = env_int("FMS_TUNE_TSPLIT_BWD_U", 2);
+        v.ctas_per_sm = env_int("FMS_TUNE_TSPLIT_CTAS_PER_SM", 2);
+        return v;
+    }();
     return t;
 }
 
@@ -84,9 +94,58 @@ int make_exchange(fms::TsExchange &ex, void *const *peer_buffers, int64_t rows, 
     return FMS_OK;
 }
 
+// Staged kernels: one CTA per SM, every CTA the same number of rows.
+inline int64_t staged_grid(int64_t rows) {
+    const int64_t resident = sm_count();
+    const int64_t q = (rows + resident - 1) / resident;
+    return (rows + q - 1) / q;
+}
+
+template <typename S>
+int launch_forward_staged(const void *gates, const void *tokens, const float *h0, void *states, float *h_in_out,
+                          const fms::TsExchange &ex, int64_t rows, int64_t T, cudaStream_t st) {
+#define FMS_TS_FWD_STAGED(UU, KK, NS)                                                                         \
+    do {                                                                                                     \
+        auto kern = fms::tsplit_forward_tma_kernel<S, UU, KK, NS>;                                           \
+        constexpr size_t smem = fms::TsRing<S, UU, KK, 2, NS>::kBytes;                                       \
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != \
+            cudaSuccess)                                                                                     \
+            return FMS_ERR_LAUNCH;                                                                           \
+        kern<<<static_cast<unsigned>(staged_grid(rows)), (KK + 1) * 32, smem, st>>>(                         \
+            static_cast<const S *>(gates), static_cast<const S *>(tokens), h0, static_cast<S *>(states), h_in_out, \
+            ex, rows, T);                                                                                    \
+    } while (0)
+    if (ts_tune().k == 8) FMS_TS_FWD_STAGED(4, 8, 6);
+    else FMS_TS_FWD_STAGED(4, 16, 3);
+#undef FMS_TS_FWD_STAGED
+    return cudaGetLastError() == cudaSuccess ? FMS_OK : FMS_ERR_LAUNCH;
+}
+
+template <typename S>
+int launch_backward_staged(const void *gates, const void *states, const void *grad_states, const float *h_in,
+                           void *grad_gates, void *grad_tokens, float *grad_h0, const fms::TsExchange &ex,
+                           int64_t rows, int64_t T, cudaStream_t st) {
+#define FMS_TS_BWD_STAGED(UU, KK, NS)                                                                         \
+    do {                                                                                                     \
+        auto kern = fms::tsplit_backward_tma_kernel<S, UU, KK, NS>;                                          \
+        constexpr size_t smem = fms::TsRing<S, UU, KK, 3, NS>::kBytes;                                       \
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != \
+            cudaSuccess)                                                                                     \
+            return FMS_ERR_LAUNCH;                                                                           \
+        kern<<<static_cast<unsigned>(staged_grid(rows)), (KK + 1) * 32, smem, st>>>(                         \
+            static_cast<const S *>(gates), static_cast<const S *>(states), static_cast<const S *>(grad_states), \
+            h_in, static_cast<S *>(grad_gates), static_cast<S *>(grad_tokens), grad_h0, ex, rows, T);        \
+    } while (0)
+    if (ts_tune().k == 8) FMS_TS_BWD_STAGED(4, 8, 4);
+    else FMS_TS_BWD_STAGED(2, 16, 4);
+#undef FMS_TS_BWD_STAGED
+    return cudaGetLastError() == cudaSuccess ? FMS_OK : FMS_ERR_LAUNCH;
+}
+
 template <typename S>
 int launch_forward(const void *gates, const void *tokens, const float *h0, void *states, float *h_in_out,
                    const fms::TsExchange &ex, int64_t rows, int64_t T, cudaStream_t st) {
+    if (ts_tune().staged) return launch_forward_staged<S>(gates, tokens, h0, states, h_in_out, ex, rows, T, st);
     const int K = ts_tune().k, U = ts_tune().u;
 #define FMS_TS_FWD(UU, KK)                                                                                   \
     do {                                                                                                     \
@@ -111,6 +170,9 @@ template <typename S>
 int launch_backward(const void *gates, const void *states, const void *grad_states, const float *h_in,
                     void *grad_gates, void *grad_tokens, float *grad_h0, const fms::TsExchange &ex, int64_t rows,
                     int64_t T, cudaStream_t st) {
+    if (ts_tune().staged)
+        return launch_backward_staged<S>(gates, states, grad_states, h_in, grad_gates, grad_tokens, grad_h0, ex, rows,
+                                         T, st);
     // three input streams: 4 tiles per step need 189 registers (one CTA of 8 warps per SM), 2 need 128
     const int K = ts_tune().k, U = ts_tune().bwd_u;
 #define FMS_TS_BWD(UU, KK)                                                                                   \

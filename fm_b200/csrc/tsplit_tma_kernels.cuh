@@ -1,0 +1,488 @@
+// The fused split-along-T kernels of tsplit_kernels.cuh with their operands staged through a
+// shared-memory ring by bulk asynchronous copies (cp.async.bulk + mbarrier, the 1-D form of TMA).
+//
+// Why: the second pass of a row finds its operands in L2 only while few rows are in flight (148
+// rows x 256 KB on the long-sequence workload; with 296 rows most of it has been evicted).  One
+// CTA per SM with register prefetch keeps too few bytes in flight to fill HBM from so few rows.
+// Here a producer warp streams the row into a ring of STAGES x (one super-tile of every operand)
+// -- up to ~200 KB per SM in flight, independent of the consumers' barriers, of the peer wait
+// between the two passes and of row boundaries -- and K consumer warps take their tiles from
+// shared memory.  A stage is K*U tiles of 512 B per operand; consumers release a stage as soon as
+// its tiles are in registers.
+//
+// The copies read THIS GPU's memory only and are not multicast.  Every mbarrier wait is bounded;
+// a wait that runs out raises the CTA's fault flag, every role stops at its next wait, the
+// producer drains the copies still in flight (bounded) and the kernel ends with the fault in the
+// status word.
+#pragma once
+
+#include "tsplit_kernels.cuh"
+
+namespace fms {
+
+constexpr int FMS_TSPLIT_ERR_PIPELINE = 5;  // status word: an mbarrier wait of the staging ring ran out
+constexpr unsigned kTsMbarSpins = 1u << 26;  // try_wait polls before a ring wait gives up (seconds)
+
+__device__ __forceinline__ unsigned ts_smem_addr(const void *p) {
+    return static_cast<unsigned>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void ts_mbar_init(uint64_t *bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(ts_smem_addr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void ts_mbar_expect_tx(uint64_t *bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(ts_smem_addr(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void ts_mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(ts_smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ bool ts_mbar_try_wait(uint64_t *bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(ts_smem_addr(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait; false = gave up (or another role already raised the ring fault).
+__device__ __forceinline__ bool ts_mbar_wait(uint64_t *bar, unsigned parity, volatile int *fault) {
+    for (unsigned spin = 0; spin < kTsMbarSpins; ++spin) {
+        if (ts_mbar_try_wait(bar, parity)) return true;
+        if ((spin & 1023u) == 1023u && *fault == FMS_TSPLIT_ERR_PIPELINE) return false;
+    }
+    return false;
+}
+// A role whose ring wait ran out: raise the CTA's fault flag and record it in the status word.
+__device__ __forceinline__ void ts_ring_fault(const TsExchange &ex, volatile int *fault) {
+    *fault = FMS_TSPLIT_ERR_PIPELINE;
+    atomicCAS(reinterpret_cast<uint32_t *>(ex.buf[ex.rank] + ex.lay.status_offset()), 0u,
+              static_cast<uint32_t>(FMS_TSPLIT_ERR_PIPELINE));
+}
+// Bulk copy global -> shared of this CTA, completion counted in bytes on `bar`.
+__device__ __forceinline__ void ts_bulk_load(void *smem_dst, const void *gmem_src, unsigned bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     ts_smem_addr(smem_dst)),
+                 "l"(gmem_src), "r"(bytes), "r"(ts_smem_addr(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void ts_consumer_sync(int threads) {
+    asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
+}
+
+// Shared memory of one CTA: NT operands per stage, each SUPER elements of S.
+template <typename S, int U, int K, int NT, int STAGES>
+struct TsRing {
+    static constexpr int E = Store<S>::E;
+    static constexpr int TILE = 32 * E;
+    static constexpr int SUPER = TILE * U * K;
+    static constexpr size_t kStageBytes = static_cast<size_t>(NT) * SUPER * sizeof(S);
+    static constexpr size_t kBytes = STAGES * kStageBytes + 2 * STAGES * sizeof(uint64_t) + 256;
+};
+
+// ---------------------------------------------------------------- forward --------------------
+template <typename S, int U, int K, int STAGES>
+__global__ void __launch_bounds__((K + 1) * 32, 1)
+tsplit_forward_tma_kernel(const S *__restrict__ gates, const S *__restrict__ tokens, const float *__restrict__ h0,
+                          S *__restrict__ states, float *__restrict__ h_in_out, TsExchange ex, int64_t R, int64_t T) {
+    using Ring = TsRing<S, U, K, 2, STAGES>;
+    constexpr int E = Ring::E, TILE = Ring::TILE;
+    constexpr int64_t SUPER = Ring::SUPER;
+    extern __shared__ __align__(128) unsigned char ts_smem[];
+    S *stage_base = reinterpret_cast<S *>(ts_smem);
+    uint64_t *full = reinterpret_cast<uint64_t *>(ts_smem + STAGES * Ring::kStageBytes);
+    uint64_t *empty = full + STAGES;
+    __shared__ float2 agg[2][K];
+    __shared__ float s_carry;
+    __shared__ int s_fault;
+    const int lane = threadIdx.x & 31;
+    const int w = threadIdx.x >> 5;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ts_mbar_init(full + s, 1);
+            ts_mbar_init(empty + s, K);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        s_fault = ts_wait_acks(ex, 0);
+        if (s_fault)
+            atomicCAS(reinterpret_cast<uint32_t *>(ex.buf[ex.rank] + ex.lay.status_offset()), 0u,
+                      static_cast<uint32_t>(s_fault));
+    }
+    __syncthreads();
+    const bool publish_ok = s_fault == 0;
+    const int64_t ngroups = (T + SUPER - 1) / SUPER;
+
+    if (w == K) {
+        // ---------------- producer: one lane streams (row, pass, group) in consumption order
+        if (lane == 0) {
+            unsigned n = 0;
+            bool alive = true;
+            for (int64_t row = blockIdx.x; row < R && alive; row += gridDim.x) {
+                const int64_t off = row * T;
+                for (int pass = 0; pass < 2 && alive; ++pass) {
+                    for (int64_t g = 0; g < ngroups; ++g, ++n) {
+                        const int s = static_cast<int>(n % STAGES);
+                        if (!ts_mbar_wait(empty + s, ((n / STAGES) & 1u) ^ 1u, &s_fault)) {
+                            alive = false;
+                            break;
+                        }
+                        const int64_t e0 = g * SUPER;
+                        const unsigned bytes = static_cast<unsigned>(min(SUPER, T - e0) * sizeof(S));
+                        S *dst = stage_base + static_cast<size_t>(s) * 2 * SUPER;
+                        ts_mbar_expect_tx(full + s, 2 * bytes);
+                        ts_bulk_load(dst, gates + off + e0, bytes, full + s);
+                        ts_bulk_load(dst + SUPER, tokens + off + e0, bytes, full + s);
+                    }
+                }
+            }
+            if (!alive) {
+                ts_ring_fault(ex, &s_fault);
+                // drain: every stage that was filled completes its copies within the bound
+                for (unsigned k = n > STAGES ? n - STAGES : 0; k < n; ++k) {
+                    const int s = static_cast<int>(k % STAGES);
+                    for (unsigned spin = 0; spin < kTsMbarSpins && !ts_mbar_try_wait(full + s, (k / STAGES) & 1u); ++spin) {
+                    }
+                }
+            }
+        }
+    } else {
+        // ---------------- consumers: K warps, the arithmetic of tsplit_forward_kernel.
+        // A warp whose ring wait ran out keeps walking the loops (every warp must meet every named
+        // barrier) but touches neither the ring nor global memory any more.
+        const int64_t e_lane = static_cast<int64_t>(w) * (TILE * U) + lane * E;  // element offset inside a stage
+        unsigned n = 0, it = 0;
+        bool alive = true;
+        for (int64_t row = blockIdx.x; row < R; row += gridDim.x) {
+            const int64_t off = row * T;
+            float carry = 0.f, prod = 1.f;
+            for (int pass = 0; pass < 2; ++pass) {
+                for (int64_t g = 0; g < ngroups; ++g, ++n, ++it) {
+                    const int s = static_cast<int>(n % STAGES);
+                    if (alive && !ts_mbar_wait(full + s, (n / STAGES) & 1u, &s_fault)) {
+                        alive = false;
+                        if (lane == 0) ts_ring_fault(ex, &s_fault);
+                    }
+                    if (!alive) {
+                        ts_consumer_sync(K * 32);
+                        continue;
+                    }
+                    const S *sa = stage_base + static_cast<size_t>(s) * 2 * SUPER;
+                    const S *sx = sa + SUPER;
+                    const int64_t v = g * SUPER + e_lane;
+                    uint4 ra[U], rx[U];
+#pragma unroll
+                    for (int j = 0; j < U; ++j) {
+                        const bool in = v + j * TILE < T;
+                        ra[j] = in ? *reinterpret_cast<const uint4 *>(sa + e_lane + j * TILE)
+                                   : make_uint4(Store<S>::kOne, Store<S>::kOne, Store<S>::kOne, Store<S>::kOne);
+                        rx[j] = in ? *reinterpret_cast<const uint4 *>(sx + e_lane + j * TILE) : make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    __syncwarp();
+                    if (lane == 0) ts_mbar_arrive(empty + s);  // this warp's tiles are in registers
+
+                    float fa[U][E], fx[U][E], A[U], H[U];
+#pragma unroll
+                    for (int j = 0; j < U; ++j) {
+                        Store<S>::unpack(ra[j], fa[j]);
+                        Store<S>::unpack(rx[j], fx[j]);
+                        A[j] = fa[j][0];
+                        H[j] = fx[j][0];
+#pragma unroll
+                        for (int i = 1; i < E; ++i) {
+                            H[j] = fmaf(fa[j][i], H[j], fx[j][i]);
+                            A[j] *= fa[j][i];
+                        }
+                    }
+#pragma unroll
+                    for (int d = 1; d < 32; d <<= 1) {
+#pragma unroll
+                        for (int j = 0; j < U; ++j) {
+                            const float pA = __shfl_up_sync(kFullMask, A[j], d);
+                            const float pH = __shfl_up_sync(kFullMask, H[j], d);
+                            if (lane >= d) {
+                                H[j] = fmaf(A[j], pH, H[j]);
+                                A[j] *= pA;
+                            }
+                        }
+                    }
+                    float WA = __shfl_sync(kFullMask, A[0], 31), WH = __shfl_sync(kFullMask, H[0], 31);
+#pragma unroll
+                    for (int j = 1; j < U; ++j) {
+                        const float tA = __shfl_sync(kFullMask, A[j], 31);
+                        WH = fmaf(tA, WH, __shfl_sync(kFullMask, H[j], 31));
+                        WA *= tA;
+                    }
+                    const int buf = static_cast<int>(it & 1u);
+                    if (lane == 0) agg[buf][w] = make_float2(WA, WH);
+                    ts_consumer_sync(K * 32);
+                    float run = carry, mine = carry;
+#pragma unroll
+                    for (int ww = 0; ww < K; ++ww) {
+                        if (ww == w) mine = run;
+                        const float2 p = agg[buf][ww];
+                        run = fmaf(p.x, run, p.y);
+                        prod *= p.x;
+                    }
+                    if (pass == 1) {
+                        float c = mine;
+#pragma unroll
+                        for (int j = 0; j < U; ++j) {
+                            const float tA = __shfl_sync(kFullMask, A[j], 31);
+                            const float tH = __shfl_sync(kFullMask, H[j], 31);
+                            float eA = __shfl_up_sync(kFullMask, A[j], 1);
+                            float eH = __shfl_up_sync(kFullMask, H[j], 1);
+                            if (lane == 0) {
+                                eA = 1.f;
+                                eH = 0.f;
+                            }
+                            float st = fmaf(eA, c, eH);
+                            float out[E];
+#pragma unroll
+                            for (int i = 0; i < E; ++i) {
+                                st = fmaf(fa[j][i], st, fx[j][i]);
+                                out[i] = st;
+                            }
+                            store_vec<S, false>(states + off, v + j * TILE, T, true, Store<S>::pack(out));
+                            c = fmaf(tA, c, tH);
+                        }
+                    }
+                    carry = run;
+                }
+                if (pass == 0) {
+                    if (w == 0 && alive) {
+                        float S_pub = carry, h_first = 0.f;
+                        if (ex.rank == 0 && h0) {
+                            h_first = h0[row];
+                            S_pub = fmaf(prod, h_first, carry);
+                        }
+                        float hin = ts_exchange_row(ex, 0, row, prod, S_pub, publish_ok, lane, &s_fault);
+                        if (ex.rank == 0) hin = h_first;
+                        if (lane == 0) {
+                            s_carry = hin;
+                            h_in_out[row] = hin;
+                        }
+                    }
+                    ts_consumer_sync(K * 32);
+                    carry = s_carry;
+                    prod = 1.f;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) ts_finish(ex, 0);
+}
+
+// ---------------------------------------------------------------- backward -------------------
+template <typename S, int U, int K, int STAGES>
+__global__ void __launch_bounds__((K + 1) * 32, 1)
+tsplit_backward_tma_kernel(const S *__restrict__ gates, const S *__restrict__ states,
+                           const S *__restrict__ grad_states, const float *__restrict__ h_in,
+                           S *__restrict__ grad_gates, S *__restrict__ grad_tokens, float *__restrict__ grad_h0,
+                           TsExchange ex, int64_t R, int64_t T) {
+    using Ring = TsRing<S, U, K, 3, STAGES>;
+    constexpr int E = Ring::E, TILE = Ring::TILE;
+    constexpr int64_t SUPER = Ring::SUPER;
+    extern __shared__ __align__(128) unsigned char ts_smem[];
+    S *stage_base = reinterpret_cast<S *>(ts_smem);
+    uint64_t *full = reinterpret_cast<uint64_t *>(ts_smem + STAGES * Ring::kStageBytes);
+    uint64_t *empty = full + STAGES;
+    __shared__ float2 agg[2][K];
+    __shared__ float s_carry;
+    __shared__ int s_fault;
+    const int lane = threadIdx.x & 31;
+    const int w = threadIdx.x >> 5;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ts_mbar_init(full + s, 1);
+            ts_mbar_init(empty + s, K);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        s_fault = ts_wait_acks(ex, 1);
+        if (s_fault)
+            atomicCAS(reinterpret_cast<uint32_t *>(ex.buf[ex.rank] + ex.lay.status_offset()), 0u,
+                      static_cast<uint32_t>(s_fault));
+    }
+    __syncthreads();
+    const bool publish_ok = s_fault == 0;
+    const int64_t ngroups = (T + SUPER - 1) / SUPER;
+
+    if (w == K) {
+        if (lane == 0) {
+            unsigned n = 0;
+            bool alive = true;
+            for (int64_t row = blockIdx.x; row < R && alive; row += gridDim.x) {
+                const int64_t off = row * T;
+                for (int pass = 0; pass < 2 && alive; ++pass) {
+                    for (int64_t g = ngroups - 1; g >= 0; --g, ++n) {  // time runs backwards
+                        const int s = static_cast<int>(n % STAGES);
+                        if (!ts_mbar_wait(empty + s, ((n / STAGES) & 1u) ^ 1u, &s_fault)) {
+                            alive = false;
+                            break;
+                        }
+                        const int64_t e0 = g * SUPER;
+                        const unsigned bytes = static_cast<unsigned>(min(SUPER, T - e0) * sizeof(S));
+                        S *dst = stage_base + static_cast<size_t>(s) * 3 * SUPER;
+                        ts_mbar_expect_tx(full + s, (pass == 1 ? 3 : 2) * bytes);
+                        ts_bulk_load(dst, gates + off + e0, bytes, full + s);
+                        ts_bulk_load(dst + SUPER, grad_states + off + e0, bytes, full + s);
+                        if (pass == 1) ts_bulk_load(dst + 2 * SUPER, states + off + e0, bytes, full + s);
+                    }
+                }
+            }
+            if (!alive) {
+                ts_ring_fault(ex, &s_fault);
+                for (unsigned k = n > STAGES ? n - STAGES : 0; k < n; ++k) {
+                    const int s = static_cast<int>(k % STAGES);
+                    for (unsigned spin = 0; spin < kTsMbarSpins && !ts_mbar_try_wait(full + s, (k / STAGES) & 1u); ++spin) {
+                    }
+                }
+            }
+        }
+    } else {
+        const int64_t e_lane = static_cast<int64_t>(w) * (TILE * U) + lane * E;
+        unsigned n = 0, it = 0;
+        bool alive = true;
+        for (int64_t row = blockIdx.x; row < R; row += gridDim.x) {
+            const int64_t off = row * T;
+            float carry = 0.f, prod = 1.f, h_before = 0.f;
+            for (int pass = 0; pass < 2; ++pass) {
+                for (int64_t g = ngroups - 1; g >= 0; --g, ++n, ++it) {
+                    const int s = static_cast<int>(n % STAGES);
+                    const int64_t v = g * SUPER + e_lane;
+                    // the state just before this group sits outside the stage: one scalar from global
+                    // memory, asked for before the wait (only the first lane of the group's first tile)
+                    float group_halo = 0.f;
+                    if (alive && pass == 1 && w == 0 && lane == 0 && g > 0)
+                        group_halo = Store<S>::to_float(states[off + g * SUPER - 1]);
+                    if (alive && !ts_mbar_wait(full + s, (n / STAGES) & 1u, &s_fault)) {
+                        alive = false;
+                        if (lane == 0) ts_ring_fault(ex, &s_fault);
+                    }
+                    if (!alive) {
+                        ts_consumer_sync(K * 32);
+                        continue;
+                    }
+                    const S *sa = stage_base + static_cast<size_t>(s) * 3 * SUPER;
+                    const S *sg = sa + SUPER, *sh = sa + 2 * SUPER;
+                    uint4 ra[U], rg[U], rh[U];
+                    float halo[U];
+#pragma unroll
+                    for (int j = 0; j < U; ++j) {
+                        const bool in = v + j * TILE < T;
+                        ra[j] = in ? *reinterpret_cast<const uint4 *>(sa + e_lane + j * TILE)
+                                   : make_uint4(Store<S>::kOne, Store<S>::kOne, Store<S>::kOne, Store<S>::kOne);
+                        rg[j] = in ? *reinterpret_cast<const uint4 *>(sg + e_lane + j * TILE) : make_uint4(0u, 0u, 0u, 0u);
+                        rh[j] = make_uint4(0u, 0u, 0u, 0u);
+                        halo[j] = 0.f;
+                        if (pass == 1 && in) {
+                            rh[j] = *reinterpret_cast<const uint4 *>(sh + e_lane + j * TILE);
+                            if (lane == 0) {
+                                const int64_t ee = e_lane + j * TILE;  // first element of this tile inside the stage
+                                halo[j] = ee > 0 ? Store<S>::to_float(sh[ee - 1]) : group_halo;
+                            }
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) ts_mbar_arrive(empty + s);
+
+                    float fa[U][E], fg[U][E], A[U], C[U];
+#pragma unroll
+                    for (int j = 0; j < U; ++j) {
+                        Store<S>::unpack(ra[j], fa[j]);
+                        Store<S>::unpack(rg[j], fg[j]);
+                        A[j] = fa[j][E - 1];
+                        C[j] = fa[j][E - 1] * fg[j][E - 1];
+#pragma unroll
+                        for (int i = E - 2; i >= 0; --i) {
+                            C[j] = fa[j][i] * (fg[j][i] + C[j]);
+                            A[j] *= fa[j][i];
+                        }
+                    }
+#pragma unroll
+                    for (int d = 1; d < 32; d <<= 1) {
+#pragma unroll
+                        for (int j = 0; j < U; ++j) {
+                            const float pA = __shfl_down_sync(kFullMask, A[j], d);
+                            const float pC = __shfl_down_sync(kFullMask, C[j], d);
+                            if (lane + d < 32) {
+                                C[j] = fmaf(A[j], pC, C[j]);
+                                A[j] *= pA;
+                            }
+                        }
+                    }
+                    float WA = __shfl_sync(kFullMask, A[U - 1], 0), WC = __shfl_sync(kFullMask, C[U - 1], 0);
+#pragma unroll
+                    for (int j = U - 2; j >= 0; --j) {
+                        const float tA = __shfl_sync(kFullMask, A[j], 0);
+                        WC = fmaf(tA, WC, __shfl_sync(kFullMask, C[j], 0));
+                        WA *= tA;
+                    }
+                    const int buf = static_cast<int>(it & 1u);
+                    if (lane == 0) agg[buf][w] = make_float2(WA, WC);
+                    ts_consumer_sync(K * 32);
+                    float run = carry, mine = carry;
+#pragma unroll
+                    for (int ww = K - 1; ww >= 0; --ww) {
+                        if (ww == w) mine = run;
+                        const float2 p = agg[buf][ww];
+                        run = fmaf(p.x, run, p.y);
+                        prod *= p.x;
+                    }
+                    if (pass == 1) {
+                        float cw = mine;
+#pragma unroll
+                        for (int j = U - 1; j >= 0; --j) {
+                            const float tA = __shfl_sync(kFullMask, A[j], 0);
+                            const float tC = __shfl_sync(kFullMask, C[j], 0);
+                            float eA = __shfl_down_sync(kFullMask, A[j], 1);
+                            float eC = __shfl_down_sync(kFullMask, C[j], 1);
+                            if (lane == 31) {
+                                eA = 1.f;
+                                eC = 0.f;
+                            }
+                            float fh[E];
+                            Store<S>::unpack(rh[j], fh);
+                            float hprev0 = __shfl_up_sync(kFullMask, fh[E - 1], 1);
+                            if (lane == 0) hprev0 = (v + j * TILE - 1 >= 0) ? halo[j] : h_before;
+                            float c = fmaf(eA, cw, eC);
+                            float dx[E], da[E];
+#pragma unroll
+                            for (int i = E - 1; i >= 0; --i) {
+                                const float delta = fg[j][i] + c;
+                                c = fa[j][i] * delta;
+                                const float hp = (i > 0) ? fh[i > 0 ? i - 1 : 0] : hprev0;
+                                dx[i] = delta;
+                                da[i] = delta * hp;
+                            }
+                            store_vec<S, false>(grad_tokens + off, v + j * TILE, T, true, Store<S>::pack(dx));
+                            store_vec<S, false>(grad_gates + off, v + j * TILE, T, true, Store<S>::pack(da));
+                            cw = fmaf(tA, cw, tC);
+                        }
+                    }
+                    carry = run;
+                }
+                if (pass == 0) {
+                    if (w == 0 && alive) {
+                        const float cin = ts_exchange_row(ex, 1, row, prod, carry, publish_ok, lane, &s_fault);
+                        if (lane == 0) s_carry = cin;
+                    }
+                    ts_consumer_sync(K * 32);
+                    carry = s_carry;
+                    prod = 1.f;
+                    h_before = h_in ? h_in[row] : 0.f;
+                } else if (grad_h0 && alive && w == 0 && lane == 0) {
+                    grad_h0[row] = carry;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) ts_finish(ex, 1);
+}
+
+}  // namespace fms

@@ -256,8 +256,13 @@ int fms_btd_backward(const void *gates, const void *states, const void *grad_sta
  * be reused by the next call on the same stream.
  * Arguments of the two entry points are those of fms_plain_forward / fms_plain_backward plus
  * the scratch.  With segments == 1 they forward to the ordinary entry points.
+ * fms_plain_split_recommended: 1 when the split is expected to beat the ordinary entry points on
+ * this GPU (measured rule: fewer than one row per four SMs, and long enough to split), else 0;
+ * the torch shim routes by it.  The split entry points themselves honour
+ * fms_plain_split_segments whenever they are called.
  */
 int64_t fms_plain_split_segments(int64_t rows, int64_t T, int dtype);
+int fms_plain_split_recommended(int64_t rows, int64_t T, int dtype);
 size_t fms_plain_split_workspace_bytes(int64_t rows, int64_t T, int dtype);
 int fms_plain_forward_split(const void *gates, const void *tokens, const float *h0, void *states,
                             float *h_last, int64_t rows, int64_t T, int dtype, void *workspace,

@@ -58,9 +58,14 @@ def _run_step(L, ptrs, world, blocks, h0, number, wait=0.5):
     return hs, grads, gh0
 
 
-@pytest.mark.parametrize("launch", [{}, {"FMS_TUNE_TSPLIT_K": "16"}, {"FMS_TUNE_TSPLIT_U": "2", "FMS_TUNE_TSPLIT_BWD_U": "4"}])
+@pytest.mark.parametrize("launch", [{},                                        # staged ring, 16 warps per row
+                                    {"FMS_TUNE_TSPLIT_K": "8"},                # staged ring, 8 warps per row
+                                    {"FMS_TUNE_TSPLIT_STAGED": "0"},           # register prefetch, 8 warps
+                                    {"FMS_TUNE_TSPLIT_STAGED": "0", "FMS_TUNE_TSPLIT_K": "16"},
+                                    {"FMS_TUNE_TSPLIT_STAGED": "0", "FMS_TUNE_TSPLIT_U": "2",
+                                     "FMS_TUNE_TSPLIT_BWD_U": "4"}])
 @pytest.mark.parametrize("storage,world,R,Tk", [("f32", 2, 37, 4096 + 512), ("bf16", 3, 300, 8192), ("f16", 8, 5, 1024),
-                                                ("f32", 4, 700, 2052)])
+                                                ("f32", 4, 700, 2052), ("f32", 2, 3, 40000)])
 def test_fused_split_matches_the_oracle_over_three_steps(storage, world, R, Tk, launch):
     import os
     import subprocess

@@ -39,7 +39,7 @@ int env_int(const char *name, int dflt) {
 // fewer rows in flight, which is what lets pass B find its operands in L2 (rows in flight x row
 // bytes x tensors must stay well inside the 126 MB).  Read once per process.
 struct TsTune {
-    int k, u, bwd_u, ctas_per_sm, staged;
+    int k, u, bwd_u, ctas_per_sm, staged, l2_hint;
 };
 const TsTune &ts_tune() {
     // staged = 1 (default): operands come through the bulk-copy shared-memory ring, one CTA per SM
@@ -51,6 +51,7 @@ const TsTune &ts_tune() {
         v.u = env_int("FMS_TUNE_TSPLIT_U", 4);
         v.bwd_u = env_int("FMS_TUNE_TSPLIT_BWD_U", 2);
         v.ctas_per_sm = env_int("FMS_TUNE_TSPLIT_CTAS_PER_SM", 2);
+        v.l2_hint = env_int("FMS_TUNE_TSPLIT_L2_HINT", 0);
         return v;
     }();
     return t;
@@ -91,6 +92,7 @@ int make_exchange(fms::TsExchange &ex, void *const *peer_buffers, int64_t rows, 
     ex.rank = rank;
     ex.epoch = exchange;
     ex.max_wait_cycles = wait_cycles(max_wait_seconds);
+    ex.l2_hint = ts_tune().l2_hint;
     return FMS_OK;
 }
 
@@ -116,6 +118,8 @@ int launch_forward_staged(const void *gates, const void *tokens, const float *h0
             ex, rows, T);                                                                                    \
     } while (0)
     if (ts_tune().k == 8) FMS_TS_FWD_STAGED(4, 8, 6);
+    else if (ts_tune().k == 24) FMS_TS_FWD_STAGED(2, 24, 4);
+    else if (ts_tune().u == 2) FMS_TS_FWD_STAGED(2, 16, 6);
     else FMS_TS_FWD_STAGED(4, 16, 3);
 #undef FMS_TS_FWD_STAGED
     return cudaGetLastError() == cudaSuccess ? FMS_OK : FMS_ERR_LAUNCH;
@@ -137,6 +141,7 @@ int launch_backward_staged(const void *gates, const void *states, const void *gr
             h_in, static_cast<S *>(grad_gates), static_cast<S *>(grad_tokens), grad_h0, ex, rows, T);        \
     } while (0)
     if (ts_tune().k == 8) FMS_TS_BWD_STAGED(4, 8, 4);
+    else if (ts_tune().k == 24) FMS_TS_BWD_STAGED(2, 24, 3);
     else FMS_TS_BWD_STAGED(2, 16, 4);
 #undef FMS_TS_BWD_STAGED
     return cudaGetLastError() == cudaSuccess ? FMS_OK : FMS_ERR_LAUNCH;

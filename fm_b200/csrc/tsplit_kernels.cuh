@@ -53,6 +53,7 @@ struct TsExchange {
     int rank;
     uint32_t epoch;
     long long max_wait_cycles;
+    int l2_hint;  // staged kernels: first pass evict-last, second pass evict-first
 };
 
 __device__ __forceinline__ void st_slot(void *p, float P, float S, uint32_t e) {

@@ -68,6 +68,22 @@ __device__ __forceinline__ void ts_bulk_load(void *smem_dst, const void *gmem_sr
                  "l"(gmem_src), "r"(bytes), "r"(ts_smem_addr(bar))
                  : "memory");
 }
+// The same copy with an L2 eviction policy: the first pass of a row asks L2 to keep the lines
+// (evict-last), the second pass releases them (evict-first).
+__device__ __forceinline__ void ts_bulk_load_hint(void *smem_dst, const void *gmem_src, unsigned bytes, uint64_t *bar,
+                                                  uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::
+            "r"(ts_smem_addr(smem_dst)),
+        "l"(gmem_src), "r"(bytes), "r"(ts_smem_addr(bar)), "l"(policy)
+        : "memory");
+}
+__device__ __forceinline__ uint64_t ts_policy(bool keep) {
+    uint64_t pol;
+    if (keep) asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    else asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
 __device__ __forceinline__ void ts_consumer_sync(int threads) {
     asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
 }
@@ -120,6 +136,7 @@ tsplit_forward_tma_kernel(const S *__restrict__ gates, const S *__restrict__ tok
         if (lane == 0) {
             unsigned n = 0;
             bool alive = true;
+            const uint64_t pol_keep = ts_policy(true), pol_release = ts_policy(false);
             for (int64_t row = blockIdx.x; row < R && alive; row += gridDim.x) {
                 const int64_t off = row * T;
                 for (int pass = 0; pass < 2 && alive; ++pass) {
@@ -133,8 +150,14 @@ tsplit_forward_tma_kernel(const S *__restrict__ gates, const S *__restrict__ tok
                         const unsigned bytes = static_cast<unsigned>(min(SUPER, T - e0) * sizeof(S));
                         S *dst = stage_base + static_cast<size_t>(s) * 2 * SUPER;
                         ts_mbar_expect_tx(full + s, 2 * bytes);
-                        ts_bulk_load(dst, gates + off + e0, bytes, full + s);
-                        ts_bulk_load(dst + SUPER, tokens + off + e0, bytes, full + s);
+                        if (ex.l2_hint) {
+                            const uint64_t pol = pass == 0 ? pol_keep : pol_release;
+                            ts_bulk_load_hint(dst, gates + off + e0, bytes, full + s, pol);
+                            ts_bulk_load_hint(dst + SUPER, tokens + off + e0, bytes, full + s, pol);
+                        } else {
+                            ts_bulk_load(dst, gates + off + e0, bytes, full + s);
+                            ts_bulk_load(dst + SUPER, tokens + off + e0, bytes, full + s);
+                        }
                     }
                 }
             }
@@ -315,6 +338,7 @@ tsplit_backward_tma_kernel(const S *__restrict__ gates, const S *__restrict__ st
         if (lane == 0) {
             unsigned n = 0;
             bool alive = true;
+            const uint64_t pol_keep = ts_policy(true), pol_release = ts_policy(false);
             for (int64_t row = blockIdx.x; row < R && alive; row += gridDim.x) {
                 const int64_t off = row * T;
                 for (int pass = 0; pass < 2 && alive; ++pass) {
@@ -328,9 +352,16 @@ tsplit_backward_tma_kernel(const S *__restrict__ gates, const S *__restrict__ st
                         const unsigned bytes = static_cast<unsigned>(min(SUPER, T - e0) * sizeof(S));
                         S *dst = stage_base + static_cast<size_t>(s) * 3 * SUPER;
                         ts_mbar_expect_tx(full + s, (pass == 1 ? 3 : 2) * bytes);
-                        ts_bulk_load(dst, gates + off + e0, bytes, full + s);
-                        ts_bulk_load(dst + SUPER, grad_states + off + e0, bytes, full + s);
-                        if (pass == 1) ts_bulk_load(dst + 2 * SUPER, states + off + e0, bytes, full + s);
+                        if (ex.l2_hint) {
+                            const uint64_t pol = pass == 0 ? pol_keep : pol_release;
+                            ts_bulk_load_hint(dst, gates + off + e0, bytes, full + s, pol);
+                            ts_bulk_load_hint(dst + SUPER, grad_states + off + e0, bytes, full + s, pol);
+                            if (pass == 1) ts_bulk_load_hint(dst + 2 * SUPER, states + off + e0, bytes, full + s, pol_release);
+                        } else {
+                            ts_bulk_load(dst, gates + off + e0, bytes, full + s);
+                            ts_bulk_load(dst + SUPER, grad_states + off + e0, bytes, full + s);
+                            if (pass == 1) ts_bulk_load(dst + 2 * SUPER, states + off + e0, bytes, full + s);
+                        }
                     }
                 }
             }

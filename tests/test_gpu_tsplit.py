@@ -60,6 +60,7 @@ def _run_step(L, ptrs, world, blocks, h0, number, wait=0.5):
 
 @pytest.mark.parametrize("launch", [{},                                        # staged ring, 16 warps per row
                                     {"FMS_TUNE_TSPLIT_K": "8"},                # staged ring, 8 warps per row
+                                    {"FMS_TUNE_TSPLIT_K": "24", "FMS_TUNE_TSPLIT_L2_HINT": "1"},   # 24 warps, L2 hints
                                     {"FMS_TUNE_TSPLIT_STAGED": "0"},           # register prefetch, 8 warps
                                     {"FMS_TUNE_TSPLIT_STAGED": "0", "FMS_TUNE_TSPLIT_K": "16"},
                                     {"FMS_TUNE_TSPLIT_STAGED": "0", "FMS_TUNE_TSPLIT_U": "2",

@@ -110,6 +110,8 @@ int launch_forward_staged(const void *gates, const void *tokens, const float *h0
     do {                                                                                                     \
         auto kern = fms::tsplit_forward_tma_kernel<S, UU, KK, NS>;                                           \
         constexpr size_t smem = fms::TsRing<S, UU, KK, 2, NS>::kBytes;                                       \
+        constexpr int64_t super = fms::TsRing<S, UU, KK, 2, NS>::SUPER;                                      \
+        if ((T + super - 1) / super * KK > fms::kTsMaxAgg) return FMS_ERR_TOO_LARGE;                         \
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != \
             cudaSuccess)                                                                                     \
             return FMS_ERR_LAUNCH;                                                                           \
@@ -133,6 +135,8 @@ int launch_backward_staged(const void *gates, const void *states, const void *gr
     do {                                                                                                     \
         auto kern = fms::tsplit_backward_tma_kernel<S, UU, KK, NS>;                                          \
         constexpr size_t smem = fms::TsRing<S, UU, KK, 3, NS>::kBytes;                                       \
+        constexpr int64_t super = fms::TsRing<S, UU, KK, 3, NS>::SUPER;                                      \
+        if ((T + super - 1) / super * KK > fms::kTsMaxAgg) return FMS_ERR_TOO_LARGE;                         \
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != \
             cudaSuccess)                                                                                     \
             return FMS_ERR_LAUNCH;                                                                           \
@@ -150,8 +154,12 @@ int launch_backward_staged(const void *gates, const void *states, const void *gr
 template <typename S>
 int launch_forward(const void *gates, const void *tokens, const float *h0, void *states, float *h_in_out,
                    const fms::TsExchange &ex, int64_t rows, int64_t T, cudaStream_t st) {
-    if (ts_tune().staged) return launch_forward_staged<S>(gates, tokens, h0, states, h_in_out, ex, rows, T, st);
-    const int K = ts_tune().k, U = ts_tune().u;
+    if (ts_tune().staged) {
+        // blocks too long for the staged kernels' per-row aggregate table use the register kernels
+        const int rc = launch_forward_staged<S>(gates, tokens, h0, states, h_in_out, ex, rows, T, st);
+        if (rc != FMS_ERR_TOO_LARGE) return rc;
+    }
+    const int K = ts_tune().k == 16 ? 16 : 8, U = ts_tune().u;
 #define FMS_TS_FWD(UU, KK)                                                                                   \
     do {                                                                                                     \
         auto kern = fms::tsplit_forward_kernel<S, UU, KK>;                                                   \
@@ -175,11 +183,13 @@ template <typename S>
 int launch_backward(const void *gates, const void *states, const void *grad_states, const float *h_in,
                     void *grad_gates, void *grad_tokens, float *grad_h0, const fms::TsExchange &ex, int64_t rows,
                     int64_t T, cudaStream_t st) {
-    if (ts_tune().staged)
-        return launch_backward_staged<S>(gates, states, grad_states, h_in, grad_gates, grad_tokens, grad_h0, ex, rows,
-                                         T, st);
+    if (ts_tune().staged) {
+        const int rc = launch_backward_staged<S>(gates, states, grad_states, h_in, grad_gates, grad_tokens, grad_h0,
+                                                 ex, rows, T, st);
+        if (rc != FMS_ERR_TOO_LARGE) return rc;
+    }
     // three input streams: 4 tiles per step need 189 registers (one CTA of 8 warps per SM), 2 need 128
-    const int K = ts_tune().k, U = ts_tune().bwd_u;
+    const int K = ts_tune().k == 16 ? 16 : 8, U = ts_tune().bwd_u;
 #define FMS_TS_BWD(UU, KK)                                                                                   \
     do {                                                                                                     \
         auto kern = fms::tsplit_backward_kernel<S, UU, KK>;                                                  \

@@ -88,6 +88,41 @@ __device__ __forceinline__ void ts_consumer_sync(int threads) {
     asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
 }
 
+// Aggregates of one row's block, one (P, S) pair per (super-tile, warp) in walk order.  The first
+// pass writes them (each warp its own, no barrier); then ONE warp turns them, in place, into
+// exclusive prefixes -- the pair that maps the block's carry-in to the carry entering that warp's
+// tiles -- and returns the block's total.  The second pass then needs no barrier at all: every
+// warp starts each super-tile from  fma(prefix.P, carry_in, prefix.S).
+constexpr int kTsMaxAgg = 1024;  // (super-tiles per block) x K must fit; longer blocks use the register kernels
+
+__device__ __forceinline__ float2 ts_scan_aggregates(float2 *aggs, int n, int lane) {
+    float rp = 1.f, rs = 0.f;  // running total of the chunks done so far
+    for (int base = 0; base < n; base += 32) {
+        const int i = base + lane;
+        const float2 v = i < n ? aggs[i] : make_float2(1.f, 0.f);
+        float P = v.x, Sv = v.y;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const float pP = __shfl_up_sync(kFullMask, P, d);
+            const float pS = __shfl_up_sync(kFullMask, Sv, d);
+            if (lane >= d) {
+                Sv = fmaf(P, pS, Sv);
+                P *= pP;
+            }
+        }
+        float eP = __shfl_up_sync(kFullMask, P, 1), eS = __shfl_up_sync(kFullMask, Sv, 1);
+        if (lane == 0) {
+            eP = 1.f;
+            eS = 0.f;
+        }
+        if (i < n) aggs[i] = make_float2(eP * rp, fmaf(eP, rs, eS));
+        const float tP = __shfl_sync(kFullMask, P, 31), tS = __shfl_sync(kFullMask, Sv, 31);
+        rs = fmaf(tP, rs, tS);
+        rp *= tP;
+    }
+    return make_float2(rp, rs);
+}
+
 // Shared memory of one CTA: NT operands per stage, each SUPER elements of S.
 template <typename S, int U, int K, int NT, int STAGES>
 struct TsRing {
@@ -110,7 +145,7 @@ tsplit_forward_tma_kernel(const S *__restrict__ gates, const S *__restrict__ tok
     S *stage_base = reinterpret_cast<S *>(ts_smem);
     uint64_t *full = reinterpret_cast<uint64_t *>(ts_smem + STAGES * Ring::kStageBytes);
     uint64_t *empty = full + STAGES;
-    __shared__ float2 agg[2][K];
+    __shared__ float2 aggs[kTsMaxAgg];
     __shared__ float s_carry;
     __shared__ int s_fault;
     const int lane = threadIdx.x & 31;
@@ -173,25 +208,24 @@ tsplit_forward_tma_kernel(const S *__restrict__ gates, const S *__restrict__ tok
         }
     } else {
         // ---------------- consumers: K warps, the arithmetic of tsplit_forward_kernel.
+        // Inside a pass the warps run free (the ring's barriers are the only coupling); the CTA
+        // meets at two named barriers per row, around the prefix scan and the peer exchange.
         // A warp whose ring wait ran out keeps walking the loops (every warp must meet every named
         // barrier) but touches neither the ring nor global memory any more.
         const int64_t e_lane = static_cast<int64_t>(w) * (TILE * U) + lane * E;  // element offset inside a stage
-        unsigned n = 0, it = 0;
+        unsigned n = 0;
         bool alive = true;
         for (int64_t row = blockIdx.x; row < R; row += gridDim.x) {
             const int64_t off = row * T;
-            float carry = 0.f, prod = 1.f;
+            float hin = 0.f;
             for (int pass = 0; pass < 2; ++pass) {
-                for (int64_t g = 0; g < ngroups; ++g, ++n, ++it) {
+                for (int64_t g = 0; g < ngroups; ++g, ++n) {
                     const int s = static_cast<int>(n % STAGES);
                     if (alive && !ts_mbar_wait(full + s, (n / STAGES) & 1u, &s_fault)) {
                         alive = false;
                         if (lane == 0) ts_ring_fault(ex, &s_fault);
                     }
-                    if (!alive) {
-                        ts_consumer_sync(K * 32);
-                        continue;
-                    }
+                    if (!alive) continue;
                     const S *sa = stage_base + static_cast<size_t>(s) * 2 * SUPER;
                     const S *sx = sa + SUPER;
                     const int64_t v = g * SUPER + e_lane;
@@ -231,26 +265,19 @@ tsplit_forward_tma_kernel(const S *__restrict__ gates, const S *__restrict__ tok
                             }
                         }
                     }
-                    float WA = __shfl_sync(kFullMask, A[0], 31), WH = __shfl_sync(kFullMask, H[0], 31);
+                    const int slot = static_cast<int>(g) * K + w;
+                    if (pass == 0) {
+                        float WA = __shfl_sync(kFullMask, A[0], 31), WH = __shfl_sync(kFullMask, H[0], 31);
 #pragma unroll
-                    for (int j = 1; j < U; ++j) {
-                        const float tA = __shfl_sync(kFullMask, A[j], 31);
-                        WH = fmaf(tA, WH, __shfl_sync(kFullMask, H[j], 31));
-                        WA *= tA;
-                    }
-                    const int buf = static_cast<int>(it & 1u);
-                    if (lane == 0) agg[buf][w] = make_float2(WA, WH);
-                    ts_consumer_sync(K * 32);
-                    float run = carry, mine = carry;
-#pragma unroll
-                    for (int ww = 0; ww < K; ++ww) {
-                        if (ww == w) mine = run;
-                        const float2 p = agg[buf][ww];
-                        run = fmaf(p.x, run, p.y);
-                        prod *= p.x;
-                    }
-                    if (pass == 1) {
-                        float c = mine;
+                        for (int j = 1; j < U; ++j) {
+                            const float tA = __shfl_sync(kFullMask, A[j], 31);
+                            WH = fmaf(tA, WH, __shfl_sync(kFullMask, H[j], 31));
+                            WA *= tA;
+                        }
+                        if (lane == 0) aggs[slot] = make_float2(WA, WH);
+                    } else {
+                        const float2 pre = aggs[slot];
+                        float c = fmaf(pre.x, hin, pre.y);  // state entering this warp's first tile
 #pragma unroll
                         for (int j = 0; j < U; ++j) {
                             const float tA = __shfl_sync(kFullMask, A[j], 31);
@@ -272,25 +299,25 @@ tsplit_forward_tma_kernel(const S *__restrict__ gates, const S *__restrict__ tok
                             c = fmaf(tA, c, tH);
                         }
                     }
-                    carry = run;
                 }
                 if (pass == 0) {
+                    ts_consumer_sync(K * 32);  // every warp's aggregates of this row are in shared memory
                     if (w == 0 && alive) {
-                        float S_pub = carry, h_first = 0.f;
-                        if (ex.rank == 0 && h0) {
+                        const float2 total = ts_scan_aggregates(aggs, static_cast<int>(ngroups) * K, lane);
+                        float S_pub = total.y, h_first = 0.f;
+                        if (ex.rank == 0 && h0) {  // the first block folds the initial state into what it publishes
                             h_first = h0[row];
-                            S_pub = fmaf(prod, h_first, carry);
+                            S_pub = fmaf(total.x, h_first, total.y);
                         }
-                        float hin = ts_exchange_row(ex, 0, row, prod, S_pub, publish_ok, lane, &s_fault);
-                        if (ex.rank == 0) hin = h_first;
+                        float c_in = ts_exchange_row(ex, 0, row, total.x, S_pub, publish_ok, lane, &s_fault);
+                        if (ex.rank == 0) c_in = h_first;
                         if (lane == 0) {
-                            s_carry = hin;
-                            h_in_out[row] = hin;
+                            s_carry = c_in;
+                            h_in_out[row] = c_in;
                         }
                     }
-                    ts_consumer_sync(K * 32);
-                    carry = s_carry;
-                    prod = 1.f;
+                    ts_consumer_sync(K * 32);  // prefixes and the carry-in are published to the CTA
+                    hin = s_carry;
                 }
             }
         }
@@ -313,7 +340,7 @@ tsplit_backward_tma_kernel(const S *__restrict__ gates, const S *__restrict__ st
     S *stage_base = reinterpret_cast<S *>(ts_smem);
     uint64_t *full = reinterpret_cast<uint64_t *>(ts_smem + STAGES * Ring::kStageBytes);
     uint64_t *empty = full + STAGES;
-    __shared__ float2 agg[2][K];
+    __shared__ float2 aggs[kTsMaxAgg];
     __shared__ float s_carry;
     __shared__ int s_fault;
     const int lane = threadIdx.x & 31;
@@ -376,13 +403,13 @@ tsplit_backward_tma_kernel(const S *__restrict__ gates, const S *__restrict__ st
         }
     } else {
         const int64_t e_lane = static_cast<int64_t>(w) * (TILE * U) + lane * E;
-        unsigned n = 0, it = 0;
+        unsigned n = 0;
         bool alive = true;
         for (int64_t row = blockIdx.x; row < R; row += gridDim.x) {
             const int64_t off = row * T;
-            float carry = 0.f, prod = 1.f, h_before = 0.f;
+            float cin = 0.f, h_before = 0.f;
             for (int pass = 0; pass < 2; ++pass) {
-                for (int64_t g = ngroups - 1; g >= 0; --g, ++n, ++it) {
+                for (int64_t g = ngroups - 1; g >= 0; --g, ++n) {
                     const int s = static_cast<int>(n % STAGES);
                     const int64_t v = g * SUPER + e_lane;
                     // the state just before this group sits outside the stage: one scalar from global
@@ -394,10 +421,7 @@ tsplit_backward_tma_kernel(const S *__restrict__ gates, const S *__restrict__ st
                         alive = false;
                         if (lane == 0) ts_ring_fault(ex, &s_fault);
                     }
-                    if (!alive) {
-                        ts_consumer_sync(K * 32);
-                        continue;
-                    }
+                    if (!alive) continue;
                     const S *sa = stage_base + static_cast<size_t>(s) * 3 * SUPER;
                     const S *sg = sa + SUPER, *sh = sa + 2 * SUPER;
                     uint4 ra[U], rg[U], rh[U];
@@ -446,26 +470,20 @@ tsplit_backward_tma_kernel(const S *__restrict__ gates, const S *__restrict__ st
                             }
                         }
                     }
-                    float WA = __shfl_sync(kFullMask, A[U - 1], 0), WC = __shfl_sync(kFullMask, C[U - 1], 0);
+                    // walk order: super-tiles from the last one down, warps from K-1 down
+                    const int slot = static_cast<int>(ngroups - 1 - g) * K + (K - 1 - w);
+                    if (pass == 0) {
+                        float WA = __shfl_sync(kFullMask, A[U - 1], 0), WC = __shfl_sync(kFullMask, C[U - 1], 0);
 #pragma unroll
-                    for (int j = U - 2; j >= 0; --j) {
-                        const float tA = __shfl_sync(kFullMask, A[j], 0);
-                        WC = fmaf(tA, WC, __shfl_sync(kFullMask, C[j], 0));
-                        WA *= tA;
-                    }
-                    const int buf = static_cast<int>(it & 1u);
-                    if (lane == 0) agg[buf][w] = make_float2(WA, WC);
-                    ts_consumer_sync(K * 32);
-                    float run = carry, mine = carry;
-#pragma unroll
-                    for (int ww = K - 1; ww >= 0; --ww) {
-                        if (ww == w) mine = run;
-                        const float2 p = agg[buf][ww];
-                        run = fmaf(p.x, run, p.y);
-                        prod *= p.x;
-                    }
-                    if (pass == 1) {
-                        float cw = mine;
+                        for (int j = U - 2; j >= 0; --j) {
+                            const float tA = __shfl_sync(kFullMask, A[j], 0);
+                            WC = fmaf(tA, WC, __shfl_sync(kFullMask, C[j], 0));
+                            WA *= tA;
+                        }
+                        if (lane == 0) aggs[slot] = make_float2(WA, WC);
+                    } else {
+                        const float2 pre = aggs[slot];
+                        float cw = fmaf(pre.x, cin, pre.y);  // c just after this warp's last tile
 #pragma unroll
                         for (int j = U - 1; j >= 0; --j) {
                             const float tA = __shfl_sync(kFullMask, A[j], 0);
@@ -494,20 +512,20 @@ tsplit_backward_tma_kernel(const S *__restrict__ gates, const S *__restrict__ st
                             store_vec<S, false>(grad_gates + off, v + j * TILE, T, true, Store<S>::pack(da));
                             cw = fmaf(tA, cw, tC);
                         }
+                        // the warp that owns the block's first tile ends with c at the block start
+                        if (grad_h0 && g == 0 && w == 0 && lane == 0) grad_h0[row] = cw;
                     }
-                    carry = run;
                 }
                 if (pass == 0) {
+                    ts_consumer_sync(K * 32);
                     if (w == 0 && alive) {
-                        const float cin = ts_exchange_row(ex, 1, row, prod, carry, publish_ok, lane, &s_fault);
-                        if (lane == 0) s_carry = cin;
+                        const float2 total = ts_scan_aggregates(aggs, static_cast<int>(ngroups) * K, lane);
+                        const float c_in = ts_exchange_row(ex, 1, row, total.x, total.y, publish_ok, lane, &s_fault);
+                        if (lane == 0) s_carry = c_in;
                     }
                     ts_consumer_sync(K * 32);
-                    carry = s_carry;
-                    prod = 1.f;
+                    cin = s_carry;
                     h_before = h_in ? h_in[row] : 0.f;
-                } else if (grad_h0 && alive && w == 0 && lane == 0) {
-                    grad_h0[row] = carry;
                 }
             }
         }

@@ -596,7 +596,7 @@ def run_time_split(args):
     device = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    B, D, T = 1, args.rows or 4096, 262144
+    B, D, T = 1, args.rows or 4096, args.seq_len or 262144
     Tk = T // world
     gen = torch.Generator(device=device).manual_seed(1004 + rank)
     a = torch.sigmoid(torch.randn(B, D, Tk, device=device, generator=gen) + 3.0).requires_grad_(True)
@@ -644,7 +644,7 @@ def run_time_split(args):
                 "n_gpus": world, "steps": K, "warmup": max(3, args.warmup), "ms_per_step": ms,
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
                 "data": "synthetic",
-                "config": {"workload": "scan fwd+bwd (B,D,T)=(1,%d,262144) fp32, T split in %d blocks" % (D, world),
+                "config": {"workload": "scan fwd+bwd (B,D,T)=(1,%d,%d) fp32, T split in %d blocks" % (D, T, world),
                            "gates": "a = sigmoid(N(0,1)+3); x, G ~ N(0,1)",
                            "exchange": (type(exchange).__name__ + ": peer stores + flags in symmetric memory"
                                         if exchange is not None else
@@ -956,6 +956,9 @@ def main():
                     help="carry transport of the long sequence split along T")
     ap.add_argument("--no-extras", action="store_true",
                     help="headline only: skip time_split, the other scaling mode and reference_cuda")
+    ap.add_argument("--seq-len", type=int, default=0,
+                    help="--workload c4: total sequence length instead of 262144 (tuning aid: 65536 on 2 GPUs "
+                         "gives each rank the block it has at 8 GPUs)")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling aid)")

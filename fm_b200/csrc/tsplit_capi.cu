@@ -39,7 +39,7 @@ int env_int(const char *name, int dflt) {
 // fewer rows in flight, which is what lets pass B find its operands in L2 (rows in flight x row
 // bytes x tensors must stay well inside the 126 MB).  Read once per process.
 struct TsTune {
-    int k, u, bwd_u, ctas_per_sm, staged, l2_hint;
+    int k, u, bwd_u, ctas_per_sm, staged, l2_hint, look;
 };
 const TsTune &ts_tune() {
     // staged = 1 (default): operands come through the bulk-copy shared-memory ring, one CTA per SM
@@ -52,6 +52,7 @@ const TsTune &ts_tune() {
         v.bwd_u = env_int("FMS_TUNE_TSPLIT_BWD_U", 2);
         v.ctas_per_sm = env_int("FMS_TUNE_TSPLIT_CTAS_PER_SM", 2);
         v.l2_hint = env_int("FMS_TUNE_TSPLIT_L2_HINT", 0);
+        v.look = std::max(0, env_int("FMS_TUNE_TSPLIT_LOOK", 0));
         return v;
     }();
     return t;
@@ -93,6 +94,7 @@ int make_exchange(fms::TsExchange &ex, void *const *peer_buffers, int64_t rows, 
     ex.epoch = exchange;
     ex.max_wait_cycles = wait_cycles(max_wait_seconds);
     ex.l2_hint = ts_tune().l2_hint;
+    ex.look = ts_tune().look;
     return FMS_OK;
 }
 

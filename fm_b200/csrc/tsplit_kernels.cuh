@@ -54,6 +54,7 @@ struct TsExchange {
     uint32_t epoch;
     long long max_wait_cycles;
     int l2_hint;  // staged kernels: first pass evict-last, second pass evict-first
+    int look;     // staged kernels: super-tiles of the NEXT row's first pass run before a row's second pass
 };
 
 __device__ __forceinline__ void st_slot(void *p, float P, float S, uint32_t e) {
@@ -104,19 +105,27 @@ __device__ __forceinline__ void ts_finish(const TsExchange &ex, int dir) {
     }
 }
 
-// Warp 0 of a CTA, after pass A of `row`: publish this block's (P, S) to the ranks that need it,
-// wait for the blocks this rank needs and fold them in scan order.  Returns the carry entering
-// this rank's block (every lane).  `fault` is the CTA's sticky fault flag: once set, nothing waits.
-// `publish` is false after an acknowledgement timeout (the slots may still be in use).
-__device__ __forceinline__ float ts_exchange_row(const TsExchange &ex, int dir, int64_t row, float P, float S,
-                                                 bool publish, int lane, volatile int *fault) {
+// Warp 0 of a CTA, after pass A of `row`: store this block's (P, S) into the buffers of the ranks
+// that need it (one lane per peer).  `publish` is false after an acknowledgement timeout (the
+// slots may still be in use).
+__device__ __forceinline__ void ts_publish_row(const TsExchange &ex, int dir, int64_t row, float P, float S,
+                                               bool publish, int lane) {
     const int world = ex.lay.world, rank = ex.rank;
     const int parity = static_cast<int>(ex.epoch & 1u);
-    // forward: later blocks read this one, earlier blocks are read; backward the other way round
+    // forward: later blocks read this one; backward: earlier blocks do
     const bool is_reader = dir == 0 ? (lane > rank && lane < world) : (lane < rank);
-    const bool is_source = dir == 0 ? (lane < rank) : (lane > rank && lane < world);
     if (is_reader && publish)
         st_slot(ex.buf[lane] + ex.lay.slot_index(parity, dir, rank, row) * 16, P, S, ex.epoch);
+}
+
+// Warp 0 of a CTA, before pass B of `row`: wait (bounded, local polls) for the blocks this rank
+// needs and fold them in scan order.  Returns the carry entering this rank's block (every lane).
+// `fault` is the CTA's sticky fault flag: once set, nothing waits and the carry is 0.
+__device__ __forceinline__ float ts_wait_row(const TsExchange &ex, int dir, int64_t row, int lane,
+                                             volatile int *fault) {
+    const int world = ex.lay.world, rank = ex.rank;
+    const int parity = static_cast<int>(ex.epoch & 1u);
+    const bool is_source = dir == 0 ? (lane < rank) : (lane > rank && lane < world);
     float Pq = 1.f, Sq = 0.f;
     bool ok = !is_source;
     if (!*fault) {
@@ -161,6 +170,13 @@ __device__ __forceinline__ float ts_exchange_row(const TsExchange &ex, int dir, 
         }
     }
     return c;
+}
+
+// Publish, then wait and fold (the register-prefetch kernels do both at the same point).
+__device__ __forceinline__ float ts_exchange_row(const TsExchange &ex, int dir, int64_t row, float P, float S,
+                                                 bool publish, int lane, volatile int *fault) {
+    ts_publish_row(ex, dir, row, P, S, publish, lane);
+    return ts_wait_row(ex, dir, row, lane, fault);
 }
 
 // ---------------------------------------------------------------- forward --------------------

@@ -93,7 +93,8 @@ __device__ __forceinline__ void ts_consumer_sync(int threads) {
 // exclusive prefixes -- the pair that maps the block's carry-in to the carry entering that warp's
 // tiles -- and returns the block's total.  The second pass then needs no barrier at all: every
 // warp starts each super-tile from  fma(prefix.P, carry_in, prefix.S).
-constexpr int kTsMaxAgg = 1024;  // (super-tiles per block) x K must fit; longer blocks use the register kernels
+constexpr int kTsMaxAgg = 512;  // (super-tiles per block) x K must fit (two tables: this row's and the next
+                                // row's); longer blocks use the register kernels
 
 __device__ __forceinline__ float2 ts_scan_aggregates(float2 *aggs, int n, int lane) {
     float rp = 1.f, rs = 0.f;  // running total of the chunks done so far
@@ -123,6 +124,27 @@ __device__ __forceinline__ float2 ts_scan_aggregates(float2 *aggs, int n, int la
     return make_float2(rp, rs);
 }
 
+// Order in which a CTA visits (pass, row, super-tile).  Between the two passes of a row the
+// first `look` super-tiles of the NEXT row's first pass are slipped in: a row's carries are then
+// published that much earlier relative to the moment the other ranks need them, which hides the
+// NVLink latency of the exchange (with look = 0 every rank meets every row's carries one hop
+// late).  The price is L2 footprint: (1 + look / super-tiles-per-row) rows per CTA in flight.
+//   A(r0) | [A(r1) first `look`]  B(r0)  [A(r1) rest] | [A(r2) first `look`]  B(r1)  [A(r2) rest] | ...
+// Producer and consumers run the same walk; `fn(pass, i, step)` is called for the i-th row of
+// the CTA and the step-th super-tile in walk order of that pass.
+template <typename F>
+__device__ __forceinline__ void ts_walk(int64_t m, int64_t ngroups, int64_t look, F &&fn) {
+    if (m <= 0) return;
+    for (int64_t g = 0; g < ngroups; ++g) fn(0, static_cast<int64_t>(0), g);
+    for (int64_t i = 0; i < m; ++i) {
+        if (i + 1 < m)
+            for (int64_t g = 0; g < look; ++g) fn(0, i + 1, g);
+        for (int64_t g = 0; g < ngroups; ++g) fn(1, i, g);
+        if (i + 1 < m)
+            for (int64_t g = look; g < ngroups; ++g) fn(0, i + 1, g);
+    }
+}
+
 // Shared memory of one CTA: NT operands per stage, each SUPER elements of S.
 template <typename S, int U, int K, int NT, int STAGES>
 struct TsRing {
@@ -145,7 +167,7 @@ tsplit_forward_tma_kernel(const S *__restrict__ gates, const S *__restrict__ tok
     S *stage_base = reinterpret_cast<S *>(ts_smem);
     uint64_t *full = reinterpret_cast<uint64_t *>(ts_smem + STAGES * Ring::kStageBytes);
     uint64_t *empty = full + STAGES;
-    __shared__ float2 aggs[kTsMaxAgg];
+    __shared__ float2 aggs[2][kTsMaxAgg];  // by parity of the CTA's row counter
     __shared__ float s_carry;
     __shared__ int s_fault;
     const int lane = threadIdx.x & 31;
@@ -165,37 +187,36 @@ tsplit_forward_tma_kernel(const S *__restrict__ gates, const S *__restrict__ tok
     __syncthreads();
     const bool publish_ok = s_fault == 0;
     const int64_t ngroups = (T + SUPER - 1) / SUPER;
+    const int64_t m = (R - blockIdx.x + gridDim.x - 1) / gridDim.x;  // rows of this CTA
+    const int64_t look = min(static_cast<int64_t>(ex.look), ngroups);
 
     if (w == K) {
-        // ---------------- producer: one lane streams (row, pass, group) in consumption order
+        // ---------------- producer: one lane streams the walk in consumption order
         if (lane == 0) {
             unsigned n = 0;
             bool alive = true;
             const uint64_t pol_keep = ts_policy(true), pol_release = ts_policy(false);
-            for (int64_t row = blockIdx.x; row < R && alive; row += gridDim.x) {
-                const int64_t off = row * T;
-                for (int pass = 0; pass < 2 && alive; ++pass) {
-                    for (int64_t g = 0; g < ngroups; ++g, ++n) {
-                        const int s = static_cast<int>(n % STAGES);
-                        if (!ts_mbar_wait(empty + s, ((n / STAGES) & 1u) ^ 1u, &s_fault)) {
-                            alive = false;
-                            break;
-                        }
-                        const int64_t e0 = g * SUPER;
-                        const unsigned bytes = static_cast<unsigned>(min(SUPER, T - e0) * sizeof(S));
-                        S *dst = stage_base + static_cast<size_t>(s) * 2 * SUPER;
-                        ts_mbar_expect_tx(full + s, 2 * bytes);
-                        if (ex.l2_hint) {
-                            const uint64_t pol = pass == 0 ? pol_keep : pol_release;
-                            ts_bulk_load_hint(dst, gates + off + e0, bytes, full + s, pol);
-                            ts_bulk_load_hint(dst + SUPER, tokens + off + e0, bytes, full + s, pol);
-                        } else {
-                            ts_bulk_load(dst, gates + off + e0, bytes, full + s);
-                            ts_bulk_load(dst + SUPER, tokens + off + e0, bytes, full + s);
-                        }
-                    }
+            ts_walk(m, ngroups, look, [&](int pass, int64_t i, int64_t g) {
+                if (!alive) return;
+                const int s = static_cast<int>(n % STAGES);
+                if (!ts_mbar_wait(empty + s, ((n / STAGES) & 1u) ^ 1u, &s_fault)) {
+                    alive = false;
+                    return;
                 }
-            }
+                const int64_t off = (blockIdx.x + i * gridDim.x) * T, e0 = g * SUPER;
+                const unsigned bytes = static_cast<unsigned>(min(SUPER, T - e0) * sizeof(S));
+                S *dst = stage_base + static_cast<size_t>(s) * 2 * SUPER;
+                ts_mbar_expect_tx(full + s, 2 * bytes);
+                if (ex.l2_hint) {
+                    const uint64_t pol = pass == 0 ? pol_keep : pol_release;
+                    ts_bulk_load_hint(dst, gates + off + e0, bytes, full + s, pol);
+                    ts_bulk_load_hint(dst + SUPER, tokens + off + e0, bytes, full + s, pol);
+                } else {
+                    ts_bulk_load(dst, gates + off + e0, bytes, full + s);
+                    ts_bulk_load(dst + SUPER, tokens + off + e0, bytes, full + s);
+                }
+                ++n;
+            });
             if (!alive) {
                 ts_ring_fault(ex, &s_fault);
                 // drain: every stage that was filled completes its copies within the bound
@@ -209,118 +230,125 @@ tsplit_forward_tma_kernel(const S *__restrict__ gates, const S *__restrict__ tok
     } else {
         // ---------------- consumers: K warps, the arithmetic of tsplit_forward_kernel.
         // Inside a pass the warps run free (the ring's barriers are the only coupling); the CTA
-        // meets at two named barriers per row, around the prefix scan and the peer exchange.
-        // A warp whose ring wait ran out keeps walking the loops (every warp must meet every named
-        // barrier) but touches neither the ring nor global memory any more.
+        // meets at two named barriers per row: when the row's first pass is complete (warp 0 then
+        // scans the aggregates and publishes) and before its second pass (warp 0 has the carry-in).
+        // A warp whose ring wait ran out keeps walking (every warp must meet every named barrier)
+        // but touches neither the ring nor global memory any more.
         const int64_t e_lane = static_cast<int64_t>(w) * (TILE * U) + lane * E;  // element offset inside a stage
         unsigned n = 0;
         bool alive = true;
-        for (int64_t row = blockIdx.x; row < R; row += gridDim.x) {
-            const int64_t off = row * T;
-            float hin = 0.f;
-            for (int pass = 0; pass < 2; ++pass) {
-                for (int64_t g = 0; g < ngroups; ++g, ++n) {
-                    const int s = static_cast<int>(n % STAGES);
-                    if (alive && !ts_mbar_wait(full + s, (n / STAGES) & 1u, &s_fault)) {
-                        alive = false;
-                        if (lane == 0) ts_ring_fault(ex, &s_fault);
-                    }
-                    if (!alive) continue;
-                    const S *sa = stage_base + static_cast<size_t>(s) * 2 * SUPER;
-                    const S *sx = sa + SUPER;
-                    const int64_t v = g * SUPER + e_lane;
-                    uint4 ra[U], rx[U];
-#pragma unroll
-                    for (int j = 0; j < U; ++j) {
-                        const bool in = v + j * TILE < T;
-                        ra[j] = in ? *reinterpret_cast<const uint4 *>(sa + e_lane + j * TILE)
-                                   : make_uint4(Store<S>::kOne, Store<S>::kOne, Store<S>::kOne, Store<S>::kOne);
-                        rx[j] = in ? *reinterpret_cast<const uint4 *>(sx + e_lane + j * TILE) : make_uint4(0u, 0u, 0u, 0u);
-                    }
-                    __syncwarp();
-                    if (lane == 0) ts_mbar_arrive(empty + s);  // this warp's tiles are in registers
-
-                    float fa[U][E], fx[U][E], A[U], H[U];
-#pragma unroll
-                    for (int j = 0; j < U; ++j) {
-                        Store<S>::unpack(ra[j], fa[j]);
-                        Store<S>::unpack(rx[j], fx[j]);
-                        A[j] = fa[j][0];
-                        H[j] = fx[j][0];
-#pragma unroll
-                        for (int i = 1; i < E; ++i) {
-                            H[j] = fmaf(fa[j][i], H[j], fx[j][i]);
-                            A[j] *= fa[j][i];
-                        }
-                    }
-#pragma unroll
-                    for (int d = 1; d < 32; d <<= 1) {
-#pragma unroll
-                        for (int j = 0; j < U; ++j) {
-                            const float pA = __shfl_up_sync(kFullMask, A[j], d);
-                            const float pH = __shfl_up_sync(kFullMask, H[j], d);
-                            if (lane >= d) {
-                                H[j] = fmaf(A[j], pH, H[j]);
-                                A[j] *= pA;
-                            }
-                        }
-                    }
-                    const int slot = static_cast<int>(g) * K + w;
-                    if (pass == 0) {
-                        float WA = __shfl_sync(kFullMask, A[0], 31), WH = __shfl_sync(kFullMask, H[0], 31);
-#pragma unroll
-                        for (int j = 1; j < U; ++j) {
-                            const float tA = __shfl_sync(kFullMask, A[j], 31);
-                            WH = fmaf(tA, WH, __shfl_sync(kFullMask, H[j], 31));
-                            WA *= tA;
-                        }
-                        if (lane == 0) aggs[slot] = make_float2(WA, WH);
-                    } else {
-                        const float2 pre = aggs[slot];
-                        float c = fmaf(pre.x, hin, pre.y);  // state entering this warp's first tile
-#pragma unroll
-                        for (int j = 0; j < U; ++j) {
-                            const float tA = __shfl_sync(kFullMask, A[j], 31);
-                            const float tH = __shfl_sync(kFullMask, H[j], 31);
-                            float eA = __shfl_up_sync(kFullMask, A[j], 1);
-                            float eH = __shfl_up_sync(kFullMask, H[j], 1);
-                            if (lane == 0) {
-                                eA = 1.f;
-                                eH = 0.f;
-                            }
-                            float st = fmaf(eA, c, eH);
-                            float out[E];
-#pragma unroll
-                            for (int i = 0; i < E; ++i) {
-                                st = fmaf(fa[j][i], st, fx[j][i]);
-                                out[i] = st;
-                            }
-                            store_vec<S, false>(states + off, v + j * TILE, T, true, Store<S>::pack(out));
-                            c = fmaf(tA, c, tH);
-                        }
+        float hin = 0.f;
+        ts_walk(m, ngroups, look, [&](int pass, int64_t i, int64_t g) {
+            const int64_t row = blockIdx.x + i * gridDim.x, off = row * T;
+            float2 *tab = aggs[i & 1];
+            if (pass == 1 && g == 0) {
+                // the carry entering this row's block: wait for the earlier blocks (published long ago
+                // when look > 0) and fold them
+                if (w == 0 && alive) {
+                    float c_in = ts_wait_row(ex, 0, row, lane, &s_fault);
+                    if (ex.rank == 0) c_in = h0 ? h0[row] : 0.f;
+                    if (lane == 0) {
+                        s_carry = c_in;
+                        h_in_out[row] = c_in;
                     }
                 }
-                if (pass == 0) {
-                    ts_consumer_sync(K * 32);  // every warp's aggregates of this row are in shared memory
-                    if (w == 0 && alive) {
-                        const float2 total = ts_scan_aggregates(aggs, static_cast<int>(ngroups) * K, lane);
-                        float S_pub = total.y, h_first = 0.f;
-                        if (ex.rank == 0 && h0) {  // the first block folds the initial state into what it publishes
-                            h_first = h0[row];
-                            S_pub = fmaf(total.x, h_first, total.y);
-                        }
-                        float c_in = ts_exchange_row(ex, 0, row, total.x, S_pub, publish_ok, lane, &s_fault);
-                        if (ex.rank == 0) c_in = h_first;
-                        if (lane == 0) {
-                            s_carry = c_in;
-                            h_in_out[row] = c_in;
-                        }
-                    }
-                    ts_consumer_sync(K * 32);  // prefixes and the carry-in are published to the CTA
-                    hin = s_carry;
+                ts_consumer_sync(K * 32);  // prefixes (scanned after the first pass) and the carry-in are visible
+                hin = s_carry;
+            }
+            if (alive) {
+                const int s = static_cast<int>(n % STAGES);
+                if (!ts_mbar_wait(full + s, (n / STAGES) & 1u, &s_fault)) {
+                    alive = false;
+                    if (lane == 0) ts_ring_fault(ex, &s_fault);
                 }
             }
-        }
+            if (alive) {
+                const int s = static_cast<int>(n % STAGES);
+                const S *sa = stage_base + static_cast<size_t>(s) * 2 * SUPER;
+                const S *sx = sa + SUPER;
+                const int64_t v = g * SUPER + e_lane;
+                uint4 ra[U], rx[U];
+#pragma unroll
+                for (int j = 0; j < U; ++j) {
+                    const bool in = v + j * TILE < T;
+                    ra[j] = in ? *reinterpret_cast<const uint4 *>(sa + e_lane + j * TILE)
+                               : make_uint4(Store<S>::kOne, Store<S>::kOne, Store<S>::kOne, Store<S>::kOne);
+                    rx[j] = in ? *reinterpret_cast<const uint4 *>(sx + e_lane + j * TILE) : make_uint4(0u, 0u, 0u, 0u);
+                }
+                __syncwarp();
+                if (lane == 0) ts_mbar_arrive(empty + s);  // this warp's tiles are in registers
+
+                float fa[U][E], fx[U][E], A[U], H[U];
+#pragma unroll
+                for (int j = 0; j < U; ++j) {
+                    Store<S>::unpack(ra[j], fa[j]);
+                    Store<S>::unpack(rx[j], fx[j]);
+                    A[j] = fa[j][0];
+                    H[j] = fx[j][0];
+#pragma unroll
+                    for (int k = 1; k < E; ++k) {
+                        H[j] = fmaf(fa[j][k], H[j], fx[j][k]);
+                        A[j] *= fa[j][k];
+                    }
+                }
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+#pragma unroll
+                    for (int j = 0; j < U; ++j) {
+                        const float pA = __shfl_up_sync(kFullMask, A[j], d);
+                        const float pH = __shfl_up_sync(kFullMask, H[j], d);
+                        if (lane >= d) {
+                            H[j] = fmaf(A[j], pH, H[j]);
+                            A[j] *= pA;
+                        }
+                    }
+                }
+                const int slot = static_cast<int>(g) * K + w;
+                if (pass == 0) {
+                    float WA = __shfl_sync(kFullMask, A[0], 31), WH = __shfl_sync(kFullMask, H[0], 31);
+#pragma unroll
+                    for (int j = 1; j < U; ++j) {
+                        const float tA = __shfl_sync(kFullMask, A[j], 31);
+                        WH = fmaf(tA, WH, __shfl_sync(kFullMask, H[j], 31));
+                        WA *= tA;
+                    }
+                    if (lane == 0) tab[slot] = make_float2(WA, WH);
+                } else {
+                    const float2 pre = tab[slot];
+                    float c = fmaf(pre.x, hin, pre.y);  // state entering this warp's first tile
+#pragma unroll
+                    for (int j = 0; j < U; ++j) {
+                        const float tA = __shfl_sync(kFullMask, A[j], 31);
+                        const float tH = __shfl_sync(kFullMask, H[j], 31);
+                        float eA = __shfl_up_sync(kFullMask, A[j], 1);
+                        float eH = __shfl_up_sync(kFullMask, H[j], 1);
+                        if (lane == 0) {
+                            eA = 1.f;
+                            eH = 0.f;
+                        }
+                        float st = fmaf(eA, c, eH);
+                        float out[E];
+#pragma unroll
+                        for (int k = 0; k < E; ++k) {
+                            st = fmaf(fa[j][k], st, fx[j][k]);
+                            out[k] = st;
+                        }
+                        store_vec<S, false>(states + off, v + j * TILE, T, true, Store<S>::pack(out));
+                        c = fmaf(tA, c, tH);
+                    }
+                }
+            }
+            ++n;
+            if (pass == 0 && g == ngroups - 1) {
+                ts_consumer_sync(K * 32);  // every warp's aggregates of this row are in shared memory
+                if (w == 0 && alive) {
+                    const float2 total = ts_scan_aggregates(tab, static_cast<int>(ngroups) * K, lane);
+                    float S_pub = total.y;
+                    if (ex.rank == 0 && h0) S_pub = fmaf(total.x, h0[row], total.y);  // the first block folds h0 in
+                    ts_publish_row(ex, 0, row, total.x, S_pub, publish_ok, lane);
+                }
+            }
+        });
     }
     __syncthreads();
     if (threadIdx.x == 0) ts_finish(ex, 0);
@@ -340,7 +368,7 @@ tsplit_backward_tma_kernel(const S *__restrict__ gates, const S *__restrict__ st
     S *stage_base = reinterpret_cast<S *>(ts_smem);
     uint64_t *full = reinterpret_cast<uint64_t *>(ts_smem + STAGES * Ring::kStageBytes);
     uint64_t *empty = full + STAGES;
-    __shared__ float2 aggs[kTsMaxAgg];
+    __shared__ float2 aggs[2][kTsMaxAgg];
     __shared__ float s_carry;
     __shared__ int s_fault;
     const int lane = threadIdx.x & 31;
@@ -360,38 +388,38 @@ tsplit_backward_tma_kernel(const S *__restrict__ gates, const S *__restrict__ st
     __syncthreads();
     const bool publish_ok = s_fault == 0;
     const int64_t ngroups = (T + SUPER - 1) / SUPER;
+    const int64_t m = (R - blockIdx.x + gridDim.x - 1) / gridDim.x;
+    const int64_t look = min(static_cast<int64_t>(ex.look), ngroups);
 
     if (w == K) {
         if (lane == 0) {
             unsigned n = 0;
             bool alive = true;
             const uint64_t pol_keep = ts_policy(true), pol_release = ts_policy(false);
-            for (int64_t row = blockIdx.x; row < R && alive; row += gridDim.x) {
-                const int64_t off = row * T;
-                for (int pass = 0; pass < 2 && alive; ++pass) {
-                    for (int64_t g = ngroups - 1; g >= 0; --g, ++n) {  // time runs backwards
-                        const int s = static_cast<int>(n % STAGES);
-                        if (!ts_mbar_wait(empty + s, ((n / STAGES) & 1u) ^ 1u, &s_fault)) {
-                            alive = false;
-                            break;
-                        }
-                        const int64_t e0 = g * SUPER;
-                        const unsigned bytes = static_cast<unsigned>(min(SUPER, T - e0) * sizeof(S));
-                        S *dst = stage_base + static_cast<size_t>(s) * 3 * SUPER;
-                        ts_mbar_expect_tx(full + s, (pass == 1 ? 3 : 2) * bytes);
-                        if (ex.l2_hint) {
-                            const uint64_t pol = pass == 0 ? pol_keep : pol_release;
-                            ts_bulk_load_hint(dst, gates + off + e0, bytes, full + s, pol);
-                            ts_bulk_load_hint(dst + SUPER, grad_states + off + e0, bytes, full + s, pol);
-                            if (pass == 1) ts_bulk_load_hint(dst + 2 * SUPER, states + off + e0, bytes, full + s, pol_release);
-                        } else {
-                            ts_bulk_load(dst, gates + off + e0, bytes, full + s);
-                            ts_bulk_load(dst + SUPER, grad_states + off + e0, bytes, full + s);
-                            if (pass == 1) ts_bulk_load(dst + 2 * SUPER, states + off + e0, bytes, full + s);
-                        }
-                    }
+            ts_walk(m, ngroups, look, [&](int pass, int64_t i, int64_t step) {
+                if (!alive) return;
+                const int s = static_cast<int>(n % STAGES);
+                if (!ts_mbar_wait(empty + s, ((n / STAGES) & 1u) ^ 1u, &s_fault)) {
+                    alive = false;
+                    return;
                 }
-            }
+                const int64_t g = ngroups - 1 - step;  // time runs backwards
+                const int64_t off = (blockIdx.x + i * gridDim.x) * T, e0 = g * SUPER;
+                const unsigned bytes = static_cast<unsigned>(min(SUPER, T - e0) * sizeof(S));
+                S *dst = stage_base + static_cast<size_t>(s) * 3 * SUPER;
+                ts_mbar_expect_tx(full + s, (pass == 1 ? 3 : 2) * bytes);
+                if (ex.l2_hint) {
+                    const uint64_t pol = pass == 0 ? pol_keep : pol_release;
+                    ts_bulk_load_hint(dst, gates + off + e0, bytes, full + s, pol);
+                    ts_bulk_load_hint(dst + SUPER, grad_states + off + e0, bytes, full + s, pol);
+                    if (pass == 1) ts_bulk_load_hint(dst + 2 * SUPER, states + off + e0, bytes, full + s, pol_release);
+                } else {
+                    ts_bulk_load(dst, gates + off + e0, bytes, full + s);
+                    ts_bulk_load(dst + SUPER, grad_states + off + e0, bytes, full + s);
+                    if (pass == 1) ts_bulk_load(dst + 2 * SUPER, states + off + e0, bytes, full + s);
+                }
+                ++n;
+            });
             if (!alive) {
                 ts_ring_fault(ex, &s_fault);
                 for (unsigned k = n > STAGES ? n - STAGES : 0; k < n; ++k) {
@@ -405,130 +433,138 @@ tsplit_backward_tma_kernel(const S *__restrict__ gates, const S *__restrict__ st
         const int64_t e_lane = static_cast<int64_t>(w) * (TILE * U) + lane * E;
         unsigned n = 0;
         bool alive = true;
-        for (int64_t row = blockIdx.x; row < R; row += gridDim.x) {
-            const int64_t off = row * T;
-            float cin = 0.f, h_before = 0.f;
-            for (int pass = 0; pass < 2; ++pass) {
-                for (int64_t g = ngroups - 1; g >= 0; --g, ++n) {
-                    const int s = static_cast<int>(n % STAGES);
-                    const int64_t v = g * SUPER + e_lane;
-                    // the state just before this group sits outside the stage: one scalar from global
-                    // memory, asked for before the wait (only the first lane of the group's first tile)
-                    float group_halo = 0.f;
-                    if (alive && pass == 1 && w == 0 && lane == 0 && g > 0)
-                        group_halo = Store<S>::to_float(states[off + g * SUPER - 1]);
-                    if (alive && !ts_mbar_wait(full + s, (n / STAGES) & 1u, &s_fault)) {
-                        alive = false;
-                        if (lane == 0) ts_ring_fault(ex, &s_fault);
-                    }
-                    if (!alive) continue;
-                    const S *sa = stage_base + static_cast<size_t>(s) * 3 * SUPER;
-                    const S *sg = sa + SUPER, *sh = sa + 2 * SUPER;
-                    uint4 ra[U], rg[U], rh[U];
-                    float halo[U];
-#pragma unroll
-                    for (int j = 0; j < U; ++j) {
-                        const bool in = v + j * TILE < T;
-                        ra[j] = in ? *reinterpret_cast<const uint4 *>(sa + e_lane + j * TILE)
-                                   : make_uint4(Store<S>::kOne, Store<S>::kOne, Store<S>::kOne, Store<S>::kOne);
-                        rg[j] = in ? *reinterpret_cast<const uint4 *>(sg + e_lane + j * TILE) : make_uint4(0u, 0u, 0u, 0u);
-                        rh[j] = make_uint4(0u, 0u, 0u, 0u);
-                        halo[j] = 0.f;
-                        if (pass == 1 && in) {
-                            rh[j] = *reinterpret_cast<const uint4 *>(sh + e_lane + j * TILE);
-                            if (lane == 0) {
-                                const int64_t ee = e_lane + j * TILE;  // first element of this tile inside the stage
-                                halo[j] = ee > 0 ? Store<S>::to_float(sh[ee - 1]) : group_halo;
-                            }
-                        }
-                    }
-                    __syncwarp();
-                    if (lane == 0) ts_mbar_arrive(empty + s);
-
-                    float fa[U][E], fg[U][E], A[U], C[U];
-#pragma unroll
-                    for (int j = 0; j < U; ++j) {
-                        Store<S>::unpack(ra[j], fa[j]);
-                        Store<S>::unpack(rg[j], fg[j]);
-                        A[j] = fa[j][E - 1];
-                        C[j] = fa[j][E - 1] * fg[j][E - 1];
-#pragma unroll
-                        for (int i = E - 2; i >= 0; --i) {
-                            C[j] = fa[j][i] * (fg[j][i] + C[j]);
-                            A[j] *= fa[j][i];
-                        }
-                    }
-#pragma unroll
-                    for (int d = 1; d < 32; d <<= 1) {
-#pragma unroll
-                        for (int j = 0; j < U; ++j) {
-                            const float pA = __shfl_down_sync(kFullMask, A[j], d);
-                            const float pC = __shfl_down_sync(kFullMask, C[j], d);
-                            if (lane + d < 32) {
-                                C[j] = fmaf(A[j], pC, C[j]);
-                                A[j] *= pA;
-                            }
-                        }
-                    }
-                    // walk order: super-tiles from the last one down, warps from K-1 down
-                    const int slot = static_cast<int>(ngroups - 1 - g) * K + (K - 1 - w);
-                    if (pass == 0) {
-                        float WA = __shfl_sync(kFullMask, A[U - 1], 0), WC = __shfl_sync(kFullMask, C[U - 1], 0);
-#pragma unroll
-                        for (int j = U - 2; j >= 0; --j) {
-                            const float tA = __shfl_sync(kFullMask, A[j], 0);
-                            WC = fmaf(tA, WC, __shfl_sync(kFullMask, C[j], 0));
-                            WA *= tA;
-                        }
-                        if (lane == 0) aggs[slot] = make_float2(WA, WC);
-                    } else {
-                        const float2 pre = aggs[slot];
-                        float cw = fmaf(pre.x, cin, pre.y);  // c just after this warp's last tile
-#pragma unroll
-                        for (int j = U - 1; j >= 0; --j) {
-                            const float tA = __shfl_sync(kFullMask, A[j], 0);
-                            const float tC = __shfl_sync(kFullMask, C[j], 0);
-                            float eA = __shfl_down_sync(kFullMask, A[j], 1);
-                            float eC = __shfl_down_sync(kFullMask, C[j], 1);
-                            if (lane == 31) {
-                                eA = 1.f;
-                                eC = 0.f;
-                            }
-                            float fh[E];
-                            Store<S>::unpack(rh[j], fh);
-                            float hprev0 = __shfl_up_sync(kFullMask, fh[E - 1], 1);
-                            if (lane == 0) hprev0 = (v + j * TILE - 1 >= 0) ? halo[j] : h_before;
-                            float c = fmaf(eA, cw, eC);
-                            float dx[E], da[E];
-#pragma unroll
-                            for (int i = E - 1; i >= 0; --i) {
-                                const float delta = fg[j][i] + c;
-                                c = fa[j][i] * delta;
-                                const float hp = (i > 0) ? fh[i > 0 ? i - 1 : 0] : hprev0;
-                                dx[i] = delta;
-                                da[i] = delta * hp;
-                            }
-                            store_vec<S, false>(grad_tokens + off, v + j * TILE, T, true, Store<S>::pack(dx));
-                            store_vec<S, false>(grad_gates + off, v + j * TILE, T, true, Store<S>::pack(da));
-                            cw = fmaf(tA, cw, tC);
-                        }
-                        // the warp that owns the block's first tile ends with c at the block start
-                        if (grad_h0 && g == 0 && w == 0 && lane == 0) grad_h0[row] = cw;
-                    }
+        float cin = 0.f, h_before = 0.f;
+        ts_walk(m, ngroups, look, [&](int pass, int64_t i, int64_t step) {
+            const int64_t row = blockIdx.x + i * gridDim.x, off = row * T;
+            const int64_t g = ngroups - 1 - step;
+            float2 *tab = aggs[i & 1];
+            if (pass == 1 && step == 0) {
+                if (w == 0 && alive) {
+                    const float c_in = ts_wait_row(ex, 1, row, lane, &s_fault);
+                    if (lane == 0) s_carry = c_in;
                 }
-                if (pass == 0) {
-                    ts_consumer_sync(K * 32);
-                    if (w == 0 && alive) {
-                        const float2 total = ts_scan_aggregates(aggs, static_cast<int>(ngroups) * K, lane);
-                        const float c_in = ts_exchange_row(ex, 1, row, total.x, total.y, publish_ok, lane, &s_fault);
-                        if (lane == 0) s_carry = c_in;
-                    }
-                    ts_consumer_sync(K * 32);
-                    cin = s_carry;
-                    h_before = h_in ? h_in[row] : 0.f;
+                ts_consumer_sync(K * 32);
+                cin = s_carry;
+                h_before = h_in ? h_in[row] : 0.f;
+            }
+            const int64_t v = g * SUPER + e_lane;
+            // the state just before this group sits outside the stage: one scalar from global memory,
+            // asked for before the wait (only the first lane of the group's first tile)
+            float group_halo = 0.f;
+            if (alive && pass == 1 && w == 0 && lane == 0 && g > 0)
+                group_halo = Store<S>::to_float(states[off + g * SUPER - 1]);
+            if (alive) {
+                const int s = static_cast<int>(n % STAGES);
+                if (!ts_mbar_wait(full + s, (n / STAGES) & 1u, &s_fault)) {
+                    alive = false;
+                    if (lane == 0) ts_ring_fault(ex, &s_fault);
                 }
             }
-        }
+            if (alive) {
+                const int s = static_cast<int>(n % STAGES);
+                const S *sa = stage_base + static_cast<size_t>(s) * 3 * SUPER;
+                const S *sg = sa + SUPER, *sh = sa + 2 * SUPER;
+                uint4 ra[U], rg[U], rh[U];
+                float halo[U];
+#pragma unroll
+                for (int j = 0; j < U; ++j) {
+                    const bool in = v + j * TILE < T;
+                    ra[j] = in ? *reinterpret_cast<const uint4 *>(sa + e_lane + j * TILE)
+                               : make_uint4(Store<S>::kOne, Store<S>::kOne, Store<S>::kOne, Store<S>::kOne);
+                    rg[j] = in ? *reinterpret_cast<const uint4 *>(sg + e_lane + j * TILE) : make_uint4(0u, 0u, 0u, 0u);
+                    rh[j] = make_uint4(0u, 0u, 0u, 0u);
+                    halo[j] = 0.f;
+                    if (pass == 1 && in) {
+                        rh[j] = *reinterpret_cast<const uint4 *>(sh + e_lane + j * TILE);
+                        if (lane == 0) {
+                            const int64_t ee = e_lane + j * TILE;  // first element of this tile inside the stage
+                            halo[j] = ee > 0 ? Store<S>::to_float(sh[ee - 1]) : group_halo;
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) ts_mbar_arrive(empty + s);
+
+                float fa[U][E], fg[U][E], A[U], C[U];
+#pragma unroll
+                for (int j = 0; j < U; ++j) {
+                    Store<S>::unpack(ra[j], fa[j]);
+                    Store<S>::unpack(rg[j], fg[j]);
+                    A[j] = fa[j][E - 1];
+                    C[j] = fa[j][E - 1] * fg[j][E - 1];
+#pragma unroll
+                    for (int k = E - 2; k >= 0; --k) {
+                        C[j] = fa[j][k] * (fg[j][k] + C[j]);
+                        A[j] *= fa[j][k];
+                    }
+                }
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+#pragma unroll
+                    for (int j = 0; j < U; ++j) {
+                        const float pA = __shfl_down_sync(kFullMask, A[j], d);
+                        const float pC = __shfl_down_sync(kFullMask, C[j], d);
+                        if (lane + d < 32) {
+                            C[j] = fmaf(A[j], pC, C[j]);
+                            A[j] *= pA;
+                        }
+                    }
+                }
+                // walk order: super-tiles from the last one down, warps from K-1 down
+                const int slot = static_cast<int>(step) * K + (K - 1 - w);
+                if (pass == 0) {
+                    float WA = __shfl_sync(kFullMask, A[U - 1], 0), WC = __shfl_sync(kFullMask, C[U - 1], 0);
+#pragma unroll
+                    for (int j = U - 2; j >= 0; --j) {
+                        const float tA = __shfl_sync(kFullMask, A[j], 0);
+                        WC = fmaf(tA, WC, __shfl_sync(kFullMask, C[j], 0));
+                        WA *= tA;
+                    }
+                    if (lane == 0) tab[slot] = make_float2(WA, WC);
+                } else {
+                    const float2 pre = tab[slot];
+                    float cw = fmaf(pre.x, cin, pre.y);  // c just after this warp's last tile
+#pragma unroll
+                    for (int j = U - 1; j >= 0; --j) {
+                        const float tA = __shfl_sync(kFullMask, A[j], 0);
+                        const float tC = __shfl_sync(kFullMask, C[j], 0);
+                        float eA = __shfl_down_sync(kFullMask, A[j], 1);
+                        float eC = __shfl_down_sync(kFullMask, C[j], 1);
+                        if (lane == 31) {
+                            eA = 1.f;
+                            eC = 0.f;
+                        }
+                        float fh[E];
+                        Store<S>::unpack(rh[j], fh);
+                        float hprev0 = __shfl_up_sync(kFullMask, fh[E - 1], 1);
+                        if (lane == 0) hprev0 = (v + j * TILE - 1 >= 0) ? halo[j] : h_before;
+                        float c = fmaf(eA, cw, eC);
+                        float dx[E], da[E];
+#pragma unroll
+                        for (int k = E - 1; k >= 0; --k) {
+                            const float delta = fg[j][k] + c;
+                            c = fa[j][k] * delta;
+                            const float hp = (k > 0) ? fh[k > 0 ? k - 1 : 0] : hprev0;
+                            dx[k] = delta;
+                            da[k] = delta * hp;
+                        }
+                        store_vec<S, false>(grad_tokens + off, v + j * TILE, T, true, Store<S>::pack(dx));
+                        store_vec<S, false>(grad_gates + off, v + j * TILE, T, true, Store<S>::pack(da));
+                        cw = fmaf(tA, cw, tC);
+                    }
+                    // the warp that owns the block's first tile ends with c at the block start
+                    if (grad_h0 && g == 0 && w == 0 && lane == 0) grad_h0[row] = cw;
+                }
+            }
+            ++n;
+            if (pass == 0 && step == ngroups - 1) {
+                ts_consumer_sync(K * 32);
+                if (w == 0 && alive) {
+                    const float2 total = ts_scan_aggregates(tab, static_cast<int>(ngroups) * K, lane);
+                    ts_publish_row(ex, 1, row, total.x, total.y, publish_ok, lane);
+                }
+            }
+        });
     }
     __syncthreads();
     if (threadIdx.x == 0) ts_finish(ex, 1);

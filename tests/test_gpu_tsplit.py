@@ -58,28 +58,38 @@ def _run_step(L, ptrs, world, blocks, h0, number, wait=0.5):
     return hs, grads, gh0
 
 
-@pytest.mark.parametrize("launch", [{},                                        # staged ring, 16 warps per row
-                                    {"FMS_TUNE_TSPLIT_K": "8"},                # staged ring, 8 warps per row
-                                    {"FMS_TUNE_TSPLIT_K": "24", "FMS_TUNE_TSPLIT_L2_HINT": "1"},   # 24 warps, L2 hints
-                                    {"FMS_TUNE_TSPLIT_STAGED": "0"},           # register prefetch, 8 warps
-                                    {"FMS_TUNE_TSPLIT_STAGED": "0", "FMS_TUNE_TSPLIT_K": "16"},
-                                    {"FMS_TUNE_TSPLIT_STAGED": "0", "FMS_TUNE_TSPLIT_U": "2",
-                                     "FMS_TUNE_TSPLIT_BWD_U": "4"}])
-@pytest.mark.parametrize("storage,world,R,Tk", [("f32", 2, 37, 4096 + 512), ("bf16", 3, 300, 8192), ("f16", 8, 5, 1024),
-                                                ("f32", 4, 700, 2052), ("f32", 2, 3, 40000),
-                                                ("bf16", 2, 2, 1 << 21)])   # too long for the staged kernels' table
+LAUNCHES = [{},                                                      # staged ring, 16 warps per row, no look-ahead
+            {"FMS_TUNE_TSPLIT_K": "8", "FMS_TUNE_TSPLIT_LOOK": "1"},     # staged ring, 8 warps, look-ahead 1
+            {"FMS_TUNE_TSPLIT_K": "24", "FMS_TUNE_TSPLIT_L2_HINT": "1", "FMS_TUNE_TSPLIT_LOOK": "3"},
+            {"FMS_TUNE_TSPLIT_LOOK": "1000"},                            # whole next row before a row's second pass
+            {"FMS_TUNE_TSPLIT_STAGED": "0"},                             # register prefetch, 8 warps
+            {"FMS_TUNE_TSPLIT_STAGED": "0", "FMS_TUNE_TSPLIT_K": "16", "FMS_TUNE_TSPLIT_U": "2",
+             "FMS_TUNE_TSPLIT_BWD_U": "4"}]
+SHAPES = [("f32", 2, 37, 4096 + 512), ("bf16", 3, 300, 8192), ("f16", 8, 5, 1024), ("f32", 4, 700, 2052),
+          ("f32", 2, 450, 40000),                                        # several rows per CTA, 5 super-tiles, ragged
+          ("bf16", 2, 2, 1 << 21)]                                       # too long for the staged kernels' table
+
+
+@pytest.mark.parametrize("launch", range(len(LAUNCHES)))
+@pytest.mark.parametrize("storage,world,R,Tk", SHAPES)
 def test_fused_split_matches_the_oracle_over_three_steps(storage, world, R, Tk, launch):
     import os
     import subprocess
     import sys
-    if launch:
-        # the launch shape of these kernels is read once per process: run this case in a child
-        env = dict(os.environ, **launch, FMS_TSPLIT_CHILD="1")
+    child = os.environ.get("FMS_TSPLIT_CHILD")
+    if child is None and launch:
+        # the launch shape of these kernels is read once per process: each non-default shape runs ALL
+        # its cases in one child process (started from the first case)
+        if (storage, world, R, Tk) != SHAPES[0]:
+            pytest.skip("runs in the child process started by the first case")
+        env = dict(os.environ, **LAUNCHES[launch], FMS_TSPLIT_CHILD=str(launch))
         res = subprocess.run([sys.executable, "-m", "pytest", "-x", "-q", "-m", "gpu",
-                              f"{__file__}::test_fused_split_matches_the_oracle_over_three_steps"
-                              f"[{storage}-{world}-{R}-{Tk}-launch0]"], env=env, capture_output=True, text=True)
+                              f"{__file__}::test_fused_split_matches_the_oracle_over_three_steps"],
+                             env=env, capture_output=True, text=True)
         assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-2000:]
         return
+    if child is not None and int(child) != launch:
+        pytest.skip("another launch shape")
     L, bufs, ptrs, status_off = _buffers(R, world)
     T = world * Tk
     f64 = np.float64

@@ -27,7 +27,7 @@
 namespace fms {
 
 template <typename S, int MC, int DC, int PD>
-__global__ void __launch_bounds__(MC * 32, DC <= 4 ? 3 : 2)
+__global__ void __launch_bounds__(MC * 32, 2)
 fm_backward_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
                            const S *__restrict__ states, const S *__restrict__ grad_states,
                            const float *__restrict__ h0, float *__restrict__ acc_gates,

@@ -49,7 +49,7 @@ struct Tune {
     int fwd_k = 0, bwd_k = 0, fwd_u = 0, bwd_u = 0;  // 0 = choose from the shape
     int max_ctas = 0x7fffffff;                       // test knob: forces the multi-row walk
     int persist = -1;                                // -1 = choose from the shape, 0 = off, 1 = on
-    int fm_pd = 4, fm_blocked = 1, fm_dc = 8, btd_warps_per_sm = 32;
+    int fm_pd = 4, fm_blocked = 1, btd_warps_per_sm = 32;
     int bwd_descending = 1;  // backward visits rows last-to-first (re-reads the forward's latest rows from L2)
     int fwd_keep = 0;        // L2 policy of the forward's state stores: 0 evict-first, 1 normal, 2 evict-last
 };
@@ -71,7 +71,6 @@ void load_tune() {
     t.persist = get("FMS_TUNE_PERSIST", -1);
     t.fm_pd = get("FMS_TUNE_FM_PD", 4);
     t.fm_blocked = get("FMS_TUNE_FM_BLOCKED", 1);
-    t.fm_dc = get("FMS_TUNE_FM_DC", 8);
     t.btd_warps_per_sm = std::max(1, get("FMS_TUNE_BTD_WARPS_PER_SM", 32));
     t.bwd_descending = get("FMS_TUNE_BWD_DESCENDING", 1);
     t.fwd_keep = get("FMS_TUNE_FWD_KEEP", 0);
@@ -546,11 +545,12 @@ template <typename S>
 int launch_fm_backward_blocked(const FmShape &sh, const void *gates, const void *tokens, const void *states,
                                const void *grad_states, const float *h0, float *acc_gates, float *acc_tokens,
                                float *grad_h0, cudaStream_t st) {
-    // CTA block: MC = 8 gate rows (one warp each) x DC token rows.  DC = 8 amortises the gate half
-    // of the scan over 8 rows and halves the global reductions; DC = 4 halves the shared-memory
-    // tile buffer and the per-thread state, so three CTAs fit an SM instead of two.
+    // CTA block: 8 gate rows (one warp each) x 8 token rows.  Four token rows per CTA (half the
+    // shared-memory tile buffer, three CTAs per SM at 80 registers) was measured and is no faster:
+    // 0.955-1.21 ms against 0.961 ms at (1,32,2048,8192) bf16 -- the spills it forces and the doubled
+    // gate-row reductions eat the occupancy.
     constexpr int MC = 8;
-    const int dc = tune().fm_dc == 4 ? 4 : 8;
+    constexpr int dc = 8;
     const int64_t m_blocks = (sh.M + MC - 1) / MC, d_blocks = (sh.D + dc - 1) / dc;
     if (sh.B > 0x7fffffffLL / m_blocks || sh.B * m_blocks > 0x7fffffffLL / d_blocks) return FMS_ERR_BAD_SHAPE;
     const unsigned grid = static_cast<unsigned>(sh.B * m_blocks * d_blocks);
@@ -567,9 +567,12 @@ int launch_fm_backward_blocked(const FmShape &sh, const void *gates, const void 
             static_cast<const S *>(states), static_cast<const S *>(grad_states), h0, acc_gates,     \
             acc_tokens, grad_h0, sh.M, sh.D, sh.L, m_blocks, d_blocks);                             \
     } while (0)
-    if (dc == 4 && tune().fm_pd == 2) FMS_LAUNCH_FM_BLOCKED(4, 2);
-    else if (dc == 4) FMS_LAUNCH_FM_BLOCKED(4, 4);
-    else FMS_LAUNCH_FM_BLOCKED(8, 4);
+#ifdef FMS_ALL_VARIANTS
+    if (tune().fm_pd == 2) FMS_LAUNCH_FM_BLOCKED(8, 2);
+    else if (tune().fm_pd == 8) FMS_LAUNCH_FM_BLOCKED(8, 8);
+    else
+#endif
+        FMS_LAUNCH_FM_BLOCKED(8, 4);
 #undef FMS_LAUNCH_FM_BLOCKED
     return check_launch();
 }

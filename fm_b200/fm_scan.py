@@ -20,6 +20,8 @@ import importlib
 
 import torch
 
+from ._nvtx import nvtx_range
+
 _ext = None
 
 
@@ -110,7 +112,8 @@ class FM_Scan(torch.autograd.Function):
             assert initial_state.shape == gates.shape[:-1]
             assert initial_state.is_contiguous()
         output = torch.empty_like(gates)
-        states = fm_scan_forward(gates, tokens, initial_state, output)
+        with nvtx_range("fm_scan.forward"):
+            states = fm_scan_forward(gates, tokens, initial_state, output)
         ctx.save_for_backward(gates, states, initial_state)
         ctx.h0_needs_grad = initial_state is not None and ctx.needs_input_grad[2]
         return states
@@ -124,7 +127,8 @@ class FM_Scan(torch.autograd.Function):
         d_h0 = None
         if ctx.h0_needs_grad:
             d_h0 = torch.empty(initial_state.shape, device=gates.device, dtype=torch.float32)
-        fm_scan_backward_ex(gates, grad_output, None, d_tokens, states, d_gates, initial_state, d_h0)
+        with nvtx_range("fm_scan.backward"):
+            fm_scan_backward_ex(gates, grad_output, None, d_tokens, states, d_gates, initial_state, d_h0)
         if d_h0 is not None:
             d_h0 = d_h0.to(initial_state.dtype)
         return d_gates, d_tokens, d_h0

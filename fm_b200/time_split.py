@@ -31,6 +31,7 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
+from ._nvtx import nvtx_range
 from .ops import CudaScanOps
 from .peer_exchange import FusedTimeSplit
 
@@ -56,7 +57,8 @@ class _TimeSplitScan(torch.autograd.Function):
             h0 = None
             if rank == 0 and initial_state is not None:
                 h0 = initial_state.to(torch.float32).reshape(-1).contiguous()
-            states, h_in = exchange.forward(gates, tokens, h0)
+            with nvtx_range("fm_scan.time_split.forward(fused: carry pass + exchange + scan pass)"):
+                states, h_in = exchange.forward(gates, tokens, h0)
             ctx.save_for_backward(gates, states, h_in)
             ctx.group, ctx.ops, ctx.rank, ctx.world, ctx.exchange = group, ops, rank, world, exchange
             ctx.fused = True
@@ -67,7 +69,8 @@ class _TimeSplitScan(torch.autograd.Function):
         if isinstance(exchange, FusedTimeSplit):
             raise RuntimeError("FusedTimeSplit needs 16-byte aligned rows (T_k * element size % 16 == 0); "
                                "use PeerCarryExchange or the default all-gather for this shape")
-        P, S = ops.reduce(gates, tokens)
+        with nvtx_range("fm_scan.time_split.carry_pass"):
+            P, S = ops.reduce(gates, tokens)
         # The initial state belongs to the first block only.  Rank 0 folds it into the carry it
         # publishes (S_0 <- P_0*h0 + S_0) and scans from it; the other ranks never look at their
         # `initial_state` argument, so no collective depends on who passed one.
@@ -88,7 +91,8 @@ class _TimeSplitScan(torch.autograd.Function):
             else:
                 h_in_all, _ = ops.combine(P_keep, PS[:, 1].contiguous(), None, reverse=False)
                 h_in = h_in_all[rank].reshape(rows_shape).contiguous()
-        states = ops.forward(gates, tokens, h_in)
+        with nvtx_range("fm_scan.time_split.scan_pass"):
+            states = ops.forward(gates, tokens, h_in)
         ctx.save_for_backward(gates, states, h_in, P_keep)
         ctx.group, ctx.ops, ctx.rank, ctx.world, ctx.exchange = group, ops, rank, world, exchange
         ctx.h0_dtype = None if initial_state is None else initial_state.dtype
@@ -99,8 +103,9 @@ class _TimeSplitScan(torch.autograd.Function):
     def backward(ctx, grad_states):
         if ctx.fused:
             gates, states, h_in = ctx.saved_tensors
-            grad_gates, grad_tokens, grad_h0 = ctx.exchange.backward(
-                gates, states, grad_states.contiguous(), h_in, want_grad_h0=ctx.h0_needs_grad)
+            with nvtx_range("fm_scan.time_split.backward(fused)"):
+                grad_gates, grad_tokens, grad_h0 = ctx.exchange.backward(
+                    gates, states, grad_states.contiguous(), h_in, want_grad_h0=ctx.h0_needs_grad)
             d_h0 = None
             if ctx.h0_needs_grad:
                 d_h0 = grad_h0 if ctx.rank == 0 else torch.zeros_like(grad_h0)

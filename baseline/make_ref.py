@@ -1,6 +1,6 @@
 """Put the UNMODIFIED reference under ``baseline/_ref/`` so that it can run beside this library.
 
-    python baseline/make_ref.py [/path/to/lexionbear-fm]
+    python baseline/make_ref.py [/path/to/lexionbear-fm] [--prebuild]
 
 The reference (lexionbear/fm, MIT) is not an installable package -- it has no ``setup.py`` or
 ``pyproject.toml`` -- so "installing" it means placing its ``fm/`` tree (5 files) and LICENSE in
@@ -53,9 +53,34 @@ def prebuild() -> None:
     import fm.scan.fm_scan  # noqa: F401  (compiles and loads the reference's extension)
 
 
+def find_reference():
+    """A checkout of the reference: ``$FM_REFERENCE``, else a folder ``reference`` beside this repository."""
+    for cand in (os.environ.get("FM_REFERENCE"), HERE.parent.parent / "reference"):
+        if cand and (Path(cand) / "fm" / "scan" / "fm_scan.cuh").exists():
+            return Path(cand)
+    return None
+
+
+def ensure(prebuilt: bool = True) -> bool:
+    """Place the reference if a checkout can be found and, unless it is there already, build its
+    extension.  Returns False when no checkout is available (nothing is done then)."""
+    src = find_reference()
+    if src is None:
+        return False
+    install(src)
+    if prebuilt and not (EXT_DIR / "fm_scan" / "fm_scan.so").exists():
+        import subprocess
+        subprocess.run([sys.executable, str(Path(__file__).resolve()), str(src), "--prebuild"], check=True,
+                       env=dict(os.environ, **reference_env()), stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+    return True
+
+
 if __name__ == "__main__":
     args = [a for a in sys.argv[1:] if not a.startswith("--")]
-    install(Path(args[0]) if args else Path(os.environ.get("FM_REFERENCE", "/root/reference")))
+    src = Path(args[0]) if args else find_reference()
+    if src is None:
+        raise SystemExit("no checkout of lexionbear/fm found: pass its path or set FM_REFERENCE")
+    install(src)
     if "--prebuild" in sys.argv:
         prebuild()
     print("reference placed in", DEST)

@@ -52,7 +52,7 @@ const TsTune &ts_tune() {
         v.bwd_u = env_int("FMS_TUNE_TSPLIT_BWD_U", 2);
         v.ctas_per_sm = env_int("FMS_TUNE_TSPLIT_CTAS_PER_SM", 2);
         v.l2_hint = env_int("FMS_TUNE_TSPLIT_L2_HINT", 0);
-        v.look = std::max(0, env_int("FMS_TUNE_TSPLIT_LOOK", 0));
+        v.look = env_int("FMS_TUNE_TSPLIT_LOOK", -1);  // -1: chosen from the number of ranks
         return v;
     }();
     return t;
@@ -94,7 +94,9 @@ int make_exchange(fms::TsExchange &ex, void *const *peer_buffers, int64_t rows, 
     ex.epoch = exchange;
     ex.max_wait_cycles = wait_cycles(max_wait_seconds);
     ex.l2_hint = ts_tune().l2_hint;
-    ex.look = ts_tune().look;
+    // Look-ahead of one super-tile pays once the exchange latency of several ranks stacks up
+    // (configuration 4, fwd+bwd: 8 GPUs 0.842 -> 0.833 ms; 2 GPUs with the same block 0.754 -> 0.773 ms).
+    ex.look = ts_tune().look >= 0 ? ts_tune().look : (world >= 4 ? 1 : 0);
     return FMS_OK;
 }
 

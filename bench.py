@@ -407,7 +407,9 @@ def measure_time_split(args, world, rank, device, barrier, max_over_ranks):
         if args.exchange in ("fused", "peer"):
             try:
                 from fm_b200.peer_exchange import FusedTimeSplit, PeerCarryExchange
-                if args.exchange == "fused":
+                # fused where a row's operands stay in L2 between its two passes (8 ranks: 128 KB rows),
+                # three launches with peer stores where they cannot (2 and 4 ranks: 512 KB and 256 KB rows)
+                if args.exchange == "fused" and FusedTimeSplit.pays(a):
                     exchange = FusedTimeSplit(B * D)
                     transport = ("one kernel per direction: carry pass, peer stores + bounded local polls, scan "
                                  "pass fused row by row (second pass re-reads the row from L2)")

@@ -177,7 +177,7 @@ struct Split {
 // Warps per unit.  A CTA of K warps per row reads K*U*512 contiguous bytes per tensor per step
 // and lets the block scheduler balance at a finer grain (all rows have the same length, so whole
 // waves finish together); each row then takes fewer loop iterations to prefetch across.
-int choose_coop(int64_t units, int64_t T, size_t es, int forced) {
+int choose_coop(int64_t units, int64_t T, size_t es, int forced, bool finer_for_small_launches = true) {
     if (forced == 1 || forced == 2 || forced == 4 || forced == 8) return forced;
     // Measured on B200 (CUDA events, fwd+bwd GB/s): 16 KB rows x 32768 rows: K=2 6306, K=4 6182,
     // K=1 5797; 16 KB rows x 8192 rows: K=4 6026, K=2 5761; 128 KB rows x 4096 rows: K=8 6284,
@@ -185,7 +185,10 @@ int choose_coop(int64_t units, int64_t T, size_t es, int forced) {
     // K=1 6217.  Rows shorter than 16 tiles keep one warp each.
     const int64_t tiles = (T * static_cast<int64_t>(es) + 511) / 512;
     int k = tiles >= 128 ? 8 : tiles >= 64 ? 4 : tiles >= 16 ? 2 : 1;
-    if (tiles >= 32 && k < 8 && units <= 8192) k *= 2;  // small launches: finer-grained CTAs shorten the tail
+    // small launches: finer-grained CTAs shorten the tail.  With the balanced persistent grid this
+    // still pays forward (4096 / 8192 rows of 16 KB: 33.0 / 63.4 us with K=4, 33.0 / 66.0 with K=2)
+    // but not backward (59.5 / 111.1 us with K=4 against 57.0 / 108.1 with K=2)
+    if (finer_for_small_launches && tiles >= 32 && k < 8 && units <= 8192) k *= 2;
     return k;
 }
 
@@ -261,7 +264,7 @@ int launch_backward(const Problem &pb, const Split &sp, const void *gates, const
                     const void *grad_states, const float *h0, const float *carry_in, void *grad_gates,
                     void *grad_tokens, float *grad_h0, float *P, cudaStream_t st) {
     const int64_t units = pb.rows * sp.nseg;
-    int K = sp.nseg > 1 ? 1 : choose_coop(units, pb.T, sizeof(S), tune().bwd_k);
+    int K = sp.nseg > 1 ? 1 : choose_coop(units, pb.T, sizeof(S), tune().bwd_k, false);
     // masked path (same measurement): two warps per row are fastest backward when rows are plentiful
     if (!pb.aligned && tune().bwd_k == 0 && units >= 1024) K = std::min(K, 2);
     // one warp per row: 2 tiles per step (4 costs occupancy: 141+ registers for three inputs)
@@ -1033,7 +1036,9 @@ FMS_EXPORT int fms_btd_backward(const void *gates, const void *states, const voi
 // ------------------------------------------------------------------ split inside one GPU ----
 namespace {
 
-constexpr int64_t kSplitTargetUnits = 148 * 32;  // enough one-warp units to fill the GPU
+constexpr int64_t kSplitTargetUnits = 148 * 32;  // one-warp units that fill a B200 (148 SMs x 32 warps); a
+                                                 // constant so that plans and workspace sizes do not
+                                                 // depend on which device happens to be current
 constexpr int64_t kSplitMinLength = 8192;        // rows shorter than this are never split
 constexpr int64_t kSplitMinSegment = 2048;       // positions; shorter segments only add carries
 constexpr int64_t kSplitQuantum = 1024;          // segment lengths are multiples of this, so

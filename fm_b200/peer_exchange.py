@@ -104,6 +104,20 @@ class FusedTimeSplit:
         T = gates.shape[-1]
         return gates.is_cuda and T >= 1 and (T * gates.element_size()) % 16 == 0 and gates.data_ptr() % 16 == 0
 
+    @staticmethod
+    def pays(gates: torch.Tensor) -> bool:
+        """Whether the fused kernels are expected to beat the three-launch path for this block.
+
+        Their advantage is that a row's second pass re-reads the row from L2, which holds while the
+        rows in flight (one per SM) fit: 148 rows x 2 operands x T_k x element size well inside the
+        126 MB L2.  Measured on B200 with fp32 rows: T_k = 32768 (38 MB in flight) 0.72 ms fused
+        against 1.01 ms; T_k = 131072 (155 MB) slower than three launches.  The bound used is 48 MB.
+        """
+        if not FusedTimeSplit.applies(gates):
+            return False
+        sms = torch.cuda.get_device_properties(gates.device).multi_processor_count
+        return sms * 2 * gates.shape[-1] * gates.element_size() <= 48 * (1 << 20)
+
     def _stream(self):
         return torch.cuda.current_stream(self.device).cuda_stream
 

@@ -203,7 +203,7 @@ def _cuda_events(n):
     return [torch.cuda.Event(enable_timing=True) for _ in range(n)]
 
 
-def time_rows_workload(rows, T, seed, device, steps, warmup, barrier):
+def time_rows_workload(rows, T, seed, device, steps, warmup, barrier, use_graph=True):
     """Device-timed fwd+bwd over `rows` x T bf16 on this rank.
 
     Returns (ms_per_step, fwd_ms, bwd_ms, tensors).  The headline loop holds nothing but the two
@@ -226,11 +226,33 @@ def time_rows_workload(rows, T, seed, device, steps, warmup, barrier):
     for _ in range(max(3, warmup)):
         step()
     barrier()
+    # The two launches of a step are captured once into a CUDA graph and replayed: at 30-60 us per
+    # kernel (8 GPUs) the launch path is worth a few per cent.  Nothing is allocated inside step().
+    # If capture is not possible the same launches are issued one by one.
+    launch, how = step, "eager launches"
+    if use_graph:
+        try:
+            graph = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step()
+                with torch.cuda.graph(graph, stream=side, capture_error_mode="thread_local"):
+                    step()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            for _ in range(3):
+                graph.replay()
+            launch, how = graph.replay, "one CUDA graph of the two launches, replayed per step"
+        except Exception as e:  # keep measuring with plain launches
+            torch.cuda.synchronize()
+            how = "eager launches (graph capture failed: %s)" % type(e).__name__
+    barrier()
     start, end = _cuda_events(2)
     barrier()
     start.record()
     for _ in range(steps):
-        step()
+        launch()
     end.record()
     barrier()
     ms_per_step = start.elapsed_time(end) / steps
@@ -246,7 +268,7 @@ def time_rows_workload(rows, T, seed, device, steps, warmup, barrier):
     torch.cuda.synchronize()
     fwd_ms = statistics.median(e[0].elapsed_time(e[1]) for e in ev)
     bwd_ms = statistics.median(e[1].elapsed_time(e[2]) for e in ev)
-    return ms_per_step, fwd_ms, bwd_ms, (a3, x3, G3)
+    return ms_per_step, fwd_ms, bwd_ms, (a3, x3, G3), how
 
 
 def run_ours(args):
@@ -287,8 +309,8 @@ def run_ours(args):
         return [float(v) for v in t.tolist()]
 
     with ClockSampler(physical_gpu_index(local_rank)) as clocks:
-        ms_per_step, fwd_ms, bwd_ms, tensors = time_rows_workload(rows, T, 1003 + rank, device, K,
-                                                                  args.warmup, barrier)
+        ms_per_step, fwd_ms, bwd_ms, tensors, launch_how = time_rows_workload(
+            rows, T, 1003 + rank, device, K, args.warmup, barrier, use_graph=not args.no_graph)
 
     # end to end through host buffers
     if args.no_e2e:
@@ -304,7 +326,8 @@ def run_ours(args):
     other = None
     if world > 1 and not args.no_extras:
         o_rows = total_rows if scaling == "strong" else total_rows // world
-        o_ms, _, _, o_t = time_rows_workload(o_rows, T, 1003 + rank, device, max(5, min(K, 50)), 3, barrier)
+        o_ms, _, _, o_t, _ = time_rows_workload(o_rows, T, 1003 + rank, device, max(5, min(K, 50)), 3, barrier,
+                                                use_graph=not args.no_graph)
         del o_t
         (o_ms,) = max_over_ranks([o_ms])
         other = {"rows_per_gpu": o_rows, "ms_per_step": o_ms, "value": o_rows * world * T / (o_ms * 1e-3),
@@ -334,7 +357,7 @@ def run_ours(args):
                              (n_local * s >> 20),
                        "sharding": ("the fixed %d rows split over the ranks" % total_rows if scaling == "strong"
                                     else "%d rows on every rank" % total_rows) + ", no collective"},
-            "gpu_launches": 2 * K,
+            "gpu_launches": 2 * K, "launch_path": launch_how,
             "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
             "fwd_elements_per_s": global_rows * T / (fwd_ms * 1e-3),
             "roofline": {"bound": "hbm", "kernel": "plain_backward_kernel", "achieved": bwd_gbs,
@@ -841,7 +864,7 @@ def run_fm_mode(args):
             "roofline_forward": {"algorithmic_bytes_per_launch": 2 * n + 2 * (M + D) * B * L,
                                  "achieved": (2 * n + 2 * (M + D) * B * L) / (fwd_ms * 1e-3) / 1e9,
                                  "peak": peak, "peak_kind": kind, "unit": "GB/s"},
-            "roofline": {"bound": "hbm", "kernel": "fm_backward_blocked_kernel",
+            "roofline": {"bound": "hbm", "kernel": "fm_backward_ring_kernel",
                          "algorithmic_bytes_per_launch": 4 * n + 4 * (M + D) * B * L,
                          "achieved": (4 * n + 4 * (M + D) * B * L) / (bwd_ms * 1e-3) / 1e9,
                          "peak": peak, "peak_kind": kind, "unit": "GB/s"},
@@ -956,6 +979,7 @@ def main():
                          "btd: the plain scan on channel-last (B,T,D) tensors")
     ap.add_argument("--exchange", choices=["nccl", "peer", "fused"], default="fused",
                     help="carry transport of the long sequence split along T")
+    ap.add_argument("--no-graph", action="store_true", help="issue the timed launches one by one (no CUDA graph)")
     ap.add_argument("--no-extras", action="store_true",
                     help="headline only: skip time_split, the other scaling mode and reference_cuda")
     ap.add_argument("--seq-len", type=int, default=0,

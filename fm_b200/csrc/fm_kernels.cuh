@@ -18,71 +18,98 @@
 //     token row d (plain 128-bit shared accesses, no shared atomics, fixed summation order);
 //   * per step each warp issues ONE vector reduction row for d_gates and the CTA DC rows for
 //     d_tokens: global atomics drop by DC and MC against one-row-per-CTA.
-// Only the big streams h and G (grad of the states) come from HBM; they are prefetched PD rows
-// ahead into registers.
+// Only the big streams h and G (grad of the states) come from HBM; they are kept PD rows ahead as
+// cp.async copies into a per-thread shared-memory ring (fm_backward_ring_kernel).
 #pragma once
 
 #include "scan_kernels.cuh"
 
 namespace fms {
 
+// 16-byte asynchronous copy global -> shared that writes zeros instead when `ok` is false (the
+// source is then not read).  Completion is awaited per thread with cp.async.wait_group.
+__device__ __forceinline__ void fm_cp_async16(void *smem_dst, const void *gmem_src, bool ok) {
+    const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+    const int bytes = ok ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem_src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void fm_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void fm_cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// The backward.  The two big streams (states and their gradient) are kept PD rows ahead as 16-byte
+// cp.async copies into a per-thread shared-memory ring rather than in registers: the copies are
+// issued where the source says, whatever the register allocator would prefer (a register ring of
+// the same depth waited on its loads for 4 of every 9 stall cycles and ran at 0.96 ms where this
+// kernel needs 0.62 ms at (1,32,2048,8192) bf16), and the depth costs no registers.  A thread
+// reads back only what it copied itself, so the ring needs no barrier, only the thread's own wait
+// on its copy groups (one group per row).  The token tiles of the next step travel the same way,
+// straight into the buffer the next step reads.
+//
+// Per row the lane first scans its own E positions from a zero carry (dl), the warp scans the
+// lanes' aggregates, and delta_i = dl_i + q_i * c with q_i = prod_{j>i} a_j shared by the DC rows.
+//
+// The state just before a tile (needed by lane 0 for d_gates at the tile's first position) is not
+// fetched separately: walking backwards, it is the last element of the NEXT tile this warp
+// processes.  Lane 0 therefore leaves that one product out, keeps delta of the first position
+// per row (`pend`), and adds  sum_d pend[d] * h_last[d]  one step later with a single scalar
+// reduction per warp and step.
 template <typename S, int MC, int DC, int PD>
 __global__ void __launch_bounds__(MC * 32, 2)
-fm_backward_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
-                           const S *__restrict__ states, const S *__restrict__ grad_states,
-                           const float *__restrict__ h0, float *__restrict__ acc_gates,
-                           float *__restrict__ acc_tokens, float *__restrict__ grad_h0, int64_t M,
-                           int64_t D, int64_t L, int64_t m_blocks, int64_t d_blocks) {
-    static_assert(DC % PD == 0 && PD <= DC, "DC must be a multiple of the prefetch distance");
+fm_backward_ring_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
+                        const S *__restrict__ states, const S *__restrict__ grad_states,
+                        const float *__restrict__ h0, float *__restrict__ acc_gates,
+                        float *__restrict__ acc_tokens, float *__restrict__ grad_h0, int64_t M, int64_t D,
+                        int64_t L, int64_t m_blocks, int64_t d_blocks) {
+    static_assert(PD >= 1 && PD < DC, "the token tiles of the next step must land within the step");
     constexpr int E = Store<S>::E;
     constexpr int W = 32 * E;  // positions per tile
-    // dynamic shared memory (more than the 48 KB static limit): token tiles, then the partial tiles
+    constexpr int NT = MC * 32;
     extern __shared__ __align__(16) unsigned char fm_smem[];
     uint4(*xs)[DC][32] = reinterpret_cast<uint4(*)[DC][32]>(fm_smem);  // [2][DC][32] token tiles, raw
-    // every warp's (1-g)*delta tile of every token row; summed over warps after the step.
-    // [warp][row][E/4][lane] float4: a lane's two vectors sit in different halves, so both the
-    // stores and the loads are conflict-free 128-bit accesses
     float4(*part)[DC][E / 4][32] =
         reinterpret_cast<float4(*)[DC][E / 4][32]>(fm_smem + sizeof(uint4) * 2 * DC * 32);  // [MC][DC][E/4][32]
+    // [PD][2][NT]: slot, {gradient, state}, thread
+    uint4 *ring = reinterpret_cast<uint4 *>(fm_smem + sizeof(uint4) * 2 * DC * 32 +
+                                            sizeof(float4) * MC * DC * (E / 4) * 32) + threadIdx.x;
     const int lane = threadIdx.x & 31;
     const int w = threadIdx.x >> 5;
 
-    // block -> (b, m block, d block); d blocks vary fastest so neighbours share the gate rows in L2
     const int64_t blk = blockIdx.x;
-    const int64_t db = blk % d_blocks, mb = (blk / d_blocks) % m_blocks, b = blk / (d_blocks * m_blocks);
+    // m blocks vary fastest: the CTAs that add into the same d_tokens rows (and read the same token
+    // tiles) run at the same time, so those reductions meet their lines in L2
+    const int64_t mb = blk % m_blocks, db = (blk / m_blocks) % d_blocks, b = blk / (d_blocks * m_blocks);
     const int64_t m = mb * MC + w, d0 = db * DC;
     const bool have_m = m < M;
     const int64_t ntiles = (L + W - 1) / W;
 
     const S *grow = gates + (b * M + (have_m ? m : 0)) * L;
     const int64_t row0 = ((b * M + (have_m ? m : 0)) * D + d0);  // first output row of this warp
-    float carry[DC], dh_before[DC];
+    float carry[DC], pend[DC];
 #pragma unroll
-    for (int d = 0; d < DC; ++d) {
-        carry[d] = 0.f;
-        dh_before[d] = (h0 && have_m && d0 + d < D) ? h0[row0 + d] : 0.f;
-    }
-    // register ring of the big streams: slot = d % PD
-    uint4 rG[PD], rH[PD];
-    float rhalo[PD];
+    for (int d = 0; d < DC; ++d) carry[d] = pend[d] = 0.f;
+
     auto fetch = [&](int slot, int64_t tile, int d) {
         const int64_t t = tile * W + lane * E;
         const bool ok = have_m && tile >= 0 && d0 + d < D && t < L;
-        const int64_t base = (row0 + d) * L;
-        rG[slot] = ok ? ldg_stream(grad_states + base + t) : make_uint4(0u, 0u, 0u, 0u);
-        rH[slot] = ok ? ldg_stream(states + base + t) : make_uint4(0u, 0u, 0u, 0u);
-        rhalo[slot] = (ok && lane == 0 && t > 0) ? Store<S>::to_float(states[base + t - 1]) : 0.f;
+        const int64_t off = ok ? (row0 + d) * L + t : 0;
+        fm_cp_async16(ring + (slot * 2) * NT, grad_states + off, ok);
+        fm_cp_async16(ring + (slot * 2 + 1) * NT, states + off, ok);
+        fm_cp_async_commit();
     };
-#pragma unroll
-    for (int p = 0; p < PD; ++p) fetch(p, ntiles - 1, p);
-
-    // Token tiles and the gate tile of a step are fetched one step ahead into registers; the token
-    // tiles then go to the shared buffer the NEXT step reads (two buffers, so a step needs only
-    // two barriers).
-    auto load_x = [&](int64_t tile, int d) -> uint4 {
+    constexpr int XPW = (DC + MC - 1) / MC;  // token rows staged per warp
+    auto stage_x = [&](unsigned buf, int64_t tile) {
         const int64_t tt = tile * W + lane * E;
-        return (tile >= 0 && tt < L && d < DC && d0 + d < D) ? ldg_stream(tokens + (b * D + d0 + d) * L + tt)
-                                                   : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int k = 0; k < XPW; ++k) {
+            const int r = w + k * MC;
+            if (r < DC) {
+                const bool ok = tile >= 0 && tt < L && d0 + r < D;
+                fm_cp_async16(&xs[buf][r][lane], tokens + (ok ? (b * D + d0 + r) * L + tt : 0), ok);
+            }
+        }
     };
     auto load_g = [&](int64_t tile) -> uint4 {
         const int64_t tt = tile * W + lane * E;
@@ -90,26 +117,31 @@ fm_backward_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ to
                    ? ldg_stream(grow + tt)
                    : make_uint4(Store<S>::kOne, Store<S>::kOne, Store<S>::kOne, Store<S>::kOne);
     };
-    constexpr int XPW = (DC + MC - 1) / MC;  // token rows staged per warp
-    uint4 gq = load_g(ntiles - 1), xq[XPW];
+    stage_x(0, ntiles - 1);
+    fm_cp_async_commit();
 #pragma unroll
-    for (int k = 0; k < XPW; ++k)
-        if (w + k * MC < DC) xs[0][w + k * MC][lane] = load_x(ntiles - 1, w + k * MC);
+    for (int p = 0; p < PD; ++p) fetch(p, ntiles - 1, p);
+    uint4 gq = load_g(ntiles - 1);
+    fm_cp_async_wait<PD>();  // the first token tiles have landed (made visible by the barrier below)
 
     unsigned step = 0;
+    int run = 0;  // ring position when PD does not divide DC (otherwise static per row)
     for (int64_t tile = ntiles - 1; tile >= 0; --tile, ++step) {
         const int64_t t = tile * W + lane * E;  // this lane's first position
         const bool in = t < L;
         const unsigned buf = step & 1u;
         __syncthreads();  // previous step's flush is complete and xs[buf] is staged
-        float fa[E], om[E];
+        float fa[E];
         Store<S>::unpack(gq, fa);
         gq = load_g(tile - 1);
+        stage_x(buf ^ 1u, tile - 1);  // rides in the copy group of the first row below
+        // Per-lane factors shared by the DC rows: Q_i = prod_{j>i} a_j carries a later lane's
+        // contribution down to element i, A = prod_j a_j is the lane's gate aggregate.
+        float q[E], om[E];
+        q[E - 1] = 1.f;
 #pragma unroll
-        for (int k = 0; k < XPW; ++k) xq[k] = load_x(tile - 1, w + k * MC);
-        float A = fa[E - 1];
-#pragma unroll
-        for (int i = E - 2; i >= 0; --i) A *= fa[i];
+        for (int i = E - 2; i >= 0; --i) q[i] = q[i + 1] * fa[i + 1];
+        float A = q[0] * fa[0];
 #pragma unroll
         for (int i = 0; i < E; ++i) om[i] = 1.f - fa[i];
         float Alvl[5];
@@ -125,22 +157,27 @@ fm_backward_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ to
         float dg[E];
 #pragma unroll
         for (int i = 0; i < E; ++i) dg[i] = 0.f;
+        float defer = 0.f;
 
 #pragma unroll
         for (int d = 0; d < DC; ++d) {
-            const int slot = d % PD;
+            const int slot = (DC % PD == 0) ? d % PD : run;
+            if (DC % PD != 0) run = (run + 1 == PD) ? 0 : run + 1;
             float fg[E], fh[E], fx[E];
-            Store<S>::unpack(rG[slot], fg);
-            Store<S>::unpack(rH[slot], fh);
-            const float halo = rhalo[slot];
+            fm_cp_async_wait<PD - 1>();  // this row's copies (the oldest group) have landed
+            Store<S>::unpack(ring[(slot * 2) * NT], fg);
+            Store<S>::unpack(ring[(slot * 2 + 1) * NT], fh);
             // refill the slot: PD rows ahead, wrapping into the next (earlier) tile
             if (d + PD < DC) fetch(slot, tile, d + PD);
             else fetch(slot, tile - 1, d + PD - DC);
             Store<S>::unpack(xs[buf][d][lane], fx);
 
-            float C = fa[E - 1] * fg[E - 1];
+            // the lane's own reverse scan from a zero carry: dl_i = G_i + a_{i+1} * dl_{i+1}
+            float dl[E];
+            dl[E - 1] = fg[E - 1];
 #pragma unroll
-            for (int i = E - 2; i >= 0; --i) C = fa[i] * (fg[i] + C);
+            for (int i = E - 2; i >= 0; --i) dl[i] = fmaf(fa[i + 1], dl[i + 1], fg[i]);
+            float C = fa[0] * dl[0];
 #pragma unroll
             for (int k = 0; k < 5; ++k) {
                 const float pC = __shfl_down_sync(kFullMask, C, 1 << k);
@@ -149,51 +186,65 @@ fm_backward_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ to
             float eC = __shfl_down_sync(kFullMask, C, 1);
             if (lane == 31) eC = 0.f;
             const float tC = __shfl_sync(kFullMask, C, 0);
-            float hprev0 = __shfl_up_sync(kFullMask, fh[E - 1], 1);
-            if (lane == 0) hprev0 = (t > 0) ? halo : dh_before[d];
-            float c = fmaf(eA, carry[d], eC);
+            // the state before this lane's vector: lane 0 receives lane 31's last state, which is
+            // the one in front of the tile processed one step ago
+            float hprev0 = __shfl_sync(kFullMask, fh[E - 1], (lane + 31) & 31);
+            if (lane == 0) {
+                defer = fmaf(pend[d], hprev0, defer);
+                hprev0 = (tile == 0 && h0 && have_m && d0 + d < D) ? h0[row0 + d] : 0.f;
+            }
+            const float c = fmaf(eA, carry[d], eC);  // a_{t+1} * delta_{t+1} just behind this lane
             carry[d] = fmaf(tA, carry[d], tC);
             float dxv[E];  // zero for masked rows and lanes (G = 0, carry = 0 there)
 #pragma unroll
-            for (int i = E - 1; i >= 0; --i) {
-                const float delta = fg[i] + c;
-                c = fa[i] * delta;
+            for (int i = 0; i < E; ++i) {
+                const float delta = fmaf(q[i], c, dl[i]);
                 const float hp = (i > 0) ? fh[i > 0 ? i - 1 : 0] : hprev0;
                 dg[i] = fmaf(delta, hp - fx[i], dg[i]);
                 dxv[i] = om[i] * delta;
+                if (i == 0) pend[d] = delta;
             }
 #pragma unroll
             for (int k = 0; k < E / 4; ++k)
                 part[w][d][k][lane] = make_float4(dxv[4 * k], dxv[4 * k + 1], dxv[4 * k + 2], dxv[4 * k + 3]);
         }
         if (in && have_m) red_vec<E, false>(acc_gates + (b * M + m) * L, t, L, dg);
-#pragma unroll
-        for (int k = 0; k < XPW; ++k)
-            if (w + k * MC < DC) xs[buf ^ 1u][w + k * MC][lane] = xq[k];
-        __syncthreads();  // every warp has published its tiles (and staged the next token tiles)
+        if (lane == 0 && have_m && tile + 1 < ntiles) atomicAdd(acc_gates + (b * M + m) * L + (tile + 1) * W, defer);
+        __syncthreads();  // every warp has published its tiles; the next token tiles have landed
 #pragma unroll
         for (int d = w; d < DC; d += MC) {
-            float v[E];
+            float2 v2[E / 2];  // pairs of neighbouring positions: add.f32x2, one issue slot for two sums
 #pragma unroll
-            for (int i = 0; i < E; ++i) v[i] = 0.f;
+            for (int k = 0; k < E / 2; ++k) v2[k] = make_float2(0.f, 0.f);
 #pragma unroll
             for (int ww = 0; ww < MC; ++ww)
 #pragma unroll
                 for (int k = 0; k < E / 4; ++k) {
                     const float4 p = part[ww][d][k][lane];
-                    v[4 * k] += p.x;
-                    v[4 * k + 1] += p.y;
-                    v[4 * k + 2] += p.z;
-                    v[4 * k + 3] += p.w;
+                    v2[2 * k] = __fadd2_rn(v2[2 * k], make_float2(p.x, p.y));
+                    v2[2 * k + 1] = __fadd2_rn(v2[2 * k + 1], make_float2(p.z, p.w));
                 }
+            float v[E];
+#pragma unroll
+            for (int k = 0; k < E / 2; ++k) {
+                v[2 * k] = v2[k].x;
+                v[2 * k + 1] = v2[k].y;
+            }
             if (in && d0 + d < D) red_vec<E, false>(acc_tokens + (b * D + d0 + d) * L, t, L, v);
         }
     }
+    fm_cp_async_wait<0>();
     if (grad_h0 && have_m && lane == 0) {
 #pragma unroll
         for (int d = 0; d < DC; ++d)
             if (d0 + d < D) grad_h0[row0 + d] = carry[d];
     }
+}
+
+template <typename S, int MC, int DC, int PD>
+constexpr size_t fm_backward_ring_smem() {
+    return sizeof(uint4) * 2 * DC * 32 + sizeof(float4) * MC * DC * (Store<S>::E / 4) * 32 +
+           sizeof(uint4) * PD * 2 * MC * 32;
 }
 
 // FM-mode forward with the same blocking: warp w owns gate row m0+w and produces the DC state
@@ -501,7 +552,7 @@ __global__ void fm_readout_scale_kernel(float *__restrict__ sumsq_to_scale, cons
     }
 }
 
-// Dynamic shared memory fm_backward_blocked_kernel and fm_readout_blocked_kernel need.
+// Dynamic shared memory fm_readout_blocked_kernel needs (token tiles and the per-warp partial tiles).
 template <typename S, int MC, int DC>
 constexpr size_t fm_backward_blocked_smem() {
     return sizeof(uint4) * 2 * DC * 32 + sizeof(float4) * MC * DC * (Store<S>::E / 4) * 32;
@@ -587,61 +638,67 @@ __global__ void fm_layer_factors_kernel(const float *__restrict__ rnorm, const S
     }
 }
 
-// Pass 2: fm_backward_blocked_kernel with the gradient of the raw states GENERATED per tile
+// Pass 2: fm_backward_ring_kernel with the gradient of the raw states GENERATED per tile
 //   G = p1 * dout - hn * p2 (+ r * ext)     and the raw states recovered as h = hn * rinv,
 // so the only (B,M,D,L) stream read is hn (and ext when the caller used the returned states).
 template <typename S, int MC, int DC, int PD, bool EXT>
 __global__ void __launch_bounds__(MC * 32, 2)
-fm_layer_backward_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
-                                 const S *__restrict__ hn, const S *__restrict__ dout,
-                                 const S *__restrict__ ext, const float *__restrict__ p1,
-                                 const float *__restrict__ p2, const float *__restrict__ rinv,
-                                 const float *__restrict__ rnorm, const float *__restrict__ h0,
-                                 float *__restrict__ acc_gates, float *__restrict__ acc_tokens,
-                                 float *__restrict__ grad_h0, int64_t M, int64_t D, int64_t L,
-                                 int64_t m_blocks, int64_t d_blocks) {
-    static_assert(DC % PD == 0 && PD <= DC, "DC must be a multiple of the prefetch distance");
+fm_layer_backward_ring_kernel(const S *__restrict__ gates, const S *__restrict__ tokens,
+                              const S *__restrict__ hn, const S *__restrict__ dout,
+                              const S *__restrict__ ext, const float *__restrict__ p1,
+                              const float *__restrict__ p2, const float *__restrict__ rinv,
+                              const float *__restrict__ rnorm, const float *__restrict__ h0,
+                              float *__restrict__ acc_gates, float *__restrict__ acc_tokens,
+                              float *__restrict__ grad_h0, int64_t M, int64_t D, int64_t L,
+                              int64_t m_blocks, int64_t d_blocks) {
+    static_assert(PD >= 1 && PD < DC, "the tiles of the next step must land within the step");
     constexpr int E = Store<S>::E;
     constexpr int W = 32 * E;
+    constexpr int NT = MC * 32;
+    constexpr int NS = EXT ? 2 : 1;  // big streams in the ring: hn (and ext)
     extern __shared__ __align__(16) unsigned char fm_smem[];
     uint4(*xs)[DC][32] = reinterpret_cast<uint4(*)[DC][32]>(fm_smem);                        // [2] tokens
     uint4(*ds)[DC][32] = reinterpret_cast<uint4(*)[DC][32]>(fm_smem + sizeof(uint4) * 2 * DC * 32);  // [2] dout
     float4(*part)[DC][E / 4][32] =
         reinterpret_cast<float4(*)[DC][E / 4][32]>(fm_smem + sizeof(uint4) * 4 * DC * 32);
+    // [PD][NS][NT]: slot, {hn, ext}, thread -- read back only by the thread that copied
+    uint4 *ring = reinterpret_cast<uint4 *>(fm_smem + sizeof(uint4) * 4 * DC * 32 +
+                                            sizeof(float4) * MC * DC * (E / 4) * 32) + threadIdx.x;
     const int lane = threadIdx.x & 31;
     const int w = threadIdx.x >> 5;
     const int64_t blk = blockIdx.x;
-    const int64_t db = blk % d_blocks, mb = (blk / d_blocks) % m_blocks, b = blk / (d_blocks * m_blocks);
+    const int64_t mb = blk % m_blocks, db = (blk / m_blocks) % d_blocks, b = blk / (d_blocks * m_blocks);
     const int64_t m = mb * MC + w, d0 = db * DC;
     const bool have_m = m < M;
     const int64_t ntiles = (L + W - 1) / W;
     const int64_t grow_off = (b * M + (have_m ? m : 0)) * L;
     const S *grow = gates + grow_off;
     const int64_t row0 = ((b * M + (have_m ? m : 0)) * D + d0);
-    float carry[DC], dh_before[DC];
+    float carry[DC], pend[DC];
 #pragma unroll
-    for (int d = 0; d < DC; ++d) {
-        carry[d] = 0.f;
-        dh_before[d] = (h0 && have_m && d0 + d < D) ? h0[row0 + d] : 0.f;
-    }
-    uint4 rH[PD], rE[EXT ? PD : 1];
-    float rhalo[PD];
+    for (int d = 0; d < DC; ++d) carry[d] = pend[d] = 0.f;
+
     auto fetch = [&](int slot, int64_t tile, int d) {
         const int64_t t = tile * W + lane * E;
         const bool ok = have_m && tile >= 0 && d0 + d < D && t < L;
-        const int64_t base = (row0 + d) * L;
-        rH[slot] = ok ? ldg_stream(hn + base + t) : make_uint4(0u, 0u, 0u, 0u);
-        if constexpr (EXT) rE[slot] = ok ? ldg_stream(ext + base + t) : make_uint4(0u, 0u, 0u, 0u);
-        // raw state just before the tile: hn[t-1] * rinv[t-1]
-        rhalo[slot] = (ok && lane == 0 && t > 0) ? Store<S>::to_float(hn[base + t - 1]) * rinv[grow_off + t - 1] : 0.f;
+        const int64_t off = ok ? (row0 + d) * L + t : 0;
+        fm_cp_async16(ring + (slot * NS) * NT, hn + off, ok);
+        if constexpr (EXT) fm_cp_async16(ring + (slot * NS + 1) * NT, ext + off, ok);
+        fm_cp_async_commit();
     };
-#pragma unroll
-    for (int p = 0; p < PD; ++p) fetch(p, ntiles - 1, p);
-
-    auto load_row = [&](const S *base_ptr, int64_t tile, int d) -> uint4 {
+    constexpr int XPW = (DC + MC - 1) / MC;
+    auto stage_rows = [&](unsigned buf, int64_t tile) {  // this warp's share of the token and dout tiles
         const int64_t tt = tile * W + lane * E;
-        return (tile >= 0 && tt < L && d < DC && d0 + d < D) ? ldg_stream(base_ptr + (b * D + d0 + d) * L + tt)
-                                                             : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int k = 0; k < XPW; ++k) {
+            const int r = w + k * MC;
+            if (r < DC) {
+                const bool ok = tile >= 0 && tt < L && d0 + r < D;
+                const int64_t off = ok ? (b * D + d0 + r) * L + tt : 0;
+                fm_cp_async16(&xs[buf][r][lane], tokens + off, ok);
+                fm_cp_async16(&ds[buf][r][lane], dout + off, ok);
+            }
+        }
     };
     auto load_g = [&](int64_t tile) -> uint4 {
         const int64_t tt = tile * W + lane * E;
@@ -649,14 +706,12 @@ fm_layer_backward_blocked_kernel(const S *__restrict__ gates, const S *__restric
                    ? ldg_stream(grow + tt)
                    : make_uint4(Store<S>::kOne, Store<S>::kOne, Store<S>::kOne, Store<S>::kOne);
     };
-    constexpr int XPW = (DC + MC - 1) / MC;
-    uint4 gq = load_g(ntiles - 1), xq[XPW], dq[XPW];
+    stage_rows(0, ntiles - 1);
+    fm_cp_async_commit();
 #pragma unroll
-    for (int k = 0; k < XPW; ++k)
-        if (w + k * MC < DC) {
-            xs[0][w + k * MC][lane] = load_row(tokens, ntiles - 1, w + k * MC);
-            ds[0][w + k * MC][lane] = load_row(dout, ntiles - 1, w + k * MC);
-        }
+    for (int p = 0; p < PD; ++p) fetch(p, ntiles - 1, p);
+    uint4 gq = load_g(ntiles - 1);
+    fm_cp_async_wait<PD>();  // the first token / dout tiles have landed
 
     auto load_f32 = [&](const float *src, int64_t t, bool ok, float fill, float (&f)[E]) {
 #pragma unroll
@@ -671,19 +726,16 @@ fm_layer_backward_blocked_kernel(const S *__restrict__ gates, const S *__restric
     };
 
     unsigned step = 0;
+    int run = 0;  // ring position when PD does not divide DC (otherwise static per row)
     for (int64_t tile = ntiles - 1; tile >= 0; --tile, ++step) {
         const int64_t t = tile * W + lane * E;
         const bool in = t < L;
         const unsigned buf = step & 1u;
         __syncthreads();  // previous flush complete; xs[buf], ds[buf] staged
-        float fa[E], om[E], f1[E], f2[E], fri[E];
+        float fa[E], f1[E], f2[E], fri[E];
         Store<S>::unpack(gq, fa);
         gq = load_g(tile - 1);
-#pragma unroll
-        for (int k = 0; k < XPW; ++k) {
-            xq[k] = load_row(tokens, tile - 1, w + k * MC);
-            dq[k] = load_row(dout, tile - 1, w + k * MC);
-        }
+        stage_rows(buf ^ 1u, tile - 1);  // rides in the copy group of the first row below
         load_f32(p1, t, in && have_m, 0.f, f1);
         load_f32(p2, t, in && have_m, 0.f, f2);
         load_f32(rinv, t, in && have_m, 1.f, fri);
@@ -695,9 +747,11 @@ fm_layer_backward_blocked_kernel(const S *__restrict__ gates, const S *__restric
                 for (int i = 0; i < E; ++i) frn[i] = 1.f;
             }
         }
-        float A = fa[E - 1];
+        float q[E], om[E];  // q_i = prod_{j>i} a_j
+        q[E - 1] = 1.f;
 #pragma unroll
-        for (int i = E - 2; i >= 0; --i) A *= fa[i];
+        for (int i = E - 2; i >= 0; --i) q[i] = q[i + 1] * fa[i + 1];
+        float A = q[0] * fa[0];
 #pragma unroll
         for (int i = 0; i < E; ++i) om[i] = 1.f - fa[i];
         float Alvl[5];
@@ -713,15 +767,17 @@ fm_layer_backward_blocked_kernel(const S *__restrict__ gates, const S *__restric
         float dg[E];
 #pragma unroll
         for (int i = 0; i < E; ++i) dg[i] = 0.f;
+        float defer = 0.f;
 
 #pragma unroll
         for (int d = 0; d < DC; ++d) {
-            const int slot = d % PD;
+            const int slot = (DC % PD == 0) ? d % PD : run;
+            if (DC % PD != 0) run = (run + 1 == PD) ? 0 : run + 1;
             float fg[E], fh[E], fx[E], fd[E];
-            Store<S>::unpack(rH[slot], fh);  // normalised states
             float fe[EXT ? E : 1];
-            if constexpr (EXT) Store<S>::unpack(rE[slot], fe);
-            const float halo = rhalo[slot];
+            fm_cp_async_wait<PD - 1>();  // this row's copies (the oldest group) have landed
+            Store<S>::unpack(ring[(slot * NS) * NT], fh);  // normalised states
+            if constexpr (EXT) Store<S>::unpack(ring[(slot * NS + 1) * NT], fe);
             if (d + PD < DC) fetch(slot, tile, d + PD);
             else fetch(slot, tile - 1, d + PD - DC);
             Store<S>::unpack(xs[buf][d][lane], fx);
@@ -733,9 +789,12 @@ fm_layer_backward_blocked_kernel(const S *__restrict__ gates, const S *__restric
                 fg[i] = gi;
                 fh[i] *= fri[i];  // raw state
             }
-            float C = fa[E - 1] * fg[E - 1];
+            // the lane's own reverse scan from a zero carry: dl_i = G_i + a_{i+1} * dl_{i+1}
+            float dl[E];
+            dl[E - 1] = fg[E - 1];
 #pragma unroll
-            for (int i = E - 2; i >= 0; --i) C = fa[i] * (fg[i] + C);
+            for (int i = E - 2; i >= 0; --i) dl[i] = fmaf(fa[i + 1], dl[i + 1], fg[i]);
+            float C = fa[0] * dl[0];
 #pragma unroll
             for (int k = 0; k < 5; ++k) {
                 const float pC = __shfl_down_sync(kFullMask, C, 1 << k);
@@ -744,49 +803,54 @@ fm_layer_backward_blocked_kernel(const S *__restrict__ gates, const S *__restric
             float eC = __shfl_down_sync(kFullMask, C, 1);
             if (lane == 31) eC = 0.f;
             const float tC = __shfl_sync(kFullMask, C, 0);
-            float hprev0 = __shfl_up_sync(kFullMask, fh[E - 1], 1);
-            if (lane == 0) hprev0 = (t > 0) ? halo : dh_before[d];
-            float c = fmaf(eA, carry[d], eC);
+            // raw state before this lane's vector; lane 0 gets lane 31's last one, which belongs
+            // in front of the tile processed one step ago (see fm_backward_ring_kernel)
+            float hprev0 = __shfl_sync(kFullMask, fh[E - 1], (lane + 31) & 31);
+            if (lane == 0) {
+                defer = fmaf(pend[d], hprev0, defer);
+                hprev0 = (tile == 0 && h0 && have_m && d0 + d < D) ? h0[row0 + d] : 0.f;
+            }
+            const float c = fmaf(eA, carry[d], eC);
             carry[d] = fmaf(tA, carry[d], tC);
             float dxv[E];
 #pragma unroll
-            for (int i = E - 1; i >= 0; --i) {
-                const float delta = fg[i] + c;
-                c = fa[i] * delta;
+            for (int i = 0; i < E; ++i) {
+                const float delta = fmaf(q[i], c, dl[i]);
                 const float hp = (i > 0) ? fh[i > 0 ? i - 1 : 0] : hprev0;
                 dg[i] = fmaf(delta, hp - fx[i], dg[i]);
                 dxv[i] = om[i] * delta;
+                if (i == 0) pend[d] = delta;
             }
 #pragma unroll
             for (int k = 0; k < E / 4; ++k)
                 part[w][d][k][lane] = make_float4(dxv[4 * k], dxv[4 * k + 1], dxv[4 * k + 2], dxv[4 * k + 3]);
         }
         if (in && have_m) red_vec<E, false>(acc_gates + grow_off, t, L, dg);
-#pragma unroll
-        for (int k = 0; k < XPW; ++k)
-            if (w + k * MC < DC) {
-                xs[buf ^ 1u][w + k * MC][lane] = xq[k];
-                ds[buf ^ 1u][w + k * MC][lane] = dq[k];
-            }
-        __syncthreads();
+        if (lane == 0 && have_m && tile + 1 < ntiles) atomicAdd(acc_gates + grow_off + (tile + 1) * W, defer);
+        __syncthreads();  // every warp has published its tiles; the next token / dout tiles have landed
 #pragma unroll
         for (int d = w; d < DC; d += MC) {
-            float v[E];
+            float2 v2[E / 2];  // pairs of neighbouring positions: add.f32x2
 #pragma unroll
-            for (int i = 0; i < E; ++i) v[i] = 0.f;
+            for (int k = 0; k < E / 2; ++k) v2[k] = make_float2(0.f, 0.f);
 #pragma unroll
             for (int ww = 0; ww < MC; ++ww)
 #pragma unroll
                 for (int k = 0; k < E / 4; ++k) {
                     const float4 p = part[ww][d][k][lane];
-                    v[4 * k] += p.x;
-                    v[4 * k + 1] += p.y;
-                    v[4 * k + 2] += p.z;
-                    v[4 * k + 3] += p.w;
+                    v2[2 * k] = __fadd2_rn(v2[2 * k], make_float2(p.x, p.y));
+                    v2[2 * k + 1] = __fadd2_rn(v2[2 * k + 1], make_float2(p.z, p.w));
                 }
+            float v[E];
+#pragma unroll
+            for (int k = 0; k < E / 2; ++k) {
+                v[2 * k] = v2[k].x;
+                v[2 * k + 1] = v2[k].y;
+            }
             if (in && d0 + d < D) red_vec<E, false>(acc_tokens + (b * D + d0 + d) * L, t, L, v);
         }
     }
+    fm_cp_async_wait<0>();
     if (grad_h0 && have_m && lane == 0) {
 #pragma unroll
         for (int d = 0; d < DC; ++d)
@@ -794,9 +858,10 @@ fm_layer_backward_blocked_kernel(const S *__restrict__ gates, const S *__restric
     }
 }
 
-template <typename S, int MC, int DC>
+template <typename S, int MC, int DC, int PD, bool EXT>
 constexpr size_t fm_layer_backward_smem() {
-    return sizeof(uint4) * 4 * DC * 32 + sizeof(float4) * MC * DC * (Store<S>::E / 4) * 32;
+    return sizeof(uint4) * 4 * DC * 32 + sizeof(float4) * MC * DC * (Store<S>::E / 4) * 32 +
+           sizeof(uint4) * PD * (EXT ? 2 : 1) * MC * 32;
 }
 
 }  // namespace fms

@@ -49,7 +49,7 @@ struct Tune {
     int fwd_k = 0, bwd_k = 0, fwd_u = 0, bwd_u = 0;  // 0 = choose from the shape
     int max_ctas = 0x7fffffff;                       // test knob: forces the multi-row walk
     int persist = -1;                                // -1 = choose from the shape, 0 = off, 1 = on
-    int fm_pd = 4, fm_blocked = 1, btd_warps_per_sm = 32;
+    int fm_blocked = 1, fm_ring = 3, fm_dc = 0, btd_warps_per_sm = 32;
     int bwd_descending = 1;  // backward visits rows last-to-first (re-reads the forward's latest rows from L2)
     int fwd_keep = 0;        // L2 policy of the forward's state stores: 0 evict-first, 1 normal, 2 evict-last
 };
@@ -69,8 +69,9 @@ void load_tune() {
     t.bwd_u = get("FMS_TUNE_BWD_U", 0);
     t.max_ctas = std::max(1, get("FMS_TUNE_MAX_CTAS", 0x7fffffff));
     t.persist = get("FMS_TUNE_PERSIST", -1);
-    t.fm_pd = get("FMS_TUNE_FM_PD", 4);
     t.fm_blocked = get("FMS_TUNE_FM_BLOCKED", 1);
+    t.fm_ring = get("FMS_TUNE_FM_RING", 3);
+    t.fm_dc = get("FMS_TUNE_FM_DC", 0);
     t.btd_warps_per_sm = std::max(1, get("FMS_TUNE_BTD_WARPS_PER_SM", 32));
     t.bwd_descending = get("FMS_TUNE_BWD_DESCENDING", 1);
     t.fwd_keep = get("FMS_TUNE_FWD_KEEP", 0);
@@ -543,25 +544,38 @@ int launch_fm_forward_blocked(const FmShape &sh, const void *gates, const void *
     return check_launch();
 }
 
-// Blocked backward (fm_kernels.cuh): 8 gate rows x 8 token rows per CTA, aligned tensors only.
+// Blocked backward (fm_kernels.cuh): 8 gate rows (one warp each) x DC token rows per CTA, aligned
+// tensors only.  Every CTA walks the whole sequence, so the launch is a few waves of equal CTAs
+// whose last one may be nearly empty: DC is 8, or 7 when that makes (waves, rounded up) x DC
+// smaller (measured: 3-4 % at (1,32,1024,8192) and (2,16,1000,4096), nothing at (1,32,2048,8192),
+// where the kernel is bound by the memory system and a thin last wave simply runs faster).
 template <typename S>
 int launch_fm_backward_blocked(const FmShape &sh, const void *gates, const void *tokens, const void *states,
                                const void *grad_states, const float *h0, float *acc_gates, float *acc_tokens,
                                float *grad_h0, cudaStream_t st) {
-    // CTA block: 8 gate rows (one warp each) x 8 token rows.  Four token rows per CTA (half the
-    // shared-memory tile buffer, three CTAs per SM at 80 registers) was measured and is no faster:
-    // 0.955-1.21 ms against 0.961 ms at (1,32,2048,8192) bf16 -- the spills it forces and the doubled
-    // gate-row reductions eat the occupancy.
     constexpr int MC = 8;
-    constexpr int dc = 8;
-    const int64_t m_blocks = (sh.M + MC - 1) / MC, d_blocks = (sh.D + dc - 1) / dc;
-    if (sh.B > 0x7fffffffLL / m_blocks || sh.B * m_blocks > 0x7fffffffLL / d_blocks) return FMS_ERR_BAD_SHAPE;
+    const int64_t m_blocks = (sh.M + MC - 1) / MC;
+    const int64_t slots = 2LL * sm_count();  // two CTAs per SM (registers and shared memory)
+    int dc = 8;
+    int64_t best = -1;
+    for (int cand = 8; cand >= 7; --cand) {
+        const int64_t d_blocks = (sh.D + cand - 1) / cand;
+        if (sh.B > 0x7fffffffLL / m_blocks || sh.B * m_blocks > 0x7fffffffLL / d_blocks) return FMS_ERR_BAD_SHAPE;
+        const int64_t ctas = sh.B * m_blocks * d_blocks;
+        const int64_t cost = ((ctas + slots - 1) / slots) * cand;
+        if (best < 0 || cost < best) {
+            best = cost;
+            dc = cand;
+        }
+    }
+    if (tune().fm_dc >= 7 && tune().fm_dc <= 8) dc = tune().fm_dc;
+    const int64_t d_blocks = (sh.D + dc - 1) / dc;
     const unsigned grid = static_cast<unsigned>(sh.B * m_blocks * d_blocks);
     // the shared-memory opt-in is per device, so it is (cheaply) repeated on every launch
-#define FMS_LAUNCH_FM_BLOCKED(DCV, PDV)                                                             \
+#define FMS_LAUNCH_FM_RING(DCV, PDV)                                                                \
     do {                                                                                            \
-        auto kern = fms::fm_backward_blocked_kernel<S, MC, DCV, PDV>;                               \
-        constexpr size_t smem = fms::fm_backward_blocked_smem<S, MC, DCV>();                        \
+        auto kern = fms::fm_backward_ring_kernel<S, MC, DCV, PDV>;                                  \
+        constexpr size_t smem = fms::fm_backward_ring_smem<S, MC, DCV, PDV>();                      \
         const cudaError_t attr = cudaFuncSetAttribute(                                              \
             kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));             \
         if (int rc = record(attr)) return rc;                                                       \
@@ -571,12 +585,14 @@ int launch_fm_backward_blocked(const FmShape &sh, const void *gates, const void 
             acc_tokens, grad_h0, sh.M, sh.D, sh.L, m_blocks, d_blocks);                             \
     } while (0)
 #ifdef FMS_ALL_VARIANTS
-    if (tune().fm_pd == 2) FMS_LAUNCH_FM_BLOCKED(8, 2);
-    else if (tune().fm_pd == 8) FMS_LAUNCH_FM_BLOCKED(8, 8);
+    if (dc == 8 && tune().fm_ring == 2) FMS_LAUNCH_FM_RING(8, 2);
+    else if (dc == 8 && tune().fm_ring == 4) FMS_LAUNCH_FM_RING(8, 4);
+    else if (dc == 8 && tune().fm_ring == 5) FMS_LAUNCH_FM_RING(8, 5);
     else
 #endif
-        FMS_LAUNCH_FM_BLOCKED(8, 4);
-#undef FMS_LAUNCH_FM_BLOCKED
+    if (dc == 8) FMS_LAUNCH_FM_RING(8, 3);
+    else FMS_LAUNCH_FM_RING(7, 3);
+#undef FMS_LAUNCH_FM_RING
     return check_launch();
 }
 
@@ -796,7 +812,6 @@ int launch_fm_layer_backward(const FmShape &sh, const void *gates, const void *t
                              const float *h0, float *ws, void *grad_gates, void *grad_tokens, void *grad_weight,
                              float *grad_h0, cudaStream_t st) {
     constexpr int MC = 8, DC = 8;
-    const int pd = tune().fm_pd;
     const int64_t m_blocks = (sh.M + MC - 1) / MC, d_blocks = (sh.D + DC - 1) / DC;
     if (sh.B > 0x7fffffffLL / m_blocks || sh.B * m_blocks > 0x7fffffffLL / d_blocks) return FMS_ERR_BAD_SHAPE;
     const unsigned grid = static_cast<unsigned>(sh.B * m_blocks * d_blocks);
@@ -817,10 +832,10 @@ int launch_fm_layer_backward(const FmShape &sh, const void *gates, const void *t
     fms::fm_layer_factors_kernel<S><<<static_cast<unsigned>(blocks), 256, 0, st>>>(rnorm, w_, dotc, p1, rinv, n_g,
                                                                                    1.f / static_cast<float>(sh.D));
     if (int rc = check_launch()) return rc;
-    constexpr size_t smem = fms::fm_layer_backward_smem<S, MC, DC>();
 #define FMS_LAUNCH_LAYER_BWD(EXTV, PDV)                                                                 \
     do {                                                                                                \
-        auto kern = fms::fm_layer_backward_blocked_kernel<S, MC, DC, PDV, EXTV>;                        \
+        auto kern = fms::fm_layer_backward_ring_kernel<S, MC, DC, PDV, EXTV>;                           \
+        constexpr size_t smem = fms::fm_layer_backward_smem<S, MC, DC, PDV, EXTV>();                    \
         const cudaError_t attr = cudaFuncSetAttribute(                                                  \
             kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));                 \
         if (int rc = record(attr)) return rc;                                                           \
@@ -828,20 +843,23 @@ int launch_fm_layer_backward(const FmShape &sh, const void *gates, const void *t
                                           ext_, p1, dotc, rinv, rnorm, h0, acc_g, acc_x, grad_h0, sh.M, sh.D,    \
                                           sh.L, m_blocks, d_blocks);                                    \
     } while (0)
-    (void)pd;
+    const int ring = tune().fm_ring;
+    (void)ring;
     if (ext) {
 #ifdef FMS_ALL_VARIANTS
-        if (pd == 2) FMS_LAUNCH_LAYER_BWD(true, 2);
+        if (ring == 2) FMS_LAUNCH_LAYER_BWD(true, 2);
+        else if (ring == 4) FMS_LAUNCH_LAYER_BWD(true, 4);
         else
 #endif
-            FMS_LAUNCH_LAYER_BWD(true, 4);
+            FMS_LAUNCH_LAYER_BWD(true, 3);
     } else {
 #ifdef FMS_ALL_VARIANTS
-        if (pd == 2) FMS_LAUNCH_LAYER_BWD(false, 2);
-        else if (pd == 8) FMS_LAUNCH_LAYER_BWD(false, 8);
+        if (ring == 2) FMS_LAUNCH_LAYER_BWD(false, 2);
+        else if (ring == 4) FMS_LAUNCH_LAYER_BWD(false, 4);
+        else if (ring == 5) FMS_LAUNCH_LAYER_BWD(false, 5);
         else
 #endif
-            FMS_LAUNCH_LAYER_BWD(false, 4);
+            FMS_LAUNCH_LAYER_BWD(false, 3);
     }
 #undef FMS_LAUNCH_LAYER_BWD
     if (int rc = check_launch()) return rc;

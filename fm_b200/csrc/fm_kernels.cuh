@@ -318,32 +318,54 @@ fm_forward_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ tok
         if (lane == 0) eA = 1.f;
         const float tA = __shfl_sync(kFullMask, A, 31);
 
+        // Rows go through the scan two at a time, stage by stage, so that the shuffle chain of one
+        // row covers the latency of the other's.
+        constexpr int R2 = 2;
 #pragma unroll
-        for (int d = 0; d < DC; ++d) {
-            float fx[E];
-            Store<S>::unpack(xs[buf][d][lane], fx);
+        for (int d = 0; d < DC; d += R2) {
+            float fx[R2][E], H[R2];
 #pragma unroll
-            for (int i = 0; i < E; ++i) fx[i] *= om[i];
-            float H = fx[0];
+            for (int r = 0; r < R2; ++r) {
+                if (d + r < DC) Store<S>::unpack(xs[buf][d + r < DC ? d + r : 0][lane], fx[r]);
+            }
 #pragma unroll
-            for (int i = 1; i < E; ++i) H = fmaf(fa[i], H, fx[i]);
+            for (int r = 0; r < R2; ++r) {
+#pragma unroll
+                for (int i = 0; i < E; ++i) fx[r][i] *= om[i];
+                H[r] = fx[r][0];
+#pragma unroll
+                for (int i = 1; i < E; ++i) H[r] = fmaf(fa[i], H[r], fx[r][i]);
+            }
 #pragma unroll
             for (int k = 0; k < 5; ++k) {
-                const float pH = __shfl_up_sync(kFullMask, H, 1 << k);
-                if (lane >= (1 << k)) H = fmaf(Alvl[k], pH, H);
-            }
-            float eH = __shfl_up_sync(kFullMask, H, 1);
-            if (lane == 0) eH = 0.f;
-            const float tH = __shfl_sync(kFullMask, H, 31);
-            float s_ = fmaf(eA, carry[d], eH);
-            carry[d] = fmaf(tA, carry[d], tH);
-            float out[E];
 #pragma unroll
-            for (int i = 0; i < E; ++i) {
-                s_ = fmaf(fa[i], s_, fx[i]);
-                out[i] = s_;
+                for (int r = 0; r < R2; ++r) {
+                    const float pH = __shfl_up_sync(kFullMask, H[r], 1 << k);
+                    if (lane >= (1 << k)) H[r] = fmaf(Alvl[k], pH, H[r]);
+                }
             }
-            if (in && have_m && d0 + d < D) stg_stream(states + (row0 + d) * L + t, Store<S>::pack(out));
+            float eH[R2], tH[R2];
+#pragma unroll
+            for (int r = 0; r < R2; ++r) {
+                eH[r] = __shfl_up_sync(kFullMask, H[r], 1);
+                if (lane == 0) eH[r] = 0.f;
+                tH[r] = __shfl_sync(kFullMask, H[r], 31);
+            }
+#pragma unroll
+            for (int r = 0; r < R2; ++r) {
+                if (d + r < DC) {
+                    const int dd = d + r < DC ? d + r : 0;
+                    float s_ = fmaf(eA, carry[dd], eH[r]);
+                    carry[dd] = fmaf(tA, carry[dd], tH[r]);
+                    float out[E];
+#pragma unroll
+                    for (int i = 0; i < E; ++i) {
+                        s_ = fmaf(fa[i], s_, fx[r][i]);
+                        out[i] = s_;
+                    }
+                    if (in && have_m && d0 + dd < D) stg_stream(states + (row0 + dd) * L + t, Store<S>::pack(out));
+                }
+            }
         }
 #pragma unroll
         for (int k = 0; k < XPW; ++k)

@@ -591,45 +591,86 @@ constexpr size_t fm_backward_blocked_smem() {
 //
 // Pass 1 (this kernel): the two sums over d, accumulated in registers over the CTA's DC token
 // rows and reduced into fp32 (B,M,L) buffers.  No recurrence here: pure streaming of hn.
-template <typename S, int MC, int DC, bool EXT>
-__global__ void __launch_bounds__(MC * 32)
+// hn (and ext) stream through a per-thread cp.async ring PD rows ahead, the dout tiles of the next
+// step go straight into the buffer the next step reads (two buffers, one barrier per step).
+template <typename S, int MC, int DC, int PD, bool EXT>
+__global__ void __launch_bounds__(MC * 32, 3)
 fm_layer_dots_kernel(const S *__restrict__ hn, const S *__restrict__ dout, const S *__restrict__ ext,
                      const S *__restrict__ weight, float *__restrict__ dotc, float *__restrict__ dw,
                      int64_t M, int64_t D, int64_t L, int64_t m_blocks, int64_t d_blocks) {
+    static_assert(PD >= 1 && PD < DC, "the dout tiles of the next step must land within the step");
     constexpr int E = Store<S>::E;
     constexpr int W = 32 * E;
-    __shared__ uint4 ds[DC][32];
+    constexpr int NT = MC * 32;
+    constexpr int NS = EXT ? 2 : 1;
+    extern __shared__ __align__(16) unsigned char fm_smem[];
+    uint4(*ds)[DC][32] = reinterpret_cast<uint4(*)[DC][32]>(fm_smem);  // [2][DC][32] dout tiles
+    uint4 *ring = reinterpret_cast<uint4 *>(fm_smem + sizeof(uint4) * 2 * DC * 32) + threadIdx.x;  // [PD][NS][NT]
     const int lane = threadIdx.x & 31;
     const int w = threadIdx.x >> 5;
     const int64_t blk = blockIdx.x;
-    const int64_t db = blk % d_blocks, mb = (blk / d_blocks) % m_blocks, b = blk / (d_blocks * m_blocks);
+    const int64_t mb = blk % m_blocks, db = (blk / m_blocks) % d_blocks, b = blk / (d_blocks * m_blocks);
     const int64_t m = mb * MC + w, d0 = db * DC;
     const bool have_m = m < M;
     const int64_t ntiles = (L + W - 1) / W;
     const int64_t grow_off = (b * M + (have_m ? m : 0)) * L;
     const int64_t row0 = ((b * M + (have_m ? m : 0)) * D + d0);
+
+    auto fetch = [&](int slot, int64_t tile, int d) {
+        const int64_t t = tile * W + lane * E;
+        const bool ok = have_m && tile < ntiles && d0 + d < D && t < L;
+        const int64_t off = ok ? (row0 + d) * L + t : 0;
+        fm_cp_async16(ring + (slot * NS) * NT, hn + off, ok);
+        if constexpr (EXT) fm_cp_async16(ring + (slot * NS + 1) * NT, ext + off, ok);
+        fm_cp_async_commit();
+    };
+    constexpr int XPW = (DC + MC - 1) / MC;
+    auto stage_d = [&](unsigned buf, int64_t tile) {
+        const int64_t tt = tile * W + lane * E;
+#pragma unroll
+        for (int k = 0; k < XPW; ++k) {
+            const int r = w + k * MC;
+            if (r < DC) {
+                const bool ok = tile < ntiles && tt < L && d0 + r < D;
+                fm_cp_async16(&ds[buf][r][lane], dout + (ok ? (b * D + d0 + r) * L + tt : 0), ok);
+            }
+        }
+    };
+    auto load_w = [&](int64_t tile) -> uint4 {
+        const int64_t tt = tile * W + lane * E;
+        return (tile < ntiles && tt < L && have_m) ? ldg_stream(weight + grow_off + tt) : make_uint4(0u, 0u, 0u, 0u);
+    };
+    stage_d(0, 0);
+    fm_cp_async_commit();
+#pragma unroll
+    for (int p = 0; p < PD; ++p) fetch(p, 0, p);
+    uint4 wq = load_w(0);
+    fm_cp_async_wait<PD>();  // the first dout tiles have landed
+
+    int run = 0;  // ring position when PD does not divide DC (otherwise static per row)
     for (int64_t tile = 0; tile < ntiles; ++tile) {
         const int64_t t = tile * W + lane * E;
         const bool in = t < L;
-        __syncthreads();
-        for (int d = w; d < DC; d += MC)
-            ds[d][lane] = (in && d0 + d < D) ? ldg_stream(dout + (b * D + d0 + d) * L + t) : make_uint4(0u, 0u, 0u, 0u);
+        const unsigned buf = static_cast<unsigned>(tile) & 1u;
+        __syncthreads();  // ds[buf] is staged; ds[buf^1] is no longer read
         float fw[E], a1[E], a2[E];
-        {
-            const uint4 q = (in && have_m) ? ldg_stream(weight + grow_off + t) : make_uint4(0u, 0u, 0u, 0u);
-            Store<S>::unpack(q, fw);
-        }
+        Store<S>::unpack(wq, fw);
+        wq = load_w(tile + 1);
+        stage_d(buf ^ 1u, tile + 1);  // rides in the copy group of the first row below
 #pragma unroll
         for (int i = 0; i < E; ++i) a1[i] = a2[i] = 0.f;
-        __syncthreads();
 #pragma unroll
         for (int d = 0; d < DC; ++d) {
-            const bool ok = in && have_m && d0 + d < D;
-            float fh[E], fd[E], fe[E];
-            Store<S>::unpack(ok ? ldg_stream(hn + (row0 + d) * L + t) : make_uint4(0u, 0u, 0u, 0u), fh);
-            Store<S>::unpack(ds[d][lane], fd);
-            if constexpr (EXT)
-                Store<S>::unpack(ok ? ldg_stream(ext + (row0 + d) * L + t) : make_uint4(0u, 0u, 0u, 0u), fe);
+            const int slot = (DC % PD == 0) ? d % PD : run;
+            if (DC % PD != 0) run = (run + 1 == PD) ? 0 : run + 1;
+            float fh[E], fd[E];
+            float fe[EXT ? E : 1];
+            fm_cp_async_wait<PD - 1>();  // this row's copies (the oldest group) have landed
+            Store<S>::unpack(ring[(slot * NS) * NT], fh);
+            if constexpr (EXT) Store<S>::unpack(ring[(slot * NS + 1) * NT], fe);
+            if (d + PD < DC) fetch(slot, tile, d + PD);
+            else fetch(slot, tile + 1, d + PD - DC);
+            Store<S>::unpack(ds[buf][d][lane], fd);
 #pragma unroll
             for (int i = 0; i < E; ++i) {
                 float ghn = fw[i] * fd[i];
@@ -643,6 +684,12 @@ fm_layer_dots_kernel(const S *__restrict__ hn, const S *__restrict__ dout, const
             red_vec<E, false>(dw + grow_off, t, L, a2);
         }
     }
+    fm_cp_async_wait<0>();
+}
+
+template <typename S, int MC, int DC, int PD, bool EXT>
+constexpr size_t fm_layer_dots_smem() {
+    return sizeof(uint4) * 2 * DC * 32 + sizeof(uint4) * PD * (EXT ? 2 : 1) * MC * 32;
 }
 
 // Small per-(b,m,t) factors for pass 2, in place:  p1 = r*w,  p2 = r*c = r*dotc/D,  rinv = 1/r.

@@ -820,12 +820,19 @@ int launch_fm_layer_backward(const FmShape &sh, const void *gates, const void *t
     if (int rc = record(cudaMemsetAsync(ws, 0, static_cast<size_t>(5 * n_g + n_x) * sizeof(float), st))) return rc;
     const S *hn_ = static_cast<const S *>(hn), *dout_ = static_cast<const S *>(dout), *ext_ = static_cast<const S *>(ext);
     const S *w_ = static_cast<const S *>(weight);
-    if (ext)
-        fms::fm_layer_dots_kernel<S, MC, DC, true><<<grid, MC * 32, 0, st>>>(hn_, dout_, ext_, w_, dotc, dw, sh.M, sh.D,
-                                                                              sh.L, m_blocks, d_blocks);
-    else
-        fms::fm_layer_dots_kernel<S, MC, DC, false><<<grid, MC * 32, 0, st>>>(hn_, dout_, nullptr, w_, dotc, dw, sh.M,
-                                                                               sh.D, sh.L, m_blocks, d_blocks);
+#define FMS_LAUNCH_LAYER_DOTS(EXTV)                                                                     \
+    do {                                                                                                \
+        constexpr int PDD = 6;                                                                          \
+        auto kern = fms::fm_layer_dots_kernel<S, MC, DC, PDD, EXTV>;                                    \
+        constexpr size_t smem = fms::fm_layer_dots_smem<S, MC, DC, PDD, EXTV>();                        \
+        const cudaError_t attr = cudaFuncSetAttribute(                                                  \
+            kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));                 \
+        if (int rc = record(attr)) return rc;                                                           \
+        kern<<<grid, MC * 32, smem, st>>>(hn_, dout_, ext_, w_, dotc, dw, sh.M, sh.D, sh.L, m_blocks, d_blocks); \
+    } while (0)
+    if (ext) FMS_LAUNCH_LAYER_DOTS(true);
+    else FMS_LAUNCH_LAYER_DOTS(false);
+#undef FMS_LAUNCH_LAYER_DOTS
     if (int rc = check_launch()) return rc;
     const int64_t blocks = (n_g + 255) / 256;
     if (blocks > 0x7fffffffLL) return FMS_ERR_BAD_SHAPE;

@@ -63,6 +63,36 @@ def test_fm_against_oracle(monkeypatch, blocked, storage, B, M, D, L):
     H.assert_close(G.host(dh0), dh0_ref, 1e-4, 1e-4 * max(1.0, float(np.abs(dh0_ref).max())), "fm d_h0")
 
 
+@pytest.mark.parametrize("rows_per_cta", [7, 8])
+@pytest.mark.parametrize("storage,B,M,D,L", [("bf16", 2, 9, 17, 520), ("f32", 1, 5, 23, 1028)])
+def test_fm_backward_rows_per_cta(monkeypatch, rows_per_cta, storage, B, M, D, L):
+    """The blocked backward takes 7 or 8 token rows per CTA from the shape; both instantiations
+    against the oracle on shapes with several tiles, a ragged last tile, M and D that are no
+    multiples of the block, and an initial state (FMS_TUNE_FM_DC forces the choice)."""
+    monkeypatch.setenv("FMS_TUNE_FM_DC", str(rows_per_cta))
+    G.reload_tune()
+    rng = np.random.Generator(np.random.PCG64(rows_per_cta * 7 + L))
+    g = H.round_storage((0.5 + 0.5 * rng.random((B, M, L), dtype=np.float32)), storage)
+    x = H.round_storage(rng.standard_normal((B, D, L), dtype=np.float32), storage)
+    Gr = H.round_storage(rng.standard_normal((B, M, D, L), dtype=np.float32), storage)
+    h0 = H.round_storage(rng.standard_normal((B, M, D), dtype=np.float32), storage)
+    gd, xd, Gd, h0d = G.dev(g, storage), G.dev(x, storage), G.dev(Gr, storage), G.dev(h0)
+    h = G.fm_forward(gd, xd, h0d)
+    dg, dx, dh0 = G.fm_backward(gd, xd, h, Gd, h0d, want_gh0=True)
+    torch.cuda.synchronize()
+    f64 = np.float64
+    hs = G.host(h)
+    dg_ref, dx_ref, dh0_ref = oc.fm_backward(g.astype(f64), x.astype(f64), hs.astype(f64), Gr.astype(f64),
+                                             h0.astype(f64), dtype=f64)
+    if storage == "f32":
+        tol = lambda ref: (H.FP32_RTOL, H.FP32_ATOL * max(1.0, float(np.abs(ref).max())))
+    else:
+        tol = lambda ref: (H.LOWP_RTOL, H.lowp_atol(ref))
+    H.assert_close(G.host(dx), dx_ref, *tol(dx_ref), "fm d_tokens")
+    H.assert_close(G.host(dg), dg_ref, *tol(dg_ref), "fm d_gates")
+    H.assert_close(G.host(dh0), dh0_ref, 1e-4, 1e-4 * max(1.0, float(np.abs(dh0_ref).max())), "fm d_h0")
+
+
 def test_fm_mode_through_the_torch_op():
     from fm_b200 import fm_scan
     g = H.load_golden("fm_2x3x5x64_h0")

@@ -137,13 +137,11 @@ fm_backward_ring_kernel(const S *__restrict__ gates, const S *__restrict__ token
         stage_x(buf ^ 1u, tile - 1);  // rides in the copy group of the first row below
         // Per-lane factors shared by the DC rows: Q_i = prod_{j>i} a_j carries a later lane's
         // contribution down to element i, A = prod_j a_j is the lane's gate aggregate.
-        float q[E], om[E];
+        float q[E];
         q[E - 1] = 1.f;
 #pragma unroll
         for (int i = E - 2; i >= 0; --i) q[i] = q[i + 1] * fa[i + 1];
         float A = q[0] * fa[0];
-#pragma unroll
-        for (int i = 0; i < E; ++i) om[i] = 1.f - fa[i];
         float Alvl[5];
 #pragma unroll
         for (int k = 0; k < 5; ++k) {
@@ -201,7 +199,7 @@ fm_backward_ring_kernel(const S *__restrict__ gates, const S *__restrict__ token
                 const float delta = fmaf(q[i], c, dl[i]);
                 const float hp = (i > 0) ? fh[i > 0 ? i - 1 : 0] : hprev0;
                 dg[i] = fmaf(delta, hp - fx[i], dg[i]);
-                dxv[i] = om[i] * delta;
+                dxv[i] = fmaf(-fa[i], delta, delta);  // (1 - a) * delta, one rounding
                 if (i == 0) pend[d] = delta;
             }
 #pragma unroll
@@ -801,13 +799,12 @@ fm_layer_backward_ring_kernel(const S *__restrict__ gates, const S *__restrict__
         const bool in = t < L;
         const unsigned buf = step & 1u;
         __syncthreads();  // previous flush complete; xs[buf], ds[buf] staged
-        float fa[E], f1[E], f2[E], fri[E];
+        float fa[E], f1[E], f2[E];
         Store<S>::unpack(gq, fa);
         gq = load_g(tile - 1);
         stage_rows(buf ^ 1u, tile - 1);  // rides in the copy group of the first row below
         load_f32(p1, t, in && have_m, 0.f, f1);
         load_f32(p2, t, in && have_m, 0.f, f2);
-        load_f32(rinv, t, in && have_m, 1.f, fri);
         float frn[EXT ? E : 1];
         if constexpr (EXT) {
             if (rnorm) load_f32(rnorm, t, in && have_m, 1.f, frn);
@@ -816,13 +813,11 @@ fm_layer_backward_ring_kernel(const S *__restrict__ gates, const S *__restrict__
                 for (int i = 0; i < E; ++i) frn[i] = 1.f;
             }
         }
-        float q[E], om[E];  // q_i = prod_{j>i} a_j
+        float q[E];  // q_i = prod_{j>i} a_j
         q[E - 1] = 1.f;
 #pragma unroll
         for (int i = E - 2; i >= 0; --i) q[i] = q[i + 1] * fa[i + 1];
         float A = q[0] * fa[0];
-#pragma unroll
-        for (int i = 0; i < E; ++i) om[i] = 1.f - fa[i];
         float Alvl[5];
 #pragma unroll
         for (int k = 0; k < 5; ++k) {
@@ -833,9 +828,12 @@ fm_layer_backward_ring_kernel(const S *__restrict__ gates, const S *__restrict__
         float eA = __shfl_down_sync(kFullMask, A, 1);
         if (lane == 31) eA = 1.f;
         const float tA = __shfl_sync(kFullMask, A, 0);
-        float dg[E];
+        // d_gates[t] = (1/r[t-1]) * sum_d delta * hn[t-1] - sum_d delta * x[t]: the raw state is
+        // hn / r, and 1/r does not depend on d, so the two sums run over the NORMALISED states and
+        // the tokens and 1/r is applied once per step
+        float dgh[E], dgx[E];
 #pragma unroll
-        for (int i = 0; i < E; ++i) dg[i] = 0.f;
+        for (int i = 0; i < E; ++i) dgh[i] = dgx[i] = 0.f;
         float defer = 0.f;
 
 #pragma unroll
@@ -856,7 +854,6 @@ fm_layer_backward_ring_kernel(const S *__restrict__ gates, const S *__restrict__
                 float gi = fmaf(f1[i], fd[i], -fh[i] * f2[i]);  // r*w*dout - hn*r*c
                 if constexpr (EXT) gi = fmaf(frn[i], fe[i], gi);
                 fg[i] = gi;
-                fh[i] *= fri[i];  // raw state
             }
             // the lane's own reverse scan from a zero carry: dl_i = G_i + a_{i+1} * dl_{i+1}
             float dl[E];
@@ -872,8 +869,9 @@ fm_layer_backward_ring_kernel(const S *__restrict__ gates, const S *__restrict__
             float eC = __shfl_down_sync(kFullMask, C, 1);
             if (lane == 31) eC = 0.f;
             const float tC = __shfl_sync(kFullMask, C, 0);
-            // raw state before this lane's vector; lane 0 gets lane 31's last one, which belongs
-            // in front of the tile processed one step ago (see fm_backward_ring_kernel)
+            // normalised state before this lane's vector; lane 0 gets lane 31's last one, which
+            // belongs in front of the tile processed one step ago (see fm_backward_ring_kernel).
+            // At the very first position the state before is the RAW initial state (factor 1 below).
             float hprev0 = __shfl_sync(kFullMask, fh[E - 1], (lane + 31) & 31);
             if (lane == 0) {
                 defer = fmaf(pend[d], hprev0, defer);
@@ -886,16 +884,28 @@ fm_layer_backward_ring_kernel(const S *__restrict__ gates, const S *__restrict__
             for (int i = 0; i < E; ++i) {
                 const float delta = fmaf(q[i], c, dl[i]);
                 const float hp = (i > 0) ? fh[i > 0 ? i - 1 : 0] : hprev0;
-                dg[i] = fmaf(delta, hp - fx[i], dg[i]);
-                dxv[i] = om[i] * delta;
+                dgh[i] = fmaf(delta, hp, dgh[i]);
+                dgx[i] = fmaf(delta, fx[i], dgx[i]);
+                dxv[i] = fmaf(-fa[i], delta, delta);  // (1 - a) * delta, one rounding
                 if (i == 0) pend[d] = delta;
             }
 #pragma unroll
             for (int k = 0; k < E / 4; ++k)
                 part[w][d][k][lane] = make_float4(dxv[4 * k], dxv[4 * k + 1], dxv[4 * k + 2], dxv[4 * k + 3]);
         }
-        if (in && have_m) red_vec<E, false>(acc_gates + grow_off, t, L, dg);
-        if (lane == 0 && have_m && tile + 1 < ntiles) atomicAdd(acc_gates + grow_off + (tile + 1) * W, defer);
+        {
+            float fri[E], dg[E];
+            load_f32(rinv, t, in && have_m, 1.f, fri);
+            // 1/r of the position before each element: the previous lane's last one for element 0
+            // (lane 0 receives lane 31's, which is the factor of its deferred sum)
+            const float rrot = __shfl_sync(kFullMask, fri[E - 1], (lane + 31) & 31);
+            dg[0] = fmaf((lane == 0) ? 1.f : rrot, dgh[0], -dgx[0]);
+#pragma unroll
+            for (int i = 1; i < E; ++i) dg[i] = fmaf(fri[i - 1], dgh[i], -dgx[i]);
+            if (in && have_m) red_vec<E, false>(acc_gates + grow_off, t, L, dg);
+            if (lane == 0 && have_m && tile + 1 < ntiles)
+                atomicAdd(acc_gates + grow_off + (tile + 1) * W, defer * rrot);
+        }
         __syncthreads();  // every warp has published its tiles; the next token / dout tiles have landed
 #pragma unroll
         for (int d = w; d < DC; d += MC) {

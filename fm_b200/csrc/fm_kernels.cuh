@@ -399,7 +399,8 @@ fm_readout_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ tok
     const int lane = threadIdx.x & 31;
     const int w = threadIdx.x >> 5;
     const int64_t blk = blockIdx.x;
-    const int64_t db = blk % d_blocks, mb = (blk / d_blocks) % m_blocks, b = blk / (d_blocks * m_blocks);
+    // m blocks fastest: the CTAs that add into the same output rows run side by side (L2)
+    const int64_t mb = blk % m_blocks, db = (blk / m_blocks) % d_blocks, b = blk / (d_blocks * m_blocks);
     const int64_t m = mb * MC + w, d0 = db * DC;
     const bool have_m = m < M;
     const int64_t ntiles = (L + W - 1) / W;
@@ -487,45 +488,65 @@ fm_readout_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ tok
         if (lane == 0) eA = 1.f;
         const float tA = __shfl_sync(kFullMask, A, 31);
 
+        // two rows at a time, stage by stage: one row's shuffle chain covers the other's latency
+        constexpr int R2 = 2;
 #pragma unroll
-        for (int d = 0; d < DC; ++d) {
-            float fx[E];
-            Store<S>::unpack(xs[buf][d][lane], fx);
+        for (int d = 0; d < DC; d += R2) {
+            float fx[R2][E], H[R2];
 #pragma unroll
-            for (int i = 0; i < E; ++i) fx[i] *= om[i];
-            float H = fx[0];
+            for (int r = 0; r < R2; ++r)
+                if (d + r < DC) Store<S>::unpack(xs[buf][d + r < DC ? d + r : 0][lane], fx[r]);
 #pragma unroll
-            for (int i = 1; i < E; ++i) H = fmaf(fa[i], H, fx[i]);
+            for (int r = 0; r < R2; ++r) {
+#pragma unroll
+                for (int i = 0; i < E; ++i) fx[r][i] *= om[i];
+                H[r] = fx[r][0];
+#pragma unroll
+                for (int i = 1; i < E; ++i) H[r] = fmaf(fa[i], H[r], fx[r][i]);
+            }
 #pragma unroll
             for (int k = 0; k < 5; ++k) {
-                const float pH = __shfl_up_sync(kFullMask, H, 1 << k);
-                if (lane >= (1 << k)) H = fmaf(Alvl[k], pH, H);
-            }
-            float eH = __shfl_up_sync(kFullMask, H, 1);
-            if (lane == 0) eH = 0.f;
-            const float tH = __shfl_sync(kFullMask, H, 31);
-            float s_ = fmaf(eA, carry[d], eH);
-            carry[d] = fmaf(tA, carry[d], tH);
-            const bool row_ok = have_m && d0 + d < D;
-            float contrib[E], hn[STORE ? E : 1];
 #pragma unroll
-            for (int i = 0; i < E; ++i) {
-                s_ = fmaf(fa[i], s_, fx[i]);
-                if constexpr (MODE == 0) {
-                    if (row_ok) ss[i] = fmaf(s_, s_, ss[i]);
-                } else {
-                    contrib[i] = sc[i] * s_;  // sc is zero for lanes and gate rows outside the problem
+                for (int r = 0; r < R2; ++r) {
+                    const float pH = __shfl_up_sync(kFullMask, H[r], 1 << k);
+                    if (lane >= (1 << k)) H[r] = fmaf(Alvl[k], pH, H[r]);
                 }
-                if constexpr (STORE) hn[i] = s_ * rn[i];
             }
-            if constexpr (STORE) {
-                if (in && row_ok) stg_stream(states_out + (row0 + d) * L + t, Store<S>::pack(hn));
-            }
-            if constexpr (READOUT) {
+            float eH[R2], tH[R2];
 #pragma unroll
-                for (int k = 0; k < E / 4; ++k)
-                    part[w][d][k][lane] =
-                        make_float4(contrib[4 * k], contrib[4 * k + 1], contrib[4 * k + 2], contrib[4 * k + 3]);
+            for (int r = 0; r < R2; ++r) {
+                eH[r] = __shfl_up_sync(kFullMask, H[r], 1);
+                if (lane == 0) eH[r] = 0.f;
+                tH[r] = __shfl_sync(kFullMask, H[r], 31);
+            }
+#pragma unroll
+            for (int r = 0; r < R2; ++r) {
+                if (d + r < DC) {
+                    const int dd = d + r < DC ? d + r : 0;
+                    float s_ = fmaf(eA, carry[dd], eH[r]);
+                    carry[dd] = fmaf(tA, carry[dd], tH[r]);
+                    const bool row_ok = have_m && d0 + dd < D;
+                    float contrib[E], hn[STORE ? E : 1];
+#pragma unroll
+                    for (int i = 0; i < E; ++i) {
+                        s_ = fmaf(fa[i], s_, fx[r][i]);
+                        if constexpr (MODE == 0) {
+                            if (row_ok) ss[i] = fmaf(s_, s_, ss[i]);
+                        } else {
+                            contrib[i] = sc[i] * s_;  // sc is zero for lanes and gate rows outside the problem
+                        }
+                        if constexpr (STORE) hn[i] = s_ * rn[i];
+                    }
+                    if constexpr (STORE) {
+                        if (in && row_ok) stg_stream(states_out + (row0 + dd) * L + t, Store<S>::pack(hn));
+                    }
+                    if constexpr (READOUT) {
+#pragma unroll
+                        for (int k = 0; k < E / 4; ++k)
+                            part[w][dd][k][lane] =
+                                make_float4(contrib[4 * k], contrib[4 * k + 1], contrib[4 * k + 2], contrib[4 * k + 3]);
+                    }
+                }
             }
         }
         if constexpr (MODE == 0) {
@@ -538,19 +559,23 @@ fm_readout_blocked_kernel(const S *__restrict__ gates, const S *__restrict__ tok
             __syncthreads();  // every warp has published its tiles
 #pragma unroll
             for (int d = w; d < DC; d += MC) {
-                float v[E];
+                float2 v2[E / 2];  // pairs of neighbouring positions: add.f32x2
 #pragma unroll
-                for (int i = 0; i < E; ++i) v[i] = 0.f;
+                for (int k = 0; k < E / 2; ++k) v2[k] = make_float2(0.f, 0.f);
 #pragma unroll
                 for (int ww = 0; ww < MC; ++ww)
 #pragma unroll
                     for (int k = 0; k < E / 4; ++k) {
                         const float4 p = part[ww][d][k][lane];
-                        v[4 * k] += p.x;
-                        v[4 * k + 1] += p.y;
-                        v[4 * k + 2] += p.z;
-                        v[4 * k + 3] += p.w;
+                        v2[2 * k] = __fadd2_rn(v2[2 * k], make_float2(p.x, p.y));
+                        v2[2 * k + 1] = __fadd2_rn(v2[2 * k + 1], make_float2(p.z, p.w));
                     }
+                float v[E];
+#pragma unroll
+                for (int k = 0; k < E / 2; ++k) {
+                    v[2 * k] = v2[k].x;
+                    v[2 * k + 1] = v2[k].y;
+                }
                 if (in && d0 + d < D) red_vec<E, false>(out32 + (b * D + d0 + d) * L, t, L, v);
             }
         }

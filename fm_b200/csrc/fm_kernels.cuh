@@ -756,6 +756,10 @@ fm_layer_backward_ring_kernel(const S *__restrict__ gates, const S *__restrict__
     // [PD][NS][NT]: slot, {hn, ext}, thread -- read back only by the thread that copied
     uint4 *ring = reinterpret_cast<uint4 *>(fm_smem + sizeof(uint4) * 4 * DC * 32 +
                                             sizeof(float4) * MC * DC * (E / 4) * 32) + threadIdx.x;
+    // The step's fp32 factor rows p1, p2 ([2][E/4][NT] float4) travel one step ahead the same way
+    // (without ext only: with it the second ring stream takes the shared memory).
+    constexpr bool FACPF = !EXT;
+    float4 *fac = reinterpret_cast<float4 *>(ring - threadIdx.x + PD * NS * NT) + threadIdx.x;
     const int lane = threadIdx.x & 31;
     const int w = threadIdx.x >> 5;
     const int64_t blk = blockIdx.x;
@@ -766,9 +770,16 @@ fm_layer_backward_ring_kernel(const S *__restrict__ gates, const S *__restrict__
     const int64_t grow_off = (b * M + (have_m ? m : 0)) * L;
     const S *grow = gates + grow_off;
     const int64_t row0 = ((b * M + (have_m ? m : 0)) * D + d0);
-    float carry[DC], pend[DC];
+    // delta of lane 0's first position per row, kept for one step (used by lane 0 only)
+    constexpr size_t kPendOff = sizeof(uint4) * 4 * DC * 32 + sizeof(float4) * MC * DC * (E / 4) * 32 +
+                                sizeof(uint4) * PD * NS * NT +
+                                (EXT ? 0 : sizeof(float4) * 2 * (E / 4) * NT);  // behind the ring and the factors
+    float *pend = reinterpret_cast<float *>(fm_smem + kPendOff) + w * DC;
+    float carry[DC];
 #pragma unroll
-    for (int d = 0; d < DC; ++d) carry[d] = pend[d] = 0.f;
+    for (int d = 0; d < DC; ++d) carry[d] = 0.f;
+    if (lane < DC) pend[lane] = 0.f;
+    __syncwarp();
 
     auto fetch = [&](int slot, int64_t tile, int d) {
         const int64_t t = tile * W + lane * E;
@@ -798,7 +809,17 @@ fm_layer_backward_ring_kernel(const S *__restrict__ gates, const S *__restrict__
                    ? ldg_stream(grow + tt)
                    : make_uint4(Store<S>::kOne, Store<S>::kOne, Store<S>::kOne, Store<S>::kOne);
     };
+    auto stage_factors = [&](int64_t tile) {
+        const int64_t tt = tile * W + lane * E;
+        const bool ok = tile >= 0 && tt < L && have_m;
+#pragma unroll
+        for (int k = 0; k < E / 4; ++k) {
+            fm_cp_async16(fac + k * NT, p1 + (ok ? grow_off + tt + 4 * k : 0), ok);
+            fm_cp_async16(fac + (E / 4 + k) * NT, p2 + (ok ? grow_off + tt + 4 * k : 0), ok);
+        }
+    };
     stage_rows(0, ntiles - 1);
+    if constexpr (FACPF) stage_factors(ntiles - 1);
     fm_cp_async_commit();
 #pragma unroll
     for (int p = 0; p < PD; ++p) fetch(p, ntiles - 1, p);
@@ -828,8 +849,19 @@ fm_layer_backward_ring_kernel(const S *__restrict__ gates, const S *__restrict__
         Store<S>::unpack(gq, fa);
         gq = load_g(tile - 1);
         stage_rows(buf ^ 1u, tile - 1);  // rides in the copy group of the first row below
-        load_f32(p1, t, in && have_m, 0.f, f1);
-        load_f32(p2, t, in && have_m, 0.f, f2);
+        if constexpr (FACPF) {
+            // landed with an earlier group of this thread (zeros outside the problem)
+#pragma unroll
+            for (int k = 0; k < E / 4; ++k) {
+                const float4 a4 = fac[k * NT], b4 = fac[(E / 4 + k) * NT];
+                f1[4 * k] = a4.x, f1[4 * k + 1] = a4.y, f1[4 * k + 2] = a4.z, f1[4 * k + 3] = a4.w;
+                f2[4 * k] = b4.x, f2[4 * k + 1] = b4.y, f2[4 * k + 2] = b4.z, f2[4 * k + 3] = b4.w;
+            }
+            stage_factors(tile - 1);  // rides in the copy group of the first row below
+        } else {
+            load_f32(p1, t, in && have_m, 0.f, f1);
+            load_f32(p2, t, in && have_m, 0.f, f2);
+        }
         float frn[EXT ? E : 1];
         if constexpr (EXT) {
             if (rnorm) load_f32(rnorm, t, in && have_m, 1.f, frn);
@@ -912,7 +944,7 @@ fm_layer_backward_ring_kernel(const S *__restrict__ gates, const S *__restrict__
                 dgh[i] = fmaf(delta, hp, dgh[i]);
                 dgx[i] = fmaf(delta, fx[i], dgx[i]);
                 dxv[i] = fmaf(-fa[i], delta, delta);  // (1 - a) * delta, one rounding
-                if (i == 0) pend[d] = delta;
+                if (i == 0 && lane == 0) pend[d] = delta;
             }
 #pragma unroll
             for (int k = 0; k < E / 4; ++k)
@@ -965,7 +997,8 @@ fm_layer_backward_ring_kernel(const S *__restrict__ gates, const S *__restrict__
 template <typename S, int MC, int DC, int PD, bool EXT>
 constexpr size_t fm_layer_backward_smem() {
     return sizeof(uint4) * 4 * DC * 32 + sizeof(float4) * MC * DC * (Store<S>::E / 4) * 32 +
-           sizeof(uint4) * PD * (EXT ? 2 : 1) * MC * 32;
+           sizeof(uint4) * PD * (EXT ? 2 : 1) * MC * 32 +
+           (EXT ? 0 : sizeof(float4) * 2 * (Store<S>::E / 4) * MC * 32) + sizeof(float) * MC * DC;
 }
 
 }  // namespace fms

@@ -336,7 +336,10 @@ def run_ours(args):
 
     time_split = None
     if not args.no_extras and args.rows == 0:
-        time_split = measure_time_split(args, world, rank, device, barrier, max_over_ranks)
+        try:
+            time_split = measure_time_split(args, world, rank, device, barrier, max_over_ranks)
+        except Exception as e:  # the headline figures above stand on their own
+            time_split = {"unavailable": "%s: %s" % (type(e).__name__, str(e)[:200])}
         torch.cuda.empty_cache()
 
     if rank == 0:

@@ -599,7 +599,7 @@ __global__ void fm_readout_scale_kernel(float *__restrict__ sumsq_to_scale, cons
 
 // Dynamic shared memory fm_readout_blocked_kernel needs (token tiles and the per-warp partial tiles).
 template <typename S, int MC, int DC>
-constexpr size_t fm_backward_blocked_smem() {
+constexpr size_t fm_readout_smem() {
     return sizeof(uint4) * 2 * DC * 32 + sizeof(float4) * MC * DC * (Store<S>::E / 4) * 32;
 }
 

@@ -734,7 +734,7 @@ int launch_fm_readout(const FmShape &sh, const void *gates, const void *tokens, 
     const int64_t m_blocks = (sh.M + MC - 1) / MC, d_blocks = (sh.D + DC - 1) / DC;
     if (sh.B > 0x7fffffffLL / m_blocks || sh.B * m_blocks > 0x7fffffffLL / d_blocks) return FMS_ERR_BAD_SHAPE;
     const unsigned grid = static_cast<unsigned>(sh.B * m_blocks * d_blocks);
-    constexpr size_t smem = fms::fm_backward_blocked_smem<S, MC, DC>();
+    constexpr size_t smem = fms::fm_readout_smem<S, MC, DC>();
     const int64_t n_g = sh.B * sh.M * sh.L, n_x = sh.B * sh.D * sh.L;
     auto k0 = fms::fm_readout_blocked_kernel<S, MC, DC, 0>;
     auto k1 = fms::fm_readout_blocked_kernel<S, MC, DC, 1>;
